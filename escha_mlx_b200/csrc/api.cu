@@ -1,0 +1,339 @@
+// extern "C" boundary of libescha_b200.so: argument validation, error
+// reporting and dispatch to the kernel launchers.  Declarations and the
+// reference call each one replaces are in include/escha_b200.h.
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+
+#include "../../include/escha_b200.h"
+#include "kernels.h"
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+int cuda_result(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return ESCHA_OK;
+    return fail(ESCHA_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#define REQUIRE_PTR(p)                                                                  \
+    do {                                                                                \
+        if ((p) == nullptr) return fail(ESCHA_EINVAL, "%s: %s is NULL", __func__, #p);  \
+        if (!aligned16(p)) return fail(ESCHA_EINVAL, "%s: %s is not 16-byte aligned", __func__, #p); \
+    } while (0)
+#define OPTIONAL_PTR(p)                                                                 \
+    do {                                                                                \
+        if ((p) != nullptr && !aligned16(p))                                            \
+            return fail(ESCHA_EINVAL, "%s: %s is not 16-byte aligned", __func__, #p);   \
+    } while (0)
+#define REQUIRE(cond, ...)                                   \
+    do {                                                     \
+        if (!(cond)) return fail(ESCHA_EINVAL, __VA_ARGS__); \
+    } while (0)
+
+int check_shape(const char* fn, int K, int IC, int OC, int mult) {
+    if (K != 2 && K != 3)
+        return fail(ESCHA_EINVAL, "%s: K=%d; this runtime implements K in [2, 3]", fn, K);
+    if (IC <= 0 || OC <= 0 || IC % mult || OC % mult)
+        return fail(ESCHA_EINVAL, "%s: dimensions must be positive multiples of %d, got %dx%d", fn,
+                    mult, IC, OC);
+    return ESCHA_OK;
+}
+
+cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" {
+
+int escha_version(void) { return ESCHA_ABI_VERSION; }
+
+const char* escha_last_error(void) { return g_err.c_str(); }
+
+int escha_lut_init(void* lut, void* stream) {
+    REQUIRE_PTR(lut);
+    return cuda_result(escha::launch_lut_init(static_cast<__half*>(lut), as_stream(stream)),
+                       "escha_lut_init");
+}
+
+int escha_decode_tiles(const void* code, int K, int IC, int OC, const void* lut, void* w,
+                       void* stream) {
+    if (int rc = check_shape(__func__, K, IC, OC, 16)) return rc;
+    REQUIRE_PTR(code);
+    REQUIRE_PTR(w);
+    OPTIONAL_PTR(lut);
+    REQUIRE(IC / 16 <= 65535, "%s: IC=%d exceeds the launch grid", __func__, IC);
+    return cuda_result(
+        escha::launch_decode_tiles(static_cast<const uint32_t*>(code), K, IC, OC,
+                                   static_cast<const __half*>(lut), static_cast<__half*>(w),
+                                   as_stream(stream)),
+        "escha_decode_tiles");
+}
+
+int escha_scaled_had(const void* rows, const float* rin, const int32_t* row_expert, int M, int IC,
+                     float rs, void* out, void* stream) {
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE(IC > 0 && IC % 128 == 0, "%s: Hadamard dimension must be divisible by 128, got %d",
+            __func__, IC);
+    REQUIRE_PTR(rows);
+    REQUIRE_PTR(rin);
+    REQUIRE_PTR(out);
+    return cuda_result(
+        escha::launch_scaled_had(false, rows, rin, static_cast<__half*>(out), IC, nullptr, nullptr,
+                                 nullptr, 0, row_expert, M, rs, as_stream(stream)),
+        "escha_scaled_had");
+}
+
+int escha_scaled_had_out(const float* mid, const float* rout, const int32_t* row_expert, int M,
+                         int OC, float rs, void* out, void* stream) {
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE(OC > 0 && OC % 128 == 0, "%s: Hadamard dimension must be divisible by 128, got %d",
+            __func__, OC);
+    REQUIRE_PTR(mid);
+    REQUIRE_PTR(rout);
+    REQUIRE_PTR(out);
+    return cuda_result(
+        escha::launch_scaled_had(true, mid, rout, static_cast<__half*>(out), OC, nullptr, nullptr,
+                                 nullptr, 0, row_expert, M, rs, as_stream(stream)),
+        "escha_scaled_had_out");
+}
+
+int escha_scaled_had_pair(const void* rows, const float* rin0, const float* rin1, int M, int IC,
+                          float rs, void* out0, void* out1, void* stream) {
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE(IC > 0 && IC % 128 == 0, "%s: Hadamard dimension must be divisible by 128, got %d",
+            __func__, IC);
+    REQUIRE_PTR(rows);
+    REQUIRE_PTR(rin0);
+    REQUIRE_PTR(rin1);
+    REQUIRE_PTR(out0);
+    REQUIRE_PTR(out1);
+    return cuda_result(
+        escha::launch_scaled_had(false, rows, rin0, static_cast<__half*>(out0), IC, rows, rin1,
+                                 static_cast<__half*>(out1), IC, nullptr, M, rs, as_stream(stream)),
+        "escha_scaled_had_pair");
+}
+
+int escha_scaled_had_out_pair(const float* mid0, const float* mid1, const float* rout0,
+                              const float* rout1, int M, int OC0, int OC1, float rs, void* out0,
+                              void* out1, void* stream) {
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE(OC0 > 0 && OC0 % 128 == 0 && OC1 > 0 && OC1 % 128 == 0,
+            "%s: Hadamard dimensions must be divisible by 128, got %d and %d", __func__, OC0, OC1);
+    REQUIRE_PTR(mid0);
+    REQUIRE_PTR(mid1);
+    REQUIRE_PTR(rout0);
+    REQUIRE_PTR(rout1);
+    REQUIRE_PTR(out0);
+    REQUIRE_PTR(out1);
+    return cuda_result(
+        escha::launch_scaled_had(true, mid0, rout0, static_cast<__half*>(out0), OC0, mid1, rout1,
+                                 static_cast<__half*>(out1), OC1, nullptr, M, rs, as_stream(stream)),
+        "escha_scaled_had_out_pair");
+}
+
+int escha_gemv_ref(const void* xh, const void* code, const int32_t* row_expert,
+                   const int32_t* row_map, int slots, const void* lut, int M, int IC, int OC,
+                   int K, int splits, float* part, float* mid, void* stream) {
+    if (int rc = check_shape(__func__, K, IC, OC, 128)) return rc;
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE_PTR(xh);
+    REQUIRE_PTR(code);
+    REQUIRE_PTR(mid);
+    OPTIONAL_PTR(lut);
+    if (splits < 1) splits = 1;
+    REQUIRE((IC / 16) % splits == 0, "%s: splits=%d does not divide IC/16=%d", __func__, splits,
+            IC / 16);
+    if (row_map) {
+        REQUIRE(splits == 1, "%s: a row_map requires splits == 1", __func__);
+        REQUIRE(slots >= 1, "%s: row_map needs slots >= 1", __func__);
+    } else {
+        slots = M;
+    }
+    REQUIRE(slots <= 65535 && splits <= 65535, "%s: %d slots exceed the launch grid", __func__,
+            slots);
+    if (splits > 1) REQUIRE_PTR(part);
+    return cuda_result(
+        escha::launch_gemv_ref(static_cast<const __half*>(xh), static_cast<const uint32_t*>(code),
+                               row_expert, row_map, slots, static_cast<const __half*>(lut), mid,
+                               part, M, IC, OC, K, splits, as_stream(stream)),
+        "escha_gemv_ref");
+}
+
+size_t escha_coded_gemv_workspace_bytes(int njobs, int OC, int splits, int rows_per_job) {
+    if (njobs < 1 || OC < 128 || rows_per_job < 1) return 0;
+    const size_t counters = align_up(static_cast<size_t>(njobs) * (OC / 128) * sizeof(int32_t), 256);
+    return counters + escha::gemv_mma_part_floats(njobs, splits, OC, rows_per_job) * sizeof(float);
+}
+
+int escha_coded_gemv_splits(int IC, int OC, int njobs, int sm_count) {
+    if (IC < 128 || OC < 128) return 1;
+    if (sm_count <= 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            sm_count = 148;
+    }
+    if (njobs < 1) njobs = 1;
+    const int nblk = IC / 128;
+    const long ctas = static_cast<long>(OC / 128) * njobs;
+    const long target = 2L * sm_count;  // two resident CTAs per SM
+    long s = (target + ctas - 1) / ctas;
+    // keep at least two 128-channel blocks per split so the pipeline has depth
+    const long smax = nblk >= 2 ? nblk / 2 : 1;
+    if (s > smax) s = smax;
+    if (s < 1) s = 1;
+    return static_cast<int>(s);
+}
+
+int escha_coded_gemv(const void* xh, const void* code, const float* rout, int M, int IC, int OC,
+                     int K, int splits, float rs, void* workspace, size_t workspace_bytes,
+                     void* out, void* stream) {
+    if (int rc = check_shape(__func__, K, IC, OC, 128)) return rc;
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE_PTR(xh);
+    REQUIRE_PTR(code);
+    REQUIRE_PTR(out);
+    OPTIONAL_PTR(rout);
+    const int rows_per_job = M <= 8 ? 8 : 16;
+    const int njobs = (M + rows_per_job - 1) / rows_per_job;
+    REQUIRE(njobs <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
+    if (splits <= 0) splits = escha_coded_gemv_splits(IC, OC, njobs, 0);
+    REQUIRE(splits <= IC / 128, "%s: splits=%d exceeds the %d input blocks", __func__, splits,
+            IC / 128);
+    escha::GemvMmaParams p{};
+    p.x = static_cast<const __half*>(xh);
+    p.code = static_cast<const uint32_t*>(code);
+    p.rout = rout;
+    p.jobs = nullptr;
+    p.out = out;
+    p.M = M; p.IC = IC; p.OC = OC; p.K = K;
+    p.splits = splits;
+    p.rows_per_job = rows_per_job;
+    p.njobs = njobs;
+    p.rs = rs;
+    if (splits > 1) {
+        const size_t need = escha_coded_gemv_workspace_bytes(njobs, OC, splits, rows_per_job);
+        REQUIRE_PTR(workspace);
+        REQUIRE(workspace_bytes >= need, "%s: workspace of %zu bytes is smaller than the %zu needed",
+                __func__, workspace_bytes, need);
+        const size_t counters = align_up(static_cast<size_t>(njobs) * (OC / 128) * sizeof(int32_t), 256);
+        p.counters = static_cast<int32_t*>(workspace);
+        p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters);
+    }
+    return cuda_result(escha::launch_gemv_mma(p, as_stream(stream)), "escha_coded_gemv");
+}
+
+int escha_moe_jobs_bound(int m, int E, int R) {
+    if (m < 1 || E < 1 || R < 1) return 0;
+    const long hit = m < E ? m : E;
+    return static_cast<int>((m + hit * (R - 1)) / R);
+}
+
+int escha_moe_group_rows(const int32_t* row_expert, int m, int E, int R, void* jobs,
+                         int njobs_cap, int32_t* njobs_out, void* stream) {
+    REQUIRE(m >= 1 && E >= 1, "%s: needs m >= 1 and E >= 1, got m=%d E=%d", __func__, m, E);
+    REQUIRE(R == 8 || R == 16, "%s: rows per job must be 8 or 16, got %d", __func__, R);
+    REQUIRE(E <= 12000, "%s: E=%d exceeds the grouping kernel's shared memory", __func__, E);
+    REQUIRE_PTR(row_expert);
+    REQUIRE_PTR(jobs);
+    REQUIRE(njobs_cap >= escha_moe_jobs_bound(m, E, R),
+            "%s: njobs_cap=%d is below the bound %d for m=%d E=%d R=%d", __func__, njobs_cap,
+            escha_moe_jobs_bound(m, E, R), m, E, R);
+    return cuda_result(escha::launch_group_rows(row_expert, m, E, R,
+                                                static_cast<escha::RowJob*>(jobs), njobs_cap,
+                                                njobs_out, as_stream(stream)),
+                       "escha_moe_group_rows");
+}
+
+int escha_jobs_from_groups(const int32_t* rows_idx, const int32_t* group_expert, int n_groups,
+                           int R, int n_rows, int rows_per_job, void* jobs, void* stream) {
+    REQUIRE(n_groups >= 1 && R >= 1 && n_rows >= 1, "%s: empty grouping (n_groups=%d R=%d n_rows=%d)",
+            __func__, n_groups, R, n_rows);
+    REQUIRE(rows_per_job == 8 || rows_per_job == 16, "%s: rows per job must be 8 or 16, got %d",
+            __func__, rows_per_job);
+    REQUIRE_PTR(rows_idx);
+    REQUIRE_PTR(group_expert);
+    REQUIRE_PTR(jobs);
+    return cuda_result(
+        escha::launch_jobs_from_groups(rows_idx, group_expert, n_groups, R, n_rows, rows_per_job,
+                                       static_cast<escha::RowJob*>(jobs), as_stream(stream)),
+        "escha_jobs_from_groups");
+}
+
+int escha_coded_gemv_jobs(const void* xh, const void* code, const float* rout, const void* jobs,
+                          int njobs, int rows_per_job, int M, int E, int IC, int OC, int K,
+                          int splits, float rs, void* workspace, size_t workspace_bytes, void* out,
+                          void* stream) {
+    if (int rc = check_shape(__func__, K, IC, OC, 128)) return rc;
+    REQUIRE(M >= 1 && E >= 1, "%s: needs M >= 1 and E >= 1, got M=%d E=%d", __func__, M, E);
+    REQUIRE(njobs >= 1 && njobs <= 65535, "%s: njobs=%d outside [1, 65535]", __func__, njobs);
+    REQUIRE(rows_per_job == 8 || rows_per_job == 16, "%s: rows per job must be 8 or 16, got %d",
+            __func__, rows_per_job);
+    REQUIRE(splits >= 1 && splits <= IC / 128, "%s: splits=%d outside [1, %d]", __func__, splits,
+            IC / 128);
+    REQUIRE_PTR(xh);
+    REQUIRE_PTR(code);
+    REQUIRE_PTR(jobs);
+    REQUIRE_PTR(out);
+    OPTIONAL_PTR(rout);
+    escha::GemvMmaParams p{};
+    p.x = static_cast<const __half*>(xh);
+    p.code = static_cast<const uint32_t*>(code);
+    p.rout = rout;
+    p.jobs = static_cast<const escha::RowJob*>(jobs);
+    p.out = out;
+    p.M = M; p.IC = IC; p.OC = OC; p.K = K;
+    p.splits = splits;
+    p.rows_per_job = rows_per_job;
+    p.njobs = njobs;
+    p.rs = rs;
+    if (splits > 1) {
+        const size_t need = escha_coded_gemv_workspace_bytes(njobs, OC, splits, rows_per_job);
+        REQUIRE_PTR(workspace);
+        REQUIRE(workspace_bytes >= need, "%s: workspace of %zu bytes is smaller than the %zu needed",
+                __func__, workspace_bytes, need);
+        const size_t counters = align_up(static_cast<size_t>(njobs) * (OC / 128) * sizeof(int32_t), 256);
+        p.counters = static_cast<int32_t*>(workspace);
+        p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters);
+    }
+    return cuda_result(escha::launch_gemv_mma(p, as_stream(stream)), "escha_coded_gemv_jobs");
+}
+
+int escha_swiglu(const void* gu, int M, int I, void* h, void* stream) {
+    REQUIRE(M >= 1 && I >= 1, "%s: empty input (M=%d I=%d)", __func__, M, I);
+    REQUIRE_PTR(gu);
+    REQUIRE_PTR(h);
+    return cuda_result(escha::launch_swiglu(static_cast<const __half*>(gu), M, I,
+                                            static_cast<__half*>(h), as_stream(stream)),
+                       "escha_swiglu");
+}
+
+int escha_moe_combine(const void* d16, const float* scores, int T, int top_k, int H, void* y,
+                      void* stream) {
+    REQUIRE(T >= 1 && top_k >= 1 && H >= 1, "%s: empty input (T=%d top_k=%d H=%d)", __func__, T,
+            top_k, H);
+    REQUIRE_PTR(d16);
+    REQUIRE_PTR(scores);
+    REQUIRE_PTR(y);
+    return cuda_result(escha::launch_moe_combine(static_cast<const __half*>(d16), scores, T, top_k,
+                                                 H, static_cast<__half*>(y), as_stream(stream)),
+                       "escha_moe_combine");
+}
+
+}  // extern "C"

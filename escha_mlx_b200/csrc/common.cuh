@@ -1,0 +1,181 @@
+// Shared device helpers for the escha coded-projection kernels (sm_100a).
+//
+// Numeric contract (escha_mlx/ref.py:37-48, escha_mlx/msl.py:34-41 of the
+// reference): a 16-bit trellis state x decodes to
+//     r = ((x * 0xCBAC1FED) & 0x8FFF8FFF) ^ 0x3B603B60          (32-bit)
+//     w = fp16(lo16(r)) + fp16(hi16(r))                         (one RNE fp16 add)
+// Everything here is compiled without fast-math; the fp16 add is the hardware
+// binary16 adder (__hadd / __hadd2), never a float add.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace escha {
+
+constexpr float kRS = 0.088388347648f;  // 1/sqrt(128) as the format pins it (ref.py:30)
+
+__device__ __forceinline__ uint32_t cba_hash(uint32_t state16) {
+    return ((state16 * 0xCBAC1FEDu) & 0x8FFF8FFFu) ^ 0x3B603B60u;
+}
+
+__device__ __forceinline__ __half2 as_half2(uint32_t r) {
+    return *reinterpret_cast<__half2*>(&r);
+}
+
+__device__ __forceinline__ uint32_t as_u32(__half2 h) {
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Scalar decode: one state -> one half.
+__device__ __forceinline__ __half cba_decode(uint32_t state16) {
+    __half2 h = as_half2(cba_hash(state16));
+    return __hadd(__low2half(h), __high2half(h));
+}
+
+// Decode into both halves of a register: (w, w).  The tensor-core GEMV feeds
+// this straight into an mma A-fragment register against a (x, 0) B register.
+__device__ __forceinline__ uint32_t cba_decode_dup(uint32_t state16) {
+    __half2 h = as_half2(cba_hash(state16));
+    return as_u32(__hadd2(__low2half2(h), __high2half2(h)));
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// ---------------------------------------------------------------------------
+// Window extraction (escha_mlx/ref.py:64-93; msl.py:45-81).  `w` points at the
+// tile's 8K words (any address space); lane is the lane index within the warp.
+// Produces the lane's eight 16-bit states, zero-extended.
+// ---------------------------------------------------------------------------
+
+struct LaneK2 {
+    uint32_t i0, i1, sel;  // word indices and the byte selector that forms the window
+    __device__ __forceinline__ explicit LaneK2(uint32_t lane) {
+        i1 = lane >> 1;          // (lane*8) >> 4
+        i0 = (i1 + 15u) & 15u;   // previous word, tail-biting wrap
+        // even lane: window = (w[i0] << 16) | (w[i1] >> 16); odd lane: w[i1]
+        sel = (lane & 1u) ? 0x3210u : 0x5432u;
+    }
+};
+
+__device__ __forceinline__ void states_k2(uint32_t w0, uint32_t w1, uint32_t sel, uint32_t s[8]) {
+    uint32_t wv = prmt(w1, w0, sel);
+    uint32_t y1 = wv >> 2, y2 = wv >> 4, y3 = wv >> 6;
+    // state j is the 16-bit window at bit 2*(7-j); byte-aligned after the shifts
+    s[7] = prmt(wv, 0u, 0x4410u);
+    s[3] = prmt(wv, 0u, 0x4421u);
+    s[6] = prmt(y1, 0u, 0x4410u);
+    s[2] = prmt(y1, 0u, 0x4421u);
+    s[5] = prmt(y2, 0u, 0x4410u);
+    s[1] = prmt(y2, 0u, 0x4421u);
+    s[4] = prmt(y3, 0u, 0x4410u);
+    s[0] = prmt(y3, 0u, 0x4421u);
+}
+
+struct LaneK3 {
+    uint32_t i0, i2, sh;  // word indices (mod 24) and the funnel shift
+    __device__ __forceinline__ explicit LaneK3(uint32_t lane) {
+        uint32_t b1 = (lane * 8u + 257u) * 3u;
+        uint32_t b0 = b1 - 16u;
+        uint32_t b2 = b1 + 21u;
+        uint32_t j0 = b0 >> 5;
+        uint32_t j2 = (b2 - 1u) >> 5;
+        sh = ((j2 + 1u) << 5) - b2;
+        i0 = j0 % 24u;
+        i2 = j2 % 24u;
+    }
+};
+
+__device__ __forceinline__ void states_k3(uint32_t whi, uint32_t wlo, uint32_t sh, uint32_t s[8]) {
+    uint64_t merged = (static_cast<uint64_t>(whi) << 32) | static_cast<uint64_t>(wlo);
+    uint32_t w7 = static_cast<uint32_t>(merged >> sh);
+    uint32_t w3 = static_cast<uint32_t>(merged >> (sh + 12u));
+    s[0] = (w3 >> 9) & 0xFFFFu;
+    s[1] = (w3 >> 6) & 0xFFFFu;
+    s[2] = (w3 >> 3) & 0xFFFFu;
+    s[3] = w3 & 0xFFFFu;
+    s[4] = (w7 >> 9) & 0xFFFFu;
+    s[5] = (w7 >> 6) & 0xFFFFu;
+    s[6] = (w7 >> 3) & 0xFFFFu;
+    s[7] = w7 & 0xFFFFu;
+}
+
+template <int K>
+struct LaneConsts;
+template <>
+struct LaneConsts<2> : LaneK2 {
+    __device__ __forceinline__ explicit LaneConsts(uint32_t lane) : LaneK2(lane) {}
+    __device__ __forceinline__ uint32_t ia() const { return i0; }
+    __device__ __forceinline__ uint32_t ib() const { return i1; }
+    __device__ __forceinline__ void states(uint32_t wa, uint32_t wb, uint32_t s[8]) const {
+        states_k2(wa, wb, sel, s);
+    }
+};
+template <>
+struct LaneConsts<3> : LaneK3 {
+    __device__ __forceinline__ explicit LaneConsts(uint32_t lane) : LaneK3(lane) {}
+    __device__ __forceinline__ uint32_t ia() const { return i0; }
+    __device__ __forceinline__ uint32_t ib() const { return i2; }
+    __device__ __forceinline__ void states(uint32_t wa, uint32_t wb, uint32_t s[8]) const {
+        states_k3(wa, wb, sh, s);
+    }
+};
+
+// ---------------------------------------------------------------------------
+// 128-point unnormalised Sylvester WHT across one warp (escha_mlx/ref.py:204-218).
+// Element i of the block lives in lane i>>2, register i&3.  Stage h pairs i with
+// i^h; the low index receives a+b, the high index a-b, exactly the operands the
+// in-place reference butterfly uses at every stage, so results are bit-identical.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void wht128_warp(float v[4], uint32_t lane) {
+    {   // h = 1
+        float a = v[0], b = v[1], c = v[2], d = v[3];
+        v[0] = __fadd_rn(a, b); v[1] = __fsub_rn(a, b);
+        v[2] = __fadd_rn(c, d); v[3] = __fsub_rn(c, d);
+    }
+    {   // h = 2
+        float a = v[0], b = v[1], c = v[2], d = v[3];
+        v[0] = __fadd_rn(a, c); v[2] = __fsub_rn(a, c);
+        v[1] = __fadd_rn(b, d); v[3] = __fsub_rn(b, d);
+    }
+#pragma unroll
+    for (uint32_t m = 1; m < 32; m <<= 1) {  // h = 4*m
+        const bool high = (lane & m) != 0;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            float mine = v[r];
+            float other = __shfl_xor_sync(0xFFFFFFFFu, mine, m);
+            v[r] = high ? __fsub_rn(other, mine) : __fadd_rn(mine, other);
+        }
+    }
+}
+
+// cp.async helpers (16-byte, L2-only caching: the code stream is read once).
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// mma.sync m16n8k16, f16 x f16 -> f32 accumulate.
+__device__ __forceinline__ void mma16816(float d[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+}  // namespace escha

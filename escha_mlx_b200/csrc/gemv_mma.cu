@@ -1,0 +1,298 @@
+// Tensor-core coded GEMV / small-batch GEMM with split-K and a fused output
+// transform.  This is the fast path behind moe_gemv / dense_gemv /
+// dense_gemm_rows[_direct[_out]] / moe_gemm_rows of the reference's kernel layer
+// (escha_mlx/msl.py:1366-1478, :1785-1870): the same product
+//
+//     mid[r, :] = f32(xh[r, :]) @ f32(decode(code[expert(r)]))
+//
+// optionally followed in the same kernel by  y = f16((H128(mid) * RS) * rout).
+//
+// Why it looks the way it does on B200:
+//  * The reference's lane -> tile-position map (ref.lane_positions) is exactly
+//    the A-fragment ownership of mma.m16n8k16 for the transposed tile, so the
+//    eight halves a lane decodes go from registers straight into the tensor
+//    core; the activations are the B operand (up to 8 rows per mma column
+//    block), accumulation is fp32.  No cvt, no FMA chain, no shuffle reduction,
+//    and up to 16 rows share one decode for free.
+//  * Each decoded weight is kept as (w, w) in one register (a single HADD2 of
+//    the hash's two halves with half-select operands) and multiplied against
+//    (x, 0): this trades an idle half of the tensor core for two byte-permute
+//    instructions per weight pair on the integer pipe, which is the pipe that
+//    limits this kernel.
+//  * The code stream is read exactly once, as 16-byte cp.async copies into a
+//    warp-private shared-memory ring (6 stages x 8 tiles per warp); the main
+//    loop has no block-wide barrier except when the activation chunk is
+//    re-staged every 1024 input channels.
+//  * 128 output channels per CTA = one Hadamard block, so the CTA that
+//    completes a block can run the output transform with warp butterflies.
+//  * Split-K over 128-channel input blocks fills the 148 SMs for any shape.
+//    Partials go to caller-provided scratch; the CTA that arrives last for an
+//    output block sums them in ascending split order (no float atomics), so the
+//    result is bit-reproducible run to run for a given (shape, splits).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace escha {
+
+namespace {
+
+constexpr int NS = 6;              // cp.async ring depth (8-kt blocks) per warp
+constexpr int XC = 8;              // 128-channel blocks of activations staged at a time
+constexpr int XS = XC * 128 + 8;   // words per staged row; +8 keeps LDS.64 conflict-free
+
+template <int K>
+struct CodeFetch {
+    static constexpr int WPT = 8 * K;
+    static constexpr int PIECES_PER_KT = WPT / 4;    // 16-byte pieces per tile
+    static constexpr int PIECES = 8 * PIECES_PER_KT; // per 8-kt block: 32 (K=2) or 48 (K=3)
+    uint32_t src0, dst0, src1, dst1;                 // word offsets
+    bool has1;
+    __device__ __forceinline__ CodeFetch(uint32_t lane, uint32_t tile_row_words) {
+        uint32_t p = lane;
+        src0 = (p / PIECES_PER_KT) * tile_row_words + (p % PIECES_PER_KT) * 4u;
+        dst0 = p * 4u;
+        p = lane + 32u;
+        has1 = p < PIECES;
+        src1 = (p / PIECES_PER_KT) * tile_row_words + (p % PIECES_PER_KT) * 4u;
+        dst1 = p * 4u;
+    }
+    __device__ __forceinline__ void issue(uint32_t* stage, const uint32_t* gblock) const {
+        cp_async16(stage + dst0, gblock + src0);
+        if (PIECES > 32 && has1) cp_async16(stage + dst1, gblock + src1);
+    }
+};
+
+template <bool FUSED_OUT>
+__device__ __forceinline__ void finalize_row(float v[4], uint32_t lane, const float* rout_blk,
+                                             void* out, size_t off, float rs) {
+    if (FUSED_OUT) {
+        const float4 sc = *reinterpret_cast<const float4*>(rout_blk + lane * 4u);
+        wht128_warp(v, lane);
+        uint2 packed;
+        packed.x = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[0], rs), sc.x),
+                                            __fmul_rn(__fmul_rn(v[1], rs), sc.y)));
+        packed.y = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[2], rs), sc.z),
+                                            __fmul_rn(__fmul_rn(v[3], rs), sc.w)));
+        *reinterpret_cast<uint2*>(static_cast<__half*>(out) + off) = packed;
+    } else {
+        *reinterpret_cast<float4*>(static_cast<float*>(out) + off) =
+            make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+template <int K, int MT>
+__global__ void __launch_bounds__(256, 2)
+gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
+    constexpr int WPT = 8 * K;
+    constexpr int STAGE_WORDS = 8 * WPT;
+    constexpr int ROWS = 8 * MT;
+    extern __shared__ __align__(16) uint32_t smem[];
+    uint32_t* const s_code = smem;                       // [8 warps][NS][STAGE_WORDS]
+    uint32_t* const s_x = smem + 8 * NS * STAGE_WORDS;   // [rows][XS] as (x, 0) pairs
+    __shared__ int s_rows[16];
+    __shared__ int s_last;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t ocb = blockIdx.x, split = blockIdx.y, job = blockIdx.z;
+    const uint32_t TN = p.OC >> 4, OCB = p.OC >> 7, nblk = p.IC >> 7;
+
+    int expert = 0, nrows;
+    if (p.jobs) {
+        const RowJob* jb = p.jobs + job;
+        expert = jb->expert;
+        nrows = jb->nrows;
+        if (tid < 16) s_rows[tid] = jb->rows[tid];
+    } else {
+        const int r0 = static_cast<int>(job) * ROWS;
+        nrows = min(ROWS, p.M - r0);
+        if (tid < 16) s_rows[tid] = r0 + static_cast<int>(tid);
+    }
+    if (nrows <= 0) return;  // uniform for the CTA
+
+    // this CTA's range of 128-channel input blocks
+    const uint32_t S = p.splits;
+    const uint32_t bbase = nblk / S, brem = nblk % S;
+    const uint32_t b0 = split * bbase + min(split, brem);
+    const uint32_t nb = bbase + (split < brem ? 1u : 0u);
+
+    const uint32_t tile_row_words = TN * WPT;  // words between kt and kt+1 of one tile column
+    const uint32_t* gtile = p.code + static_cast<size_t>(expert) * (p.IC >> 4) * tile_row_words +
+                            (ocb * 8u + warp) * WPT;
+    uint32_t* const my_stages = s_code + warp * (NS * STAGE_WORDS);
+    const CodeFetch<K> fetch(lane, tile_row_words);
+    const LaneConsts<K> lc(lane);
+
+    // prologue: fill NS-1 stages
+#pragma unroll
+    for (int s = 0; s < NS - 1; ++s) {
+        if (static_cast<uint32_t>(s) < nb)
+            fetch.issue(my_stages + s * STAGE_WORDS,
+                        gtile + static_cast<size_t>(b0 + s) * 8u * tile_row_words);
+        cp_async_commit();
+    }
+
+    float d[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d[mt][i] = 0.0f;
+
+    bool row_ok[MT];
+    const uint32_t* xrow[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        row_ok[mt] = static_cast<int>(g) + 8 * mt < nrows;
+        xrow[mt] = s_x + (g + 8u * mt) * XS + 2u * t;
+    }
+
+    for (uint32_t i = 0; i < nb; ++i) {
+        const uint32_t cblk = i % XC;
+        if (cblk == 0) {
+            // (re)stage activations for blocks [b0+i, b0+i+cnt) as (x, 0) word pairs
+            __syncthreads();
+            const uint32_t cnt = min(static_cast<uint32_t>(XC), nb - i);
+            const uint32_t vec_per_row = cnt * 16u;  // 8-half vectors per row
+            const uint32_t total = static_cast<uint32_t>(nrows) * vec_per_row;
+            for (uint32_t idx = tid; idx < total; idx += 256u) {
+                const uint32_t r = idx / vec_per_row, v = idx - r * vec_per_row;
+                const uint4 raw = *reinterpret_cast<const uint4*>(
+                    p.x + static_cast<size_t>(s_rows[r]) * p.IC + (b0 + i) * 128u + v * 8u);
+                uint4* dst = reinterpret_cast<uint4*>(s_x + r * XS + v * 8u);
+                dst[0] = make_uint4(raw.x & 0xFFFFu, raw.x >> 16, raw.y & 0xFFFFu, raw.y >> 16);
+                dst[1] = make_uint4(raw.z & 0xFFFFu, raw.z >> 16, raw.w & 0xFFFFu, raw.w >> 16);
+            }
+            __syncthreads();
+        }
+        cp_async_wait<NS - 2>();
+        __syncwarp();
+        {
+            const uint32_t nxt = i + NS - 1;
+            if (nxt < nb)
+                fetch.issue(my_stages + (nxt % NS) * STAGE_WORDS,
+                            gtile + static_cast<size_t>(b0 + nxt) * 8u * tile_row_words);
+            cp_async_commit();
+        }
+        const uint32_t* stage = my_stages + (i % NS) * STAGE_WORDS;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t* tw = stage + kk * WPT;
+            uint32_t s[8], a[8];
+            lc.states(tw[lc.ia()], tw[lc.ib()], s);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] = cba_decode_dup(s[j]);
+            const uint32_t koff = (cblk * 8u + kk) * 16u;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint2 b01 = make_uint2(0u, 0u), b23 = make_uint2(0u, 0u);
+                if (row_ok[mt]) {
+                    b01 = *reinterpret_cast<const uint2*>(xrow[mt] + koff);
+                    b23 = *reinterpret_cast<const uint2*>(xrow[mt] + koff + 8u);
+                }
+                // value j sits at (channel g + 8*(j>=4), input 2t + (j&1) + 8*((j>>1)&1))
+                mma16816(d[mt], a[0], a[4], a[2], a[6], b01.x, b23.x);
+                mma16816(d[mt], a[1], a[5], a[3], a[7], b01.y, b23.y);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // accumulators -> shared [ROWS][128] (aliases the drained code ring)
+    float* const s_acc = reinterpret_cast<float*>(s_code);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const uint32_t ch = warp * 16u + g, n0 = 2u * t + 8u * mt;
+        s_acc[n0 * 128u + ch] = d[mt][0];
+        s_acc[(n0 + 1u) * 128u + ch] = d[mt][1];
+        s_acc[n0 * 128u + ch + 8u] = d[mt][2];
+        s_acc[(n0 + 1u) * 128u + ch + 8u] = d[mt][3];
+    }
+    __syncthreads();
+
+    const float* rout_blk =
+        p.rout ? p.rout + static_cast<size_t>(expert) * p.OC + ocb * 128u : nullptr;
+
+    if (S == 1) {
+        for (uint32_t r = warp; r < static_cast<uint32_t>(nrows); r += 8u) {
+            const float4 a4 = *reinterpret_cast<const float4*>(s_acc + r * 128u + lane * 4u);
+            float v[4] = {a4.x, a4.y, a4.z, a4.w};
+            const size_t off = static_cast<size_t>(s_rows[r]) * p.OC + ocb * 128u + lane * 4u;
+            if (p.rout) finalize_row<true>(v, lane, rout_blk, p.out, off, p.rs);
+            else finalize_row<false>(v, lane, rout_blk, p.out, off, p.rs);
+        }
+        return;
+    }
+
+    // split-K: publish this CTA's partial, last arriver reduces in split order
+    const size_t unit_floats = static_cast<size_t>(ROWS) * 128u;
+    float* const my_part =
+        p.part + ((static_cast<size_t>(job) * S + split) * OCB + ocb) * unit_floats;
+    for (uint32_t r = warp; r < static_cast<uint32_t>(nrows); r += 8u)
+        __stcg(reinterpret_cast<float4*>(my_part + r * 128u + lane * 4u),
+               *reinterpret_cast<const float4*>(s_acc + r * 128u + lane * 4u));
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int32_t* ctr = p.counters + static_cast<size_t>(job) * OCB + ocb;
+        const int prev = atomicAdd(ctr, 1);
+        const int last = prev == static_cast<int>(S) - 1;
+        if (last) *ctr = 0;  // every split has arrived: leave the counter clean for the next launch
+        s_last = last;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* const part0 = p.part + (static_cast<size_t>(job) * S * OCB + ocb) * unit_floats;
+    for (uint32_t r = warp; r < static_cast<uint32_t>(nrows); r += 8u) {
+        float v[4];
+        for (uint32_t s = 0; s < S; ++s) {
+            const float4 q = __ldcg(reinterpret_cast<const float4*>(
+                part0 + static_cast<size_t>(s) * OCB * unit_floats + r * 128u + lane * 4u));
+            if (s == 0) { v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+            else {
+                v[0] = __fadd_rn(v[0], q.x); v[1] = __fadd_rn(v[1], q.y);
+                v[2] = __fadd_rn(v[2], q.z); v[3] = __fadd_rn(v[3], q.w);
+            }
+        }
+        const size_t off = static_cast<size_t>(s_rows[r]) * p.OC + ocb * 128u + lane * 4u;
+        if (p.rout) finalize_row<true>(v, lane, rout_blk, p.out, off, p.rs);
+        else finalize_row<false>(v, lane, rout_blk, p.out, off, p.rs);
+    }
+}
+
+template <int K, int MT>
+cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
+    constexpr int STAGE_WORDS = 8 * 8 * K;
+    const size_t smem = (static_cast<size_t>(8 * NS * STAGE_WORDS) + static_cast<size_t>(xrows) * XS) * 4u;
+    static size_t configured[64] = {0};  // per device: largest size already enabled
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || smem > configured[dev]) {
+        e = cudaFuncSetAttribute(gemv_mma_kernel<K, MT>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = smem;
+    }
+    dim3 grid(p.OC / 128, p.splits, p.njobs), block(256);
+    gemv_mma_kernel<K, MT><<<grid, block, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t gemv_mma_part_floats(int njobs, int splits, int OC, int rows_per_job) {
+    if (splits <= 1) return 0;
+    return static_cast<size_t>(njobs) * splits * (OC / 128) * rows_per_job * 128u;
+}
+
+cudaError_t launch_gemv_mma(const GemvMmaParams& p, cudaStream_t st) {
+    const int rows = p.rows_per_job;
+    const int xrows = p.jobs ? rows : (p.M < rows ? p.M : rows);
+    if (p.K == 2) return rows == 8 ? launch_t<2, 1>(p, xrows, st) : launch_t<2, 2>(p, xrows, st);
+    return rows == 8 ? launch_t<3, 1>(p, xrows, st) : launch_t<3, 2>(p, xrows, st);
+}
+
+}  // namespace escha

@@ -1,0 +1,82 @@
+// Scaled 128-block Hadamard transforms around the coded product.
+// Replaces escha_scaled_had[_dense], escha_scaled_had_out[_dense] and the
+// two-projection *_pair dispatches of the reference
+// (escha_mlx/msl.py:875-977, wrappers :1029-1067 and :1481-1527):
+//     input :  xh = f16( H128( f32(x) * rin[e] ) * RS )
+//     output:  y  = f16( (H128(mid) * RS) * rout[e] )     (two f32 multiplies, in that order)
+// One warp owns one (row, 128-block): each lane holds four consecutive
+// channels, two butterfly stages run in registers and five through warp
+// shuffles -- no shared memory and no barriers.  Every multiply/add is an
+// explicit round-to-nearest intrinsic so no FMA contraction can move a
+// rounding point; the result is bit-identical to ref.input_transform /
+// ref.output_transform.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace escha {
+
+struct HadShard {
+    const void* src;    // f16 rows (input transform) or f32 mid (output transform)
+    const float* vec;   // rin / rout: [dim] or [E, dim]
+    __half* out;
+    int dim;            // IC or OC of this shard
+};
+
+template <bool OUTPUT>
+__global__ void __launch_bounds__(256)
+scaled_had_kernel(HadShard s0, HadShard s1, const int32_t* __restrict__ row_expert, int M,
+                  float rs) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t nb0 = s0.dim >> 7, nb1 = s1.dim >> 7;
+    const uint32_t per_row = nb0 + nb1;
+    const uint32_t row = unit / per_row;
+    if (row >= static_cast<uint32_t>(M)) return;
+    uint32_t blk = unit - row * per_row;
+    const bool second = blk >= nb0;
+    const HadShard& s = second ? s1 : s0;
+    if (second) blk -= nb0;
+
+    const size_t off = static_cast<size_t>(row) * s.dim + blk * 128u + lane * 4u;
+    const size_t voff = (row_expert ? static_cast<size_t>(row_expert[row]) * s.dim : 0) +
+                        blk * 128u + lane * 4u;
+    const float4 sc = *reinterpret_cast<const float4*>(s.vec + voff);
+    float v[4];
+    if (OUTPUT) {
+        const float4 m = *reinterpret_cast<const float4*>(static_cast<const float*>(s.src) + off);
+        v[0] = m.x; v[1] = m.y; v[2] = m.z; v[3] = m.w;
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __half*>(s.src) + off);
+        const float2 a = __half22float2(as_half2(raw.x)), b = __half22float2(as_half2(raw.y));
+        v[0] = __fmul_rn(a.x, sc.x); v[1] = __fmul_rn(a.y, sc.y);
+        v[2] = __fmul_rn(b.x, sc.z); v[3] = __fmul_rn(b.y, sc.w);
+    }
+    wht128_warp(v, lane);
+    float o[4];
+    if (OUTPUT) {
+        o[0] = __fmul_rn(__fmul_rn(v[0], rs), sc.x); o[1] = __fmul_rn(__fmul_rn(v[1], rs), sc.y);
+        o[2] = __fmul_rn(__fmul_rn(v[2], rs), sc.z); o[3] = __fmul_rn(__fmul_rn(v[3], rs), sc.w);
+    } else {
+        o[0] = __fmul_rn(v[0], rs); o[1] = __fmul_rn(v[1], rs);
+        o[2] = __fmul_rn(v[2], rs); o[3] = __fmul_rn(v[3], rs);
+    }
+    uint2 packed;
+    packed.x = as_u32(__floats2half2_rn(o[0], o[1]));
+    packed.y = as_u32(__floats2half2_rn(o[2], o[3]));
+    *reinterpret_cast<uint2*>(s.out + off) = packed;
+}
+
+cudaError_t launch_scaled_had(bool output, const void* src0, const float* vec0, __half* out0,
+                              int dim0, const void* src1, const float* vec1, __half* out1,
+                              int dim1, const int32_t* row_expert, int M, float rs,
+                              cudaStream_t st) {
+    HadShard s0{src0, vec0, out0, dim0}, s1{src1, vec1, out1, dim1};
+    const long units = static_cast<long>(M) * ((dim0 + dim1) / 128);
+    const int warps = 8;
+    dim3 grid(static_cast<unsigned>((units + warps - 1) / warps)), block(warps * 32);
+    if (output) scaled_had_kernel<true><<<grid, block, 0, st>>>(s0, s1, row_expert, M, rs);
+    else scaled_had_kernel<false><<<grid, block, 0, st>>>(s0, s1, row_expert, M, rs);
+    return cudaGetLastError();
+}
+
+}  // namespace escha

@@ -1,0 +1,56 @@
+// Internal launcher declarations shared by the .cu files and the C-ABI layer.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace escha {
+
+// One unit of row work for the tensor-core GEMV: up to 16 rows that share one
+// code stream (one expert).  Built on the device by the grouping kernel for the
+// MoE path; implicit (rows z*R .. z*R+R-1, expert 0) for a dense linear.
+struct RowJob {
+    int32_t expert;
+    int32_t nrows;
+    int32_t rows[16];
+};
+
+struct GemvMmaParams {
+    const __half* x;          // [*, IC] f16: transformed rows xh
+    const uint32_t* code;     // [E?, TK, TN, 8K]
+    const float* rout;        // nullptr -> write f32 mid; else [E?, OC] and write f16 y
+    const RowJob* jobs;       // nullptr -> dense implicit jobs
+    void* out;                // f32 [M, OC] or f16 [M, OC]
+    float* part;              // split-K partials (unused when splits == 1)
+    int32_t* counters;        // one per (job, output block); zero on entry, zero on exit
+    int M, IC, OC, K;
+    int splits;               // >= 1
+    int rows_per_job;         // 8 or 16
+    int njobs;                // grid.z
+    float rs;
+};
+
+cudaError_t launch_lut_init(__half* lut, cudaStream_t st);
+cudaError_t launch_decode_tiles(const uint32_t* code, int K, int IC, int OC, const __half* lut,
+                                __half* w, cudaStream_t st);
+cudaError_t launch_scaled_had(bool output, const void* src0, const float* vec0, __half* out0,
+                              int dim0, const void* src1, const float* vec1, __half* out1,
+                              int dim1, const int32_t* row_expert, int M, float rs,
+                              cudaStream_t st);
+cudaError_t launch_gemv_ref(const __half* xh, const uint32_t* code, const int32_t* row_expert,
+                            const int32_t* row_map, int slots, const __half* lut, float* out,
+                            float* part, int M, int IC, int OC, int K, int splits,
+                            cudaStream_t st);
+cudaError_t launch_gemv_mma(const GemvMmaParams& p, cudaStream_t st);
+cudaError_t launch_group_rows(const int32_t* row_expert, int m, int E, int R, RowJob* jobs,
+                              int njobs_cap, int32_t* njobs_out, cudaStream_t st);
+cudaError_t launch_jobs_from_groups(const int32_t* rows_idx, const int32_t* group_expert,
+                                    int n_groups, int R, int n_rows, int rows_per_job,
+                                    RowJob* jobs, cudaStream_t st);
+cudaError_t launch_swiglu(const __half* gu, int M, int I, __half* h, cudaStream_t st);
+cudaError_t launch_moe_combine(const __half* d16, const float* scores, int T, int top_k, int H,
+                               __half* y, cudaStream_t st);
+size_t gemv_mma_part_floats(int njobs, int splits, int OC, int rows_per_job);
+
+}  // namespace escha

@@ -1,0 +1,292 @@
+"""Dense coded linears: one trellis-coded weight stream per projection.
+
+Mirror of the reference's ``escha_mlx/dense.py`` (``EschaWeight`` :158-265,
+``EschaLinear`` :268-362, ``project_pair`` :365-437, ``build`` :440-452,
+``pack_code`` :145-155, ``coded_bytes`` :455-483) over CUDA ``torch.Tensor``s.
+The forward contract is the reference's, rounding points included:
+
+    xh  = f16( H128(x_f32 * rin_f32) * RS )
+    mid = xh_f32 @ W_f32                      (W = decoded fp16 tiles, f32 accumulate)
+    y   = f16( H128(mid) * RS * rout_f32 )    [+ f16(f32(y) + f32(bias)) if enabled]
+
+There is no NumPy "ops" path here: every forward runs the CUDA kernels, and a
+missing GPU or library is an error, not a fallback.
+"""
+from __future__ import annotations
+
+import logging
+
+import numpy as np
+import torch
+
+from . import envs, msl
+
+logger = logging.getLogger(__name__)
+
+RS = msl.RS
+
+#: Rates the codec implements; anything else is refused at load (reference :66-68).
+SUPPORTED_K = frozenset({2, 3})
+
+#: escha_config layout: [L, K, V, codebook_id, in_features, out_features].
+_CONFIG_LEN = 6
+_PRODUCTION_CODEBOOK = 1
+
+
+def _check_scale(name: str, vec, expect: int) -> None:
+    """A scale vector must be 1-D of exactly ``expect`` entries, or absent."""
+    if vec is None:
+        return
+    shape = tuple(np.shape(vec))
+    if shape != (expect,):
+        raise ValueError(f"{name} must have shape ({expect},), got {shape}")
+
+
+def fold_scales(rin, rout, s_in=None, s_out=None):
+    """rin_eff = f32(rin) * f32(s_in), rout_eff = f32(rout) * f32(s_out)
+    (reference: escha_mlx/ref.py:242-277).  None leaves that vector unchanged."""
+    ri = np.asarray(rin).astype(np.float32)
+    ro = np.asarray(rout).astype(np.float32)
+    if s_in is not None:
+        ri = ri * np.asarray(s_in).astype(np.float32)
+    if s_out is not None:
+        ro = ro * np.asarray(s_out).astype(np.float32)
+    return ri, ro
+
+
+def apply_bias() -> bool:
+    """Whether to apply the per-linear correction a dense export ships.  Default
+    NO, as in the reference (:107-132): the published numbers for those
+    checkpoints were produced without it; ESCHA_MLX_BIAS=1 applies it."""
+    return bool(envs.ESCHA_MLX_BIAS.get())
+
+
+def linear_mode() -> str:
+    """Always ``fused``: the CUDA kernels are the only execution path."""
+    return "fused"
+
+
+def pack_code(code_i16: np.ndarray, device=None) -> torch.Tensor:
+    """int16 [TK, TN, 16K] -> 32-bit words [TK, TN, 8K] on the device (:145-155)."""
+    return msl.code_tensor(code_i16, device)
+
+
+class EschaWeight:
+    """One dense linear's coded stream plus its folded transform vectors.
+
+    Kept off the module parameter tree (the owner holds it under a
+    leading-underscore attribute); ``arrays()`` enumerates its device tensors.
+    """
+
+    def __init__(self, code, rin, rout, s_in=None, s_out=None, config=None, device=None) -> None:
+        if isinstance(code, torch.Tensor):
+            tk, tn, wpt = code.shape          # already packed: 8K 32-bit words
+            if wpt % 8:
+                raise ValueError(f"packed escha code last dim must be 8*K, got {wpt}")
+            self.K = wpt // 8
+            code_dev = code
+            device = code.device
+        else:
+            tk, tn, wpt2 = np.shape(code)     # raw export: 16K int16 words
+            if wpt2 % 16:
+                raise ValueError(f"escha code last dim must be 16*K, got {wpt2}")
+            self.K = wpt2 // 16
+            code_dev = None
+        if self.K not in SUPPORTED_K:
+            raise ValueError(
+                f"escha code implies K={self.K}; this runtime implements "
+                f"K in {sorted(SUPPORTED_K)}")
+        self.IC, self.OC = tk * 16, tn * 16
+        if np.shape(rin) != (self.IC,) or np.shape(rout) != (self.OC,):
+            raise ValueError(
+                f"transform vectors {np.shape(rin)}/{np.shape(rout)} do not match "
+                f"the code stream's {self.IC}x{self.OC}; both must be 1-D "
+                f"({self.IC},)/({self.OC},)")
+        if self.IC % 128 or self.OC % 128:
+            raise ValueError(
+                f"escha linear dimensions must be multiples of 128, got "
+                f"{self.IC}x{self.OC}")
+        if config is not None:
+            cfg = [int(v) for v in np.asarray(config).ravel()]
+            if len(cfg) != _CONFIG_LEN:
+                raise ValueError(
+                    f"escha_config has {len(cfg)} fields, expected {_CONFIG_LEN} "
+                    f"([L, K, V, codebook_id, in_features, out_features]); this "
+                    f"export was written by an incompatible version")
+            _, k_cfg, _, cb, ic_cfg, oc_cfg = cfg
+            if (k_cfg, ic_cfg, oc_cfg) != (self.K, self.IC, self.OC):
+                raise ValueError(
+                    f"escha_config {(k_cfg, ic_cfg, oc_cfg)} disagrees with the "
+                    f"code stream {(self.K, self.IC, self.OC)}")
+            if cb != _PRODUCTION_CODEBOOK:
+                raise ValueError(
+                    f"escha_config selects codebook id {cb}; this runtime "
+                    f"implements the production codebook "
+                    f"(id {_PRODUCTION_CODEBOOK}) only")
+        _check_scale("escha_s_in", s_in, self.IC)
+        _check_scale("escha_s_out", s_out, self.OC)
+        if code_dev is None:
+            code_dev = pack_code(code, device)
+        self.code = code_dev                                   # [TK, TN, 8K] 32-bit words
+        ri, ro = fold_scales(_to_numpy(rin), _to_numpy(rout), _to_numpy(s_in), _to_numpy(s_out))
+        self.rin = torch.from_numpy(ri).to(code_dev.device)    # [IC] f32
+        self.rout = torch.from_numpy(ro).to(code_dev.device)   # [OC] f32
+
+    def weight_numpy(self) -> np.ndarray:
+        """Decoded bare weight [IC, OC] as f32 (debug/inspection; decoded on the GPU)."""
+        return msl.decode_tiles(self.code, self.K, self.IC, self.OC).float().cpu().numpy()
+
+    def arrays(self) -> list[torch.Tensor]:
+        return [self.code, self.rin, self.rout]
+
+    def shard_out(self, index: int, count: int) -> "EschaWeight":
+        """Split-N shard: output channels [index*OC/count, (index+1)*OC/count), whole
+        128-channel blocks.  Decode tiles, GEMV columns and the output transform
+        are block-local, so a shard's output equals the matching slice of the
+        full linear bit for bit."""
+        blocks = self.OC // 128
+        if blocks % count:
+            raise ValueError(f"{blocks} output blocks do not split {count} ways")
+        per = self.OC // count
+        tn0, tn1 = index * per // 16, (index + 1) * per // 16
+        w = object.__new__(EschaWeight)
+        w.K, w.IC, w.OC = self.K, self.IC, per
+        w.code = self.code[:, tn0:tn1, :].contiguous()
+        w.rin = self.rin
+        w.rout = self.rout[index * per:(index + 1) * per].contiguous()
+        return w
+
+
+def _to_numpy(v):
+    if v is None:
+        return None
+    if isinstance(v, torch.Tensor):
+        return v.detach().cpu().numpy()
+    return np.asarray(v)
+
+
+class EschaLinear(torch.nn.Module):
+    """A trellis-coded dense linear.  Drop-in for ``nn.Linear`` (bias folded in)."""
+
+    def __init__(self, w: EschaWeight, bias: np.ndarray | None = None) -> None:
+        super().__init__()
+        self._w = w
+        self.bias = None if bias is None else torch.from_numpy(
+            np.asarray(bias).astype(np.float16)).to(w.code.device)
+        self._mode = linear_mode()
+        # latched at construction so a forward is self-consistent (reference :278-281)
+        self._fused_had = msl.use_fused_had()
+        self._block_r_pin = msl.dense_block_r_pin()
+
+    @property
+    def K(self) -> int:
+        return self._w.K
+
+    def _input_rows(self, rows: torch.Tensor) -> torch.Tensor:
+        """f16( H128(rows * rin) * RS )."""
+        return msl.dense_scaled_had(rows, self._w.rin, RS)
+
+    def _output_rows(self, mid: torch.Tensor) -> torch.Tensor:
+        """f16( H128(mid) * RS * rout )."""
+        return msl.dense_scaled_had_out(mid, self._w.rout, RS)
+
+    def _gemv(self, xh: torch.Tensor) -> torch.Tensor:
+        w = self._w
+        return msl.dense_gemv(xh, w.code, w.K, w.IC, w.OC)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        if shape[-1] != self._w.IC:
+            raise ValueError(f"input has {shape[-1]} channels, the linear takes {self._w.IC}")
+        rows = x.reshape(-1, shape[-1])
+        if rows.dtype != torch.float16:
+            rows = rows.to(torch.float16)
+        rows = rows.contiguous()
+        xh = self._input_rows(rows)
+        if self._fused_had:
+            y = msl.dense_gemm_rows_direct_out(
+                xh, self._w.code, self._w.rout, self.K, self._w.IC, self._w.OC,
+                msl.dense_block_r(rows.shape[0], self._block_r_pin), RS)
+        else:
+            y = self._output_rows(self._gemv(xh))
+        if self.bias is not None:
+            # the transform output is rounded to f16 before the correction is added
+            y = (y.float() + self.bias.float()).to(torch.float16)
+        return y.reshape(*shape[:-1], self._w.OC).to(x.dtype)
+
+
+def project_pair(first: EschaLinear, second: EschaLinear, x: torch.Tensor):
+    """Evaluate two coded projections of the same input (gate/up, K/V) with the
+    paired launches (:365-437).  Outputs equal ``first(x), second(x)`` bit for bit."""
+    shape = x.shape
+    rows = x.reshape(-1, shape[-1])
+    compatible = (
+        first._w.IC == second._w.IC == rows.shape[-1]
+        and first._fused_had and second._fused_had
+        and rows.dtype == torch.float16
+    )
+    if not compatible:
+        return first(x), second(x)
+    rows = rows.contiguous()
+    r = msl.dense_block_r(rows.shape[0], first._block_r_pin)
+    xh0, xh1 = msl.dense_scaled_had_pair(rows, first._w.rin, second._w.rin, RS)
+    out0, out1 = msl.dense_gemm_pair_out(
+        xh0, xh1, first._w.code, second._w.code, first._w.rout, second._w.rout,
+        first.K, second.K, first._w.IC, first._w.OC, second._w.OC, r, RS)
+
+    def finish(linear, value):
+        if linear.bias is not None:
+            value = (value.float() + linear.bias.float()).to(torch.float16)
+        return value.reshape(*shape[:-1], linear._w.OC).to(x.dtype)
+
+    return finish(first, out0), finish(second, out1)
+
+
+def build(group: dict, device=None) -> EschaLinear:
+    """Assemble one linear from its streamed tensors, keyed by HF leaf name (:440-452).
+
+    Required: ``escha_code``, ``escha_rin``, ``escha_rout``.  Optional:
+    ``escha_s_in``/``escha_s_out`` (implicitly ones when absent), ``escha_config``
+    (cross-checked), ``bias`` (applied only with ESCHA_MLX_BIAS=1).
+    """
+    missing = REQUIRED - set(group)
+    if missing:
+        raise ValueError(f"coded linear is missing leaves {sorted(missing)}")
+    w = EschaWeight(group["escha_code"], group["escha_rin"], group["escha_rout"],
+                    group.get("escha_s_in"), group.get("escha_s_out"),
+                    group.get("escha_config"), device=device)
+    bias = group.get("bias") if apply_bias() else None
+    return EschaLinear(w, bias)
+
+
+def coded_bytes(obj) -> int:
+    """Bytes of every coded stream under ``obj`` -- the ones NOT on the parameter
+    tree (:455-483).  Accepts a Module or any list/tuple/dict of them."""
+    total = 0
+    stack = [obj]
+    seen: set[int] = set()
+    while stack:
+        node = stack.pop()
+        if id(node) in seen:
+            continue
+        seen.add(id(node))
+        if isinstance(node, EschaLinear):
+            total += sum(a.numel() * a.element_size() for a in node._w.arrays())
+            continue
+        if isinstance(node, torch.nn.Module):
+            stack.extend(node.children())
+            stack.extend(v for k, v in vars(node).items() if k.startswith("_") and
+                         isinstance(v, (list, tuple, dict, torch.nn.Module)))
+        elif isinstance(node, dict):
+            stack.extend(node.values())
+        elif isinstance(node, (list, tuple)):
+            stack.extend(node)
+    return total
+
+
+#: Leaf names that together define one coded linear.
+LEAVES = frozenset({"escha_code", "escha_rin", "escha_rout",
+                    "escha_s_in", "escha_s_out", "escha_config", "bias"})
+
+#: The subset that must be present before a linear can be built.
+REQUIRED = frozenset({"escha_code", "escha_rin", "escha_rout"})

@@ -1,0 +1,444 @@
+"""Kernel layer of the coded-projection path on B200.
+
+Mirrors the function surface of the reference's ``escha_mlx/msl.py`` (the
+module whose functions each launch one Metal kernel) with the same names,
+argument order and error behaviour, taking contiguous CUDA ``torch.Tensor``s in
+place of ``mx.array``s and calling hand-written sm_100a kernels through the C
+ABI in ``include/escha_b200.h``.  Wrappers are pure: inputs are borrowed, a
+freshly allocated output is returned, nothing synchronises.
+
+Two GEMV kernel families exist (``ESCHA_MLX_GEMV``):
+
+* ``mma`` (default) -- the tensor-core kernel: decoded tile fragments feed
+  ``mma.sync`` directly, 8 or 16 rows share one decode, split-K over 128-channel
+  input blocks with a fixed-order reduction, optional fused output transform.
+  Deterministic: bit-reproducible run to run, and a row's result does not
+  depend on which other rows are in the batch.
+* ``reforder`` -- a scalar kernel in the reference kernels' exact accumulation
+  order (bit-identical to them and to the CPU oracle).
+
+Reference citations are to ``escha_mlx/msl.py`` unless stated otherwise.
+"""
+from __future__ import annotations
+
+import ctypes
+from functools import lru_cache
+
+import numpy as np
+import torch
+
+from . import envs
+from ._lib import check, lib, ptr, stream, workspaces
+
+RS = 0.088388347648  # escha_mlx/ref.py:30
+
+#: Rows that share one decode in the tensor-core kernel (one or two mma column blocks).
+MMA_ROWS = (8, 16)
+
+#: Largest rows-per-group the reference's dense row-blocked GEMM chooses (:1548);
+#: kept for API compatibility -- here 16 rows always share a decode.
+DENSE_R_MAX = 16
+DENSE_MAT_R = 16
+
+
+# ---------------------------------------------------------------------------
+# knobs (reference: :1024-1026, :1070, :1140-1242, :1551-1601, :1729-1759)
+# ---------------------------------------------------------------------------
+
+def use_fused_had() -> bool:
+    return bool(envs.ESCHA_MLX_FUSED_HAD.get())
+
+
+def use_lut() -> bool:
+    return bool(envs.ESCHA_MLX_LUT.get())
+
+
+def gemv_family() -> str:
+    return envs.ESCHA_MLX_GEMV.get()
+
+
+def use_dense_mat() -> bool:
+    """The reference gates its reassociated matrix-unit GEMM behind a flag
+    (:1729-1759); here the tensor-core kernel IS the default family."""
+    return gemv_family() == "mma"
+
+
+def kt_block() -> int:
+    """kt tiles per pipeline stage of the tensor-core kernel (fixed at 8 = one
+    128-channel block; the reference stages a configurable count, :1229-1242)."""
+    return 8
+
+
+def dense_block_r_pin() -> int | None:
+    return envs.ESCHA_MLX_DENSE_BLOCK_R.get()
+
+
+def dense_block_r(m: int, pin: int | None = None) -> int:
+    """Rows per decode the reference's policy would pick (:1562-1601): min(m, 16)
+    snapped down to a power of two.  Informational here -- the tensor-core kernel
+    shares every decode across up to 16 rows regardless."""
+    if pin is not None:
+        return pin
+    r = min(m, DENSE_R_MAX)
+    while r & (r - 1):
+        r &= r - 1
+    return max(1, r)
+
+
+def split_k_for(m: int, oc: int, tk: int, njobs: int = 1) -> int:
+    """Split factor for an [m, tk*16] x [tk*16, oc] coded product (:1191-1226).
+
+    ``ESCHA_MLX_SPLITK``: an integer pins it, ``auto`` (default) fills the GPU:
+    enough splits for two resident CTAs per SM, at least two 128-channel blocks
+    per split.  Depends on the shape only -- never on the data and, for a dense
+    stream, not on m -- so results are reproducible and batch-invariant.
+    """
+    setting = envs.ESCHA_MLX_SPLITK.get()
+    nblk = tk // 8
+    if setting != "auto":
+        s = int(setting)
+        return s if 1 < s <= nblk else 1
+    return int(lib.escha_coded_gemv_splits(tk * 16, oc, njobs, 0))
+
+
+# ---------------------------------------------------------------------------
+# helpers
+# ---------------------------------------------------------------------------
+
+def code_to_u32(code_i16: np.ndarray) -> np.ndarray:
+    """View an int16 code tensor [..., 16K] as little-endian uint32 [..., 8K] (:1398-1401)."""
+    a = np.ascontiguousarray(code_i16).view(np.uint16)
+    return a.view(np.uint32)
+
+
+def code_tensor(code_i16: np.ndarray, device=None) -> torch.Tensor:
+    """Host int16 export -> device code stream (stored as int32 words; torch has
+    no arithmetic on uint32 and the kernels only read the bits)."""
+    words = code_to_u32(code_i16).view(np.int32)
+    return torch.from_numpy(words).to(device or "cuda")
+
+
+_LUTS: dict[int, torch.Tensor] = {}
+
+
+def _lut_tensor(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _LUTS.get(idx)
+    if t is None:
+        t = torch.empty(65536, dtype=torch.float16, device=device)
+        check(lib.escha_lut_init(ptr(t), stream()))
+        _LUTS[idx] = t
+    return t
+
+
+def _maybe_lut(device) -> torch.Tensor | None:
+    return _lut_tensor(device) if use_lut() else None
+
+
+def _check_code(code: torch.Tensor) -> None:
+    if code.dtype not in (torch.int32, torch.uint32):
+        raise ValueError(f"code stream must be 32-bit words, got {code.dtype}")
+
+
+def _i32(t: torch.Tensor | None) -> torch.Tensor | None:
+    if t is None:
+        return None
+    if t.dtype != torch.int32:
+        raise ValueError(f"index tensors must be int32, got {t.dtype}")
+    return t
+
+
+# ---------------------------------------------------------------------------
+# decode
+# ---------------------------------------------------------------------------
+
+def decode_tiles(code_u32: torch.Tensor, K: int, IC: int, OC: int) -> torch.Tensor:
+    """Decode one projection's packed stream -> fp16 bare weight [IC, OC] (:1404-1421)."""
+    _check_code(code_u32)
+    w = torch.empty((IC, OC), dtype=torch.float16, device=code_u32.device)
+    check(lib.escha_decode_tiles(ptr(code_u32), K, IC, OC, ptr(_maybe_lut(code_u32.device)),
+                                 ptr(w), stream()))
+    return w
+
+
+# ---------------------------------------------------------------------------
+# scaled Hadamard transforms
+# ---------------------------------------------------------------------------
+
+def scaled_had(rows: torch.Tensor, rin: torch.Tensor, row_expert: torch.Tensor | None,
+               rs: float) -> torch.Tensor:
+    """rows [m, IC] f16, rin [E, IC] f32 (or [IC] with row_expert=None) -> [m, IC] f16 (:1029-1047)."""
+    m, ic = rows.shape
+    out = torch.empty((m, ic), dtype=torch.float16, device=rows.device)
+    check(lib.escha_scaled_had(ptr(rows, torch.float16), ptr(rin, torch.float32),
+                               ptr(_i32(row_expert)), m, ic, float(rs), ptr(out), stream()))
+    return out
+
+
+def scaled_had_out(mid: torch.Tensor, rout: torch.Tensor, row_expert: torch.Tensor | None,
+                   rs: float) -> torch.Tensor:
+    """mid [m, OC] f32, rout [E, OC] f32 -> transformed [m, OC] f16 (:1050-1067)."""
+    m, oc = mid.shape
+    out = torch.empty((m, oc), dtype=torch.float16, device=mid.device)
+    check(lib.escha_scaled_had_out(ptr(mid, torch.float32), ptr(rout, torch.float32),
+                                   ptr(_i32(row_expert)), m, oc, float(rs), ptr(out), stream()))
+    return out
+
+
+def dense_scaled_had(rows: torch.Tensor, rin: torch.Tensor, rs: float) -> torch.Tensor:
+    return scaled_had(rows, rin, None, rs)
+
+
+def dense_scaled_had_out(mid: torch.Tensor, rout: torch.Tensor, rs: float) -> torch.Tensor:
+    return scaled_had_out(mid, rout, None, rs)
+
+
+def dense_scaled_had_pair(rows: torch.Tensor, rin0: torch.Tensor, rin1: torch.Tensor, rs: float):
+    """Two dense input transforms in one launch (:1491-1504)."""
+    m, ic = rows.shape
+    out0 = torch.empty((m, ic), dtype=torch.float16, device=rows.device)
+    out1 = torch.empty_like(out0)
+    check(lib.escha_scaled_had_pair(ptr(rows, torch.float16), ptr(rin0, torch.float32),
+                                    ptr(rin1, torch.float32), m, ic, float(rs), ptr(out0),
+                                    ptr(out1), stream()))
+    return out0, out1
+
+
+def dense_scaled_had_out_pair(mid0: torch.Tensor, mid1: torch.Tensor, rout0: torch.Tensor,
+                              rout1: torch.Tensor, rs: float):
+    """Two dense output transforms in one launch (:1507-1527)."""
+    m, oc0 = mid0.shape
+    if mid1.shape[0] != m:
+        raise ValueError("output transform pair requires equal row counts")
+    oc1 = mid1.shape[1]
+    out0 = torch.empty((m, oc0), dtype=torch.float16, device=mid0.device)
+    out1 = torch.empty((m, oc1), dtype=torch.float16, device=mid0.device)
+    check(lib.escha_scaled_had_out_pair(ptr(mid0, torch.float32), ptr(mid1, torch.float32),
+                                        ptr(rout0, torch.float32), ptr(rout1, torch.float32), m,
+                                        oc0, oc1, float(rs), ptr(out0), ptr(out1), stream()))
+    return out0, out1
+
+
+# ---------------------------------------------------------------------------
+# row jobs (device-side grouping for E-stacked streams)
+# ---------------------------------------------------------------------------
+
+JOB_INTS = 18
+
+
+def jobs_bound(m: int, E: int, R: int = 8) -> int:
+    return int(lib.escha_moe_jobs_bound(m, E, R))
+
+
+def group_rows(row_expert: torch.Tensor, E: int, R: int = 8) -> torch.Tensor:
+    """row_expert [m] i32 -> row jobs [jobs_bound(m, E, R), 18] i32, device-resident
+    (replaces moe.build_groups for the tensor-core kernel; no host sync)."""
+    m = row_expert.shape[0]
+    cap = jobs_bound(m, E, R)
+    jobs = torch.empty((cap, JOB_INTS), dtype=torch.int32, device=row_expert.device)
+    check(lib.escha_moe_group_rows(ptr(_i32(row_expert)), m, E, R, ptr(jobs), cap, None, stream()))
+    return jobs
+
+
+def expected_jobs(m: int, E: int) -> int:
+    """Expected number of distinct experts hit by m uniformly routed rows; the
+    data-independent job count the split policy is evaluated at."""
+    return max(1, int(round(E * (1.0 - (1.0 - 1.0 / E) ** m))))
+
+
+# ---------------------------------------------------------------------------
+# coded GEMV / small-batch GEMM
+# ---------------------------------------------------------------------------
+
+def _gemv_reforder(xh, code, row_expert, K, IC, OC, splits, row_map=None, n_out=None):
+    m = xh.shape[0] if n_out is None else n_out
+    s = splits if splits and splits > 1 and (IC // 16) % splits == 0 else 1
+    mid = torch.zeros((m, OC), dtype=torch.float32, device=xh.device) if row_map is not None \
+        else torch.empty((m, OC), dtype=torch.float32, device=xh.device)
+    part = torch.empty((s, m, OC), dtype=torch.float32, device=xh.device) if s > 1 else None
+    slots = 0 if row_map is None else row_map.shape[0]
+    check(lib.escha_gemv_ref(ptr(xh, torch.float16), ptr(code), ptr(_i32(row_expert)),
+                             ptr(_i32(row_map)), slots, ptr(_maybe_lut(xh.device)), m, IC, OC, K,
+                             s, ptr(part), ptr(mid), stream()))
+    return mid
+
+
+def _gemv_mma_dense(xh, code, rout, K, IC, OC, splits, rs=RS):
+    m = xh.shape[0]
+    s = split_k_for(m, OC, IC // 16) if splits is None else max(1, min(int(splits), IC // 128))
+    rows_per_job = 8 if m <= 8 else 16
+    njobs = (m + rows_per_job - 1) // rows_per_job
+    out = torch.empty((m, OC), dtype=torch.float32 if rout is None else torch.float16,
+                      device=xh.device)
+    ws, nbytes = None, 0
+    if s > 1:
+        nbytes = int(lib.escha_coded_gemv_workspace_bytes(njobs, OC, s, rows_per_job))
+        ws = workspaces.get(nbytes, xh.device)
+        nbytes = ws.numel()
+    check(lib.escha_coded_gemv(ptr(xh, torch.float16), ptr(code),
+                               ptr(rout, torch.float32) if rout is not None else None, m, IC, OC,
+                               K, s, float(rs), ptr(ws), ctypes.c_size_t(nbytes), ptr(out),
+                               stream()))
+    return out
+
+
+def coded_gemv_jobs(xh: torch.Tensor, code_u32: torch.Tensor, jobs: torch.Tensor,
+                    rout: torch.Tensor | None, K: int, IC: int, OC: int, E: int,
+                    splits: int | None = None, rs: float = RS, rows_per_job: int = 8,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tensor-core expert GEMV over row jobs (see ``group_rows``).  Returns f32
+    mid [m, OC], or f16 y [m, OC] with the output transform fused when ``rout``
+    ([E, OC] f32) is given."""
+    m = xh.shape[0]
+    njobs = jobs.shape[0]
+    s = split_k_for(m, OC, IC // 16, expected_jobs(m, E)) if splits is None \
+        else max(1, min(int(splits), IC // 128))
+    if out is None:
+        out = torch.empty((m, OC), dtype=torch.float32 if rout is None else torch.float16,
+                          device=xh.device)
+    ws, nbytes = None, 0
+    if s > 1:
+        nbytes = int(lib.escha_coded_gemv_workspace_bytes(njobs, OC, s, rows_per_job))
+        ws = workspaces.get(nbytes, xh.device)
+        nbytes = ws.numel()
+    check(lib.escha_coded_gemv_jobs(ptr(xh, torch.float16), ptr(code_u32),
+                                    ptr(rout, torch.float32) if rout is not None else None,
+                                    ptr(jobs, torch.int32), njobs, rows_per_job, m, E, IC, OC, K, s,
+                                    float(rs), ptr(ws), ctypes.c_size_t(nbytes), ptr(out), stream()))
+    return out
+
+
+def moe_gemv(xh: torch.Tensor, code_u32: torch.Tensor, row_expert: torch.Tensor | None,
+             K: int, IC: int, OC: int, splits: int | None = None,
+             jobs: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused expert GEMV: mid[r, :] = xh[r, :] @ decode(code[row_expert[r]]) (:1424-1478).
+
+    xh [M, IC] f16; code_u32 [E, TK, TN, 8K] (E-stacked) or [TK, TN, 8K] with
+    ``row_expert=None`` for a dense linear; returns mid [M, OC] f32.
+    ``splits``: None = the size policy, 1 = no split.  ``jobs`` lets a caller
+    that runs several projections over the same rows group them once.
+    """
+    _check_code(code_u32)
+    if xh.shape[0] < 1:
+        raise ValueError("moe_gemv needs at least one row")
+    if gemv_family() == "reforder":
+        return _gemv_reforder(xh, code_u32, row_expert, K, IC, OC, splits)
+    if row_expert is None:
+        return _gemv_mma_dense(xh, code_u32, None, K, IC, OC, splits)
+    E = code_u32.shape[0]
+    if jobs is None:
+        jobs = group_rows(row_expert, E)
+    return coded_gemv_jobs(xh, code_u32, jobs, None, K, IC, OC, E, splits)
+
+
+def dense_gemv(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int, OC: int,
+               splits: int | None = None) -> torch.Tensor:
+    """Fused dense GEMV: mid = xh @ decode(code), code_u32 [TK, TN, 8K] (:1530-1538)."""
+    return moe_gemv(xh, code_u32, None, K, IC, OC, splits)
+
+
+def dense_gemm_rows(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int, OC: int,
+                    R: int) -> torch.Tensor:
+    """Row-blocked dense GEMM: mid = xh @ decode(code) (:1785-1812).  Bit-identical
+    to ``dense_gemv`` on the same rows, as in the reference (same kernel, same
+    per-row summation order; R only reports the reference's blocking)."""
+    if xh.shape[0] < 1:
+        raise ValueError("dense_gemm_rows needs at least one row")
+    return dense_gemv(xh, code_u32, K, IC, OC)
+
+
+def dense_gemm_rows_direct(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int, OC: int,
+                           R: int) -> torch.Tensor:
+    """Small-row dense GEMM (:1815-1841); same kernel as ``dense_gemm_rows``."""
+    if xh.shape[0] < 1:
+        raise ValueError("dense_gemm_rows_direct needs at least one row")
+    return dense_gemv(xh, code_u32, K, IC, OC)
+
+
+def dense_gemm_mat(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int,
+                   OC: int) -> torch.Tensor:
+    """Matrix-unit dense GEMM (:1762-1782): always the tensor-core kernel here."""
+    _check_code(code_u32)
+    return _gemv_mma_dense(xh, code_u32, None, K, IC, OC, None)
+
+
+def dense_gemm_rows_direct_out(xh: torch.Tensor, code: torch.Tensor, rout: torch.Tensor, K: int,
+                               IC: int, OC: int, R: int, rs: float) -> torch.Tensor:
+    """Small-row GEMM with its output transform fused (:1844-1870) -> f16 [M, OC]."""
+    _check_code(code)
+    if xh.shape[0] < 1:
+        raise ValueError("dense_gemm_rows_direct_out needs at least one row")
+    if gemv_family() == "reforder":
+        return scaled_had_out(_gemv_reforder(xh, code, None, K, IC, OC, None), rout, None, rs)
+    return _gemv_mma_dense(xh, code, rout, K, IC, OC, None, rs)
+
+
+def dense_gemm_pair(xh0, xh1, code0, code1, K0: int, K1: int, IC: int, OC0: int, OC1: int,
+                    R: int):
+    """Two coded projections with the same input geometry (:1909-1950)."""
+    if xh0.shape != xh1.shape or xh0.shape[0] < 1:
+        raise ValueError("dense_gemm_pair requires matching non-empty input rows")
+    return (dense_gemv(xh0, code0, K0, IC, OC0), dense_gemv(xh1, code1, K1, IC, OC1))
+
+
+def dense_gemm_pair_out(xh0, xh1, code0, code1, rout0, rout1, K0: int, K1: int, IC: int,
+                        OC0: int, OC1: int, R: int, rs: float):
+    """Mixed-K projection pair with both output transforms fused (:1873-1906)."""
+    if xh0.shape != xh1.shape or xh0.shape[0] < 1:
+        raise ValueError("dense_gemm_pair_out requires matching non-empty input rows")
+    return (dense_gemm_rows_direct_out(xh0, code0, rout0, K0, IC, OC0, R, rs),
+            dense_gemm_rows_direct_out(xh1, code1, rout1, K1, IC, OC1, R, rs))
+
+
+def moe_gemm_rows(xh: torch.Tensor, code_u32: torch.Tensor, rows_idx: torch.Tensor,
+                  group_expert: torch.Tensor, K: int, IC: int, OC: int, R: int, n_rows: int,
+                  sort_idx=None) -> torch.Tensor:
+    """Row-blocked expert GEMM over ``moe.build_groups`` output (:1366-1395).
+
+    xh [n_rows + 1, IC] f16 (row n_rows is the zero padding sink), rows_idx
+    [n_groups * R] i32 with padding == n_rows, group_expert [n_groups] i32 with -1
+    past the end.  Returns mid [n_rows + 1, OC] f32 whose padding row is zero.
+    ``sort_idx`` (the reference's sorted-x addressing) is accepted and ignored:
+    the kernel gathers rows by index either way.
+    """
+    _check_code(code_u32)
+    n_groups = group_expert.shape[0]
+    if gemv_family() == "reforder":
+        row_expert = torch.zeros(n_rows + 1, dtype=torch.int32, device=xh.device)
+        ge = group_expert.clamp(min=0).repeat_interleave(R)
+        row_expert.scatter_(0, rows_idx.long(), ge)
+        # padding slots point at the zero sink row n_rows and yield a zero row
+        return _gemv_reforder(xh, code_u32, row_expert, K, IC, OC, 1, row_map=rows_idx,
+                              n_out=n_rows + 1)
+    rows_per_job = 8 if R <= 8 else 16
+    per_group = (R + rows_per_job - 1) // rows_per_job
+    jobs = torch.empty((n_groups * per_group, JOB_INTS), dtype=torch.int32, device=xh.device)
+    check(lib.escha_jobs_from_groups(ptr(_i32(rows_idx)), ptr(_i32(group_expert)), n_groups, R,
+                                     n_rows, rows_per_job, ptr(jobs), stream()))
+    E = code_u32.shape[0]
+    out = torch.zeros((n_rows + 1, OC), dtype=torch.float32, device=xh.device)
+    coded_gemv_jobs(xh, code_u32, jobs, None, K, IC, OC, E, None, rows_per_job=rows_per_job,
+                    out=out)
+    return out
+
+
+# ---------------------------------------------------------------------------
+# elementwise stages of the routed-expert path
+# ---------------------------------------------------------------------------
+
+def swiglu(gu16: torch.Tensor) -> torch.Tensor:
+    """gu16 [m, 2I] f16 (gate first) -> f16(f16(silu(g)) * u) [m, I]
+    (models/qwen3_5_moe.py:221-223 of the reference)."""
+    m, two_i = gu16.shape
+    h = torch.empty((m, two_i // 2), dtype=torch.float16, device=gu16.device)
+    check(lib.escha_swiglu(ptr(gu16, torch.float16), m, two_i // 2, ptr(h), stream()))
+    return h
+
+
+def moe_combine(d16: torch.Tensor, scores: torch.Tensor, T: int, top_k: int) -> torch.Tensor:
+    """Fixed slot-order combine -> f16 [T, H] (models/qwen3_5_moe.py:227-253)."""
+    H = d16.shape[1]
+    y = torch.empty((T, H), dtype=torch.float16, device=d16.device)
+    check(lib.escha_moe_combine(ptr(d16, torch.float16), ptr(scores, torch.float32), T, top_k, H,
+                                ptr(y), stream()))
+    return y

@@ -1,0 +1,173 @@
+/*
+ * escha_b200.h -- C ABI of libescha_b200.so: the escha coded-projection hot
+ * path (trellis-coded 2/3-bit weight decode fused into GEMV / small-batch GEMM /
+ * expert GEMV, plus the scaled 128-block Hadamard transforms) for NVIDIA B200
+ * (sm_100a).
+ *
+ * The reference project (EschaLabs/escha-mlx) has no compiled plugin ABI: its
+ * boundary for this path is the Python function surface of escha_mlx/msl.py,
+ * whose functions each launch one Metal kernel.  Every entry point below
+ * replaces one of those launches; the comment gives the reference file:line.
+ *
+ * Conventions
+ *  - All pointers are DEVICE pointers owned by the caller, 16-byte aligned,
+ *    dense row-major.  The library allocates nothing and keeps no device state.
+ *  - Half-precision buffers are IEEE binary16 (declared void*).
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream).  Calls
+ *    only enqueue work; they never synchronise.
+ *  - Return value: ESCHA_OK, or a negative code; escha_last_error() returns a
+ *    thread-local description of the most recent failure on this thread.
+ *    Arguments are validated on the host before any launch; the kernels
+ *    themselves do no bounds checks (as in the reference, dense.py:202-209).
+ *  - Code streams are uint32 [TK, TN, 8K] (dense) or [E, TK, TN, 8K]
+ *    (E-stacked), TK = IC/16, TN = OC/16, K in {2, 3}: the reference's int16
+ *    [.., 16K] export viewed as little-endian uint32 (msl.py:1398-1401).
+ */
+#ifndef ESCHA_B200_H
+#define ESCHA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ESCHA_OK 0
+#define ESCHA_EINVAL (-1) /* contract violation; nothing was launched */
+#define ESCHA_ECUDA (-2)  /* a CUDA runtime call failed */
+
+#define ESCHA_ABI_VERSION 1
+
+int escha_version(void);
+const char *escha_last_error(void);
+
+/* Fill a 65,536-entry binary16 table lut[state] = decode(state) on the device.
+ * Replaces ref.cba_lut()/msl._lut_array (ref.py:37-48, msl.py:1074-1076): the
+ * table the *_lut kernel variants read instead of hashing. */
+int escha_lut_init(void *lut, void *stream);
+
+/* code [TK,TN,8K] -> w [IC,OC] binary16, bit-exact to ref.reconstruct.
+ * lut == NULL selects the integer-hash decode, otherwise the table decode.
+ * Replaces msl.decode_tiles (msl.py:1404-1421; kernel source :183-202).
+ * IC and OC must be multiples of 16. */
+int escha_decode_tiles(const void *code, int K, int IC, int OC, const void *lut, void *w,
+                       void *stream);
+
+/* out = f16( H128( f32(rows) * rin[e] ) * rs ),  rows [M,IC] binary16.
+ * row_expert == NULL: rin is [IC]; else rin is [E,IC] and row r uses
+ * rin[row_expert[r]].  Replaces msl.scaled_had / dense_scaled_had
+ * (msl.py:1029-1047, :1481-1483; kernel source :875-916). */
+int escha_scaled_had(const void *rows, const float *rin, const int32_t *row_expert, int M, int IC,
+                     float rs, void *out, void *stream);
+
+/* out = f16( (H128(mid) * rs) * rout[e] ),  mid [M,OC] f32.
+ * Replaces msl.scaled_had_out / dense_scaled_had_out
+ * (msl.py:1050-1067, :1486-1488; kernel source :919-949). */
+int escha_scaled_had_out(const float *mid, const float *rout, const int32_t *row_expert, int M,
+                         int OC, float rs, void *out, void *stream);
+
+/* Two dense input transforms of the same rows in one launch.
+ * Replaces msl.dense_scaled_had_pair (msl.py:1491-1504). */
+int escha_scaled_had_pair(const void *rows, const float *rin0, const float *rin1, int M, int IC,
+                          float rs, void *out0, void *out1, void *stream);
+
+/* Two dense output transforms in one launch (equal row counts).
+ * Replaces msl.dense_scaled_had_out_pair (msl.py:1507-1527). */
+int escha_scaled_had_out_pair(const float *mid0, const float *mid1, const float *rout0,
+                              const float *rout1, int M, int OC0, int OC1, float rs, void *out0,
+                              void *out1, void *stream);
+
+/* Per-row coded GEMV in the reference kernels' exact accumulation order
+ * (bit-identical to them for a given input):
+ *     mid[r,:] = f32(xh[r,:]) @ f32(decode(code[row_expert[r]]))      f32 [M,OC]
+ * Replaces msl.moe_gemv / dense_gemv incl. the split-K variant
+ * (msl.py:1424-1478, :1530-1538; kernel sources :205-435) and, through
+ * row_map, the row-blocked forms msl.moe_gemm_rows / dense_gemm_rows[_direct]
+ * (msl.py:1366-1395, :1785-1841), whose per-(row, channel) order is the same.
+ *  row_expert NULL -> dense stream.   lut NULL -> hash decode.
+ *  row_map NULL -> slots == M and slot s is row s; else row_map[slots] gives the
+ *    row of each slot and entries >= M are padding (skipped).  splits must be 1
+ *    with a row_map.
+ *  splits > 1 must divide IC/16; part must then hold splits*M*OC floats and the
+ *    partials are summed in ascending split order. */
+int escha_gemv_ref(const void *xh, const void *code, const int32_t *row_expert,
+                   const int32_t *row_map, int slots, const void *lut, int M, int IC, int OC,
+                   int K, int splits, float *part, float *mid, void *stream);
+
+/* Workspace the tensor-core GEMV needs for a given launch shape, in bytes
+ * (counters + split-K partials).  The caller allocates it once, zero-filled;
+ * every launch leaves the counter region zero again.  njobs = number of row
+ * groups (escha_coded_gemv: (M + rows_per_job - 1) / rows_per_job). */
+size_t escha_coded_gemv_workspace_bytes(int njobs, int OC, int splits, int rows_per_job);
+
+/* Split policy: how many ways the kernel splits the input dimension so that the
+ * grid fills the GPU (sm_count <= 0 queries the current device).  Depends only
+ * on the shape and njobs, never on data, so results are reproducible. */
+int escha_coded_gemv_splits(int IC, int OC, int njobs, int sm_count);
+
+/* Tensor-core coded GEMV / small-batch GEMM for a dense stream (M >= 1 rows,
+ * any M: rows are processed 8 or 16 per decode).
+ *   rout == NULL: out is f32 mid [M,OC]                (msl.dense_gemv,
+ *                                                        dense_gemm_rows[_direct])
+ *   rout != NULL: out is binary16 y = f16((H128(mid)*rs)*rout)
+ *                                                       (msl.dense_gemm_rows_direct_out,
+ *                                                        msl.py:1844-1870)
+ * Same product as escha_gemv_ref with a different (fixed) summation order:
+ * tolerance-equal to it, bit-reproducible run to run for fixed (shape, splits).
+ * splits <= 0 selects escha_coded_gemv_splits(). */
+int escha_coded_gemv(const void *xh, const void *code, const float *rout, int M, int IC, int OC,
+                     int K, int splits, float rs, void *workspace, size_t workspace_bytes,
+                     void *out, void *stream);
+
+/* ---- routed experts (E-stacked streams) ---------------------------------- */
+
+/* A row job: up to 16 rows that read the same expert's stream.  Plain int32
+ * record, ESCHA_ROW_JOB_INTS words: {expert, nrows, rows[16]}. */
+#define ESCHA_ROW_JOB_INTS 18
+
+/* Upper bound on the number of jobs escha_moe_group_rows can emit for m rows
+ * over E experts with R rows per job: (m + min(m,E)*(R-1)) / R. */
+int escha_moe_jobs_bound(int m, int E, int R);
+
+/* Group m (token, slot) rows by expert into row jobs of at most R rows
+ * (R = 8 or 16), rows ascending inside an expert; jobs past the last real one
+ * get nrows = 0.  jobs must hold njobs_cap records; njobs_out (optional) gets
+ * the real count.  Device-resident replacement for moe.build_groups
+ * (escha_mlx/moe.py:30-78) -- same stable order, no padding rows. */
+int escha_moe_group_rows(const int32_t *row_expert, int m, int E, int R, void *jobs,
+                         int njobs_cap, int32_t *njobs_out, void *stream);
+
+/* Convert the (rows_idx [n_groups*R], group_expert [n_groups]) form that
+ * moe.build_groups returns (padding slots == n_rows, expert -1 past the end)
+ * into row jobs; emits n_groups * ceil(R / rows_per_job) records. */
+int escha_jobs_from_groups(const int32_t *rows_idx, const int32_t *group_expert, int n_groups,
+                           int R, int n_rows, int rows_per_job, void *jobs, void *stream);
+
+/* Tensor-core expert GEMV over row jobs: for every job, rows read
+ * code[job.expert]; rout (if given) is [E,OC] and indexed by job.expert.
+ * xh is [M,IC], out is [M,OC] (f32 mid, or binary16 y when rout != NULL); rows
+ * no job names are left untouched.  Replaces msl.moe_gemv with a row_expert
+ * and msl.moe_gemm_rows (msl.py:1366-1395, :1424-1478).  splits must be >= 1
+ * (use escha_coded_gemv_splits with the expected job count); workspace as
+ * escha_coded_gemv_workspace_bytes(njobs, OC, splits, rows_per_job). */
+int escha_coded_gemv_jobs(const void *xh, const void *code, const float *rout, const void *jobs,
+                          int njobs, int rows_per_job, int M, int E, int IC, int OC, int K,
+                          int splits, float rs, void *workspace, size_t workspace_bytes, void *out,
+                          void *stream);
+
+/* h = f16( f16(silu(g)) * u ) on gu [M,2I] binary16 (gate = first I channels).
+ * Replaces the elementwise stage at models/qwen3_5_moe.py:221-223
+ * (ref.swiglu, ref.py:296-301). */
+int escha_swiglu(const void *gu, int M, int I, void *h, void *stream);
+
+/* y[t,:] = f16( sum over slots s, ascending, of f32(d16[t*top_k+s,:]) *
+ * f32(f16(scores[t*top_k+s])) ) -- the fixed-order combine at
+ * models/qwen3_5_moe.py:227-253 (never a scatter-add). */
+int escha_moe_combine(const void *d16, const float *scores, int T, int top_k, int H, void *y,
+                      void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ESCHA_B200_H */
