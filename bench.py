@@ -1,0 +1,422 @@
+#!/usr/bin/env python
+"""Benchmark of the coded-projection hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch M] [--impl b200|reference]
+
+Workload (BASELINE.json configs[1]): one layer of a 27B-class dense model at
+decode batch M (default 1) -- seven trellis-coded projections, hidden 5120:
+q/k/v/o 2-bit 5120x{6144,1024,1024,5120}, gate/up 3-bit 5120x17408, down 3-bit
+17408x5120 = 117,309,440 bytes of code per layer.  A step is one pass of the
+layer (input transform, coded GEMV, output transform per projection, SwiGLU
+before down) over one batch of synthetic fp16 activations.  Several layers'
+worth of distinct weights are resident and rotated step to step so every step's
+code stream misses L2 (the reference's bench/p0_gates.py:111-116 draws fresh
+experts per call for the same reason).
+
+Metric: compressed-weight GB/s = code bytes per step / time per step, whole job.
+  value  -- inputs resident in HBM, steps replayed as CUDA graphs, CUDA events.
+  e2e    -- same, through the public Python API with pinned HOST activations copied
+            in and the layer output copied back out inside the timed region.
+  roofline -- the coded GEMV kernel alone (algorithmic = code bytes per launch).
+  cpu_baseline -- the CPU oracle (C port of the reference's NumPy path) on the
+            host cores, bounded sample of the same layer.
+
+At N > 1 GPUs the projections are split-N tensor parallel (whole 128-channel
+output blocks per rank) with an NCCL all-gather of each projection's f16 output;
+total work is fixed, so scaling is "strong".
+
+`--impl reference` times the reference's CPU implementation of the path: its
+NumPy module cannot be installed on the GPU machine (it needs mlx), so this arm
+runs the C port under oracle/ with every host thread.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+LAYER = (  # name, IC, OC, K  (escha_mlx_b200.synth.DENSE_LAYER_27B)
+    ("q_proj", 5120, 6144, 2), ("k_proj", 5120, 1024, 2), ("v_proj", 5120, 1024, 2),
+    ("o_proj", 5120, 5120, 2), ("gate_proj", 5120, 17408, 3), ("up_proj", 5120, 17408, 3),
+    ("down_proj", 17408, 5120, 3),
+)
+LAYER_BYTES = sum(ic * oc * k // 8 for _, ic, oc, k in LAYER)
+HIDDEN = 5120
+L2_BYTES = 126 * 1024 * 1024
+METRIC = "coded GEMV compressed-weight GB/s"
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu = gpu_index
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 8:
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU legs
+
+def cpu_layer_inputs(batch: int, seed: int = 1234):
+    from escha_mlx_b200 import synth
+    rng = np.random.default_rng(seed)
+    projs = {}
+    for name, ic, oc, k in LAYER:
+        code, rin, rout = synth.coded_projection(rng, ic, oc, k)
+        projs[name] = (code, rin.astype(np.float32), rout.astype(np.float32), k)
+    x = synth.activations(rng, batch, HIDDEN)
+    return projs, x
+
+
+def cpu_layer_pass(oracle, projs, x):
+    """One layer pass on the CPU oracle, same dataflow as the GPU step."""
+    out = {}
+    for name in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj"):
+        code, rin, rout, k = projs[name]
+        out[name] = oracle.dense_linear(x, code, rin, rout, k)
+    h = oracle.swiglu(np.concatenate([out["gate_proj"], out["up_proj"]], axis=-1))
+    code, rin, rout, k = projs["down_proj"]
+    out["down_proj"] = oracle.dense_linear(h, code, rin, rout, k)
+    return out
+
+
+def time_cpu(batch: int, min_seconds: float, max_passes: int):
+    from oracle import escha_oracle as oracle
+    oracle.set_num_threads(os.cpu_count() or 1)
+    projs, x = cpu_layer_inputs(batch)
+    cpu_layer_pass(oracle, projs, x)  # warm (LUT, page-in)
+    passes, t0 = 0, time.perf_counter()
+    while True:
+        cpu_layer_pass(oracle, projs, x)
+        passes += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds or passes >= max_passes:
+            break
+    return LAYER_BYTES * passes / dt / 1e9, passes, dt, oracle.num_threads()
+
+
+def run_reference(args, rank: int) -> None:
+    """`--impl reference`: the reference's CPU path (C port), rank 0 only."""
+    if rank != 0:
+        return
+    from oracle import escha_oracle as oracle
+    oracle.set_num_threads(os.cpu_count() or 1)
+    projs, x = cpu_layer_inputs(args.batch)
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu_layer_pass(oracle, projs, x)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_layer_pass(oracle, projs, x)
+    dt = time.perf_counter() - t0
+    value = LAYER_BYTES * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16 weights, f32 accumulate", "data": "synthetic",
+        "config": workload_config(args, 1),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": oracle.num_threads(),
+                         "kind": "port",
+                         "sample": f"{args.steps} full passes of the layer (7 projections, "
+                                   f"{LAYER_BYTES} code bytes each pass), batch {args.batch}"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, n_sets: int) -> dict:
+    return {"workload": f"dense27b_layer_decode_b{args.batch}",
+            "projections": "q/k/v/o 2-bit 5120x{6144,1024,1024,5120}; gate/up 3-bit 5120x17408; "
+                           "down 3-bit 17408x5120",
+            "batch": args.batch, "code_bytes_per_step": LAYER_BYTES,
+            "parallelism": f"tp{args.gpus} split-N" if args.gpus > 1 else "single GPU",
+            "l2_policy": f"{n_sets} distinct weight sets rotated per step "
+                         f"({n_sets * LAYER_BYTES // args.gpus} B per GPU > L2)"}
+
+
+# --------------------------------------------------------------------------- GPU side
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0,
+                    help="bounded CPU-baseline sample (rank 0, N=1)")
+    ap.add_argument("--only", default=None,
+                    help="profiling aid: run just this projection's GEMV for --steps launches")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from escha_mlx_b200 import dense, graphs, msl
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path (use --impl reference "
+                         "for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    args.warmup = max(args.warmup, 3)
+    M = args.batch
+
+    # weight sets: enough distinct layers that a step's per-GPU code bytes never sit in L2
+    per_gpu = LAYER_BYTES // world
+    n_sets = max(2, -(-3 * L2_BYTES // per_gpu))
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1234 + rank)
+
+    def make_weight(ic: int, oc: int, k: int) -> dense.EschaWeight:
+        oc_local = oc // world
+        code = torch.randint(-2**31, 2**31 - 1, (ic // 16, oc_local // 16, 8 * k),
+                             dtype=torch.int32, device=device, generator=gen)
+        w = object.__new__(dense.EschaWeight)
+        w.K, w.IC, w.OC, w.code = k, ic, oc_local, code
+
+        def vec(n):
+            scale = torch.randn(n, device=device, generator=gen).abs() * 0.02 + 1e-3
+            sign = torch.randint(0, 2, (n,), device=device, generator=gen).float() * 2 - 1
+            return (scale * sign).half().float()   # f16-representable, held as f32
+        w.rin, w.rout = vec(ic), vec(oc_local)
+        return w
+
+    for _, ic, oc, _ in LAYER:
+        if (oc // 128) % world:
+            raise SystemExit(f"{oc // 128} output blocks do not split over {world} GPUs")
+    sets = [{name: dense.EschaLinear(make_weight(ic, oc, k)) for name, ic, oc, k in LAYER}
+            for _ in range(n_sets)]
+
+    def gather(y):
+        if world == 1:
+            return y
+        from escha_mlx_b200 import sharding
+        return sharding.all_gather_columns(y)
+
+    def layer_step(layer, x):
+        q = gather(layer["q_proj"](x))
+        k, v = dense.project_pair(layer["k_proj"], layer["v_proj"], x)
+        k, v = gather(k), gather(v)
+        o = gather(layer["o_proj"](x))
+        g, u = dense.project_pair(layer["gate_proj"], layer["up_proj"], x)
+        h = gather(msl.swiglu_pair(g, u))
+        d = gather(layer["down_proj"](h))
+        return q, k, v, o, d
+
+    launches_per_step = 13  # 5 transforms (2 paired) + 7 GEMV + swiglu, all kernels of this library
+
+    x0 = torch.randn((M, HIDDEN), device=device, generator=gen).half()
+
+    if args.only:
+        # profiling aid: K launches of one projection's fused GEMV, rotating weight sets
+        lin = [s[args.only] for s in sets]
+        ic = lin[0]._w.IC
+        xh = msl.dense_scaled_had(torch.randn((M, ic), device=device, generator=gen).half(),
+                                  lin[0]._w.rin, msl.RS)
+        for i in range(args.warmup + args.steps):
+            w = lin[i % n_sets]._w
+            msl.dense_gemm_rows_direct_out(xh, w.code, w.rout, w.K, w.IC, w.OC, 8, msl.RS)
+        torch.cuda.synchronize()
+        print(json.dumps({"only": args.only, "launches": args.steps}))
+        return
+
+    step_graphs = [graphs.GraphedCall(lambda x, L=L: layer_step(L, x), [x0]) for L in sets]
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+    for i in range(args.warmup):
+        step_graphs[i % n_sets].replay()
+    sync_all()
+
+    # ---- value: resident inputs, device-timed -----------------------------------------------
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        sync_all()
+        ev0.record(stream)
+        for i in range(args.steps):
+            step_graphs[i % n_sets].replay()
+        ev1.record(stream)
+        sync_all()
+    ms_total = ev0.elapsed_time(ev1)
+
+    # ---- e2e: pinned host activations in, layer output back out, every step -------------------
+    x_host = [torch.randn((M, HIDDEN)).half().pin_memory() for _ in range(4)]
+    y_host = torch.empty((M, HIDDEN), dtype=torch.float16).pin_memory()
+    for i in range(args.warmup):
+        out = step_graphs[i % n_sets](x_host[i % 4])
+        y_host.copy_(out[4], non_blocking=True)
+    sync_all()
+    ee0, ee1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ee0.record(stream)
+    for i in range(args.steps):
+        out = step_graphs[i % n_sets](x_host[i % 4])      # H2D copy + graph replay
+        y_host.copy_(out[4], non_blocking=True)           # D2H of the layer output
+    ee1.record(stream)
+    sync_all()
+    ms_e2e = ee0.elapsed_time(ee1)
+
+    # ---- roofline leg: the coded GEMV kernel alone --------------------------------------------
+    def gemv_only(layer, xs):
+        outs = []
+        for name, _, _, _ in LAYER:
+            w = layer[name]._w
+            outs.append(msl.dense_gemm_rows_direct_out(xs[w.IC], w.code, w.rout, w.K, w.IC, w.OC,
+                                                       8, msl.RS))
+        return outs
+
+    xs = {ic: msl.dense_scaled_had(torch.randn((M, ic), device=device, generator=gen).half(),
+                                   sets[0]["q_proj" if ic == HIDDEN else "down_proj"]._w.rin, msl.RS)
+          for ic in (HIDDEN, 17408)}
+    gemv_graphs = [graphs.GraphedCall(lambda L=L: gemv_only(L, xs), []) for L in sets]
+    for g in gemv_graphs:
+        g.replay()
+    sync_all()
+    er0, er1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(1, args.steps)
+    er0.record(stream)
+    for i in range(reps):
+        gemv_graphs[i % n_sets].replay()
+    er1.record(stream)
+    sync_all()
+    ms_gemv = er0.elapsed_time(er1)
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_total, ms_e2e, ms_gemv = (max_over_ranks(v) for v in (ms_total, ms_e2e, ms_gemv))
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        value = LAYER_BYTES * args.steps / (ms_total * 1e-3) / 1e9
+        e2e = LAYER_BYTES * args.steps / (ms_e2e * 1e-3) / 1e9
+        launches = 7 * reps
+        achieved = (LAYER_BYTES / world) * reps / (ms_gemv * 1e-3) / 1e9   # per GPU
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, "profiles", "gemv_mma_traffic.json")) as f:
+                traffic = json.load(f).get("dram_bytes_per_launch_avg")
+        except Exception:
+            pass
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 weights, f32 accumulate", "data": "synthetic",
+            "config": workload_config(args, n_sets),
+            "pct_of_hbm_peak": 100.0 * value / (peak * world),
+            "tokens_per_s": M * args.steps / (ms_total * 1e-3),
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": M * HIDDEN * 2,
+                    "d2h_bytes_per_step": M * HIDDEN * 2},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": traffic,
+                         "kernel": "gemv_mma_kernel (coded GEMV + fused output transform)",
+                         "launches_timed": launches,
+                         "avg_launch_us": ms_gemv * 1e3 / launches,
+                         "algorithmic_bytes_per_launch_avg": LAYER_BYTES / world / 7,
+                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
+            "clocks": clocks.summary(),
+        }
+        if world == 1:
+            cpu_gbs, passes, dt, cores = time_cpu(M, args.cpu_seconds, 200)
+            line["cpu_baseline"] = {
+                "value": cpu_gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                "sample": f"{passes} full layer passes ({dt:.1f} s) of the same 7-projection "
+                          f"layer at batch {M} on the CPU oracle (C port of escha_mlx/ref.py)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -147,6 +147,29 @@ int escha_scaled_had_out_pair(const float* mid0, const float* mid1, const float*
         "escha_scaled_had_out_pair");
 }
 
+int escha_had128(const float* x, long nblocks, float* out, void* stream) {
+    REQUIRE(nblocks >= 1, "%s: needs at least one 128-block, got %ld", __func__, nblocks);
+    REQUIRE_PTR(x);
+    REQUIRE_PTR(out);
+    return cuda_result(escha::launch_had128(x, out, nblocks, as_stream(stream)), "escha_had128");
+}
+
+int escha_w8a16(const void* x, const void* w8, const void* scale, int M, int N, int Kd, void* y,
+                void* stream) {
+    REQUIRE(M >= 1 && N >= 1, "%s: empty input (M=%d N=%d)", __func__, M, N);
+    REQUIRE(Kd >= 16 && Kd % 16 == 0, "%s: input width must be a positive multiple of 16, got %d",
+            __func__, Kd);
+    REQUIRE_PTR(x);
+    REQUIRE_PTR(w8);
+    REQUIRE(scale != nullptr && y != nullptr, "%s: NULL pointer", __func__);
+    REQUIRE((M + 7) / 8 <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
+    return cuda_result(
+        escha::launch_w8a16(static_cast<const __half*>(x), static_cast<const int8_t*>(w8),
+                            static_cast<const __half*>(scale), static_cast<__half*>(y), M, N, Kd,
+                            as_stream(stream)),
+        "escha_w8a16");
+}
+
 int escha_gemv_ref(const void* xh, const void* code, const int32_t* row_expert,
                    const int32_t* row_map, int slots, const void* lut, int M, int IC, int OC,
                    int K, int splits, float* part, float* mid, void* stream) {
@@ -315,11 +338,14 @@ int escha_coded_gemv_jobs(const void* xh, const void* code, const float* rout, c
     return cuda_result(escha::launch_gemv_mma(p, as_stream(stream)), "escha_coded_gemv_jobs");
 }
 
-int escha_swiglu(const void* gu, int M, int I, void* h, void* stream) {
+int escha_swiglu(const void* gate, const void* up, int M, int I, long stride, void* h,
+                 void* stream) {
     REQUIRE(M >= 1 && I >= 1, "%s: empty input (M=%d I=%d)", __func__, M, I);
-    REQUIRE_PTR(gu);
-    REQUIRE_PTR(h);
-    return cuda_result(escha::launch_swiglu(static_cast<const __half*>(gu), M, I,
+    REQUIRE(stride >= I, "%s: row stride %ld is below I=%d", __func__, stride, I);
+    if (gate == nullptr || up == nullptr || h == nullptr)
+        return fail(ESCHA_EINVAL, "%s: NULL pointer", __func__);
+    return cuda_result(escha::launch_swiglu(static_cast<const __half*>(gate),
+                                            static_cast<const __half*>(up), M, I, stride,
                                             static_cast<__half*>(h), as_stream(stream)),
                        "escha_swiglu");
 }

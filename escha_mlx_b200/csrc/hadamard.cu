@@ -66,6 +66,26 @@ scaled_had_kernel(HadShard s0, HadShard s1, const int32_t* __restrict__ row_expe
     *reinterpret_cast<uint2*>(s.out + off) = packed;
 }
 
+// Plain unnormalised H128 on f32 blocks (the reference's moe.had_blocks, which
+// calls mx.hadamard_transform(scale=1.0): escha_mlx/moe.py:19-27).
+__global__ void __launch_bounds__(256)
+had128_kernel(const float* __restrict__ x, float* __restrict__ out, long nblocks) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const long blk = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (blk >= nblocks) return;
+    const float4 m = *reinterpret_cast<const float4*>(x + blk * 128 + lane * 4u);
+    float v[4] = {m.x, m.y, m.z, m.w};
+    wht128_warp(v, lane);
+    *reinterpret_cast<float4*>(out + blk * 128 + lane * 4u) = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+cudaError_t launch_had128(const float* x, float* out, long nblocks, cudaStream_t st) {
+    const int warps = 8;
+    had128_kernel<<<static_cast<unsigned>((nblocks + warps - 1) / warps), warps * 32, 0, st>>>(
+        x, out, nblocks);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_scaled_had(bool output, const void* src0, const float* vec0, __half* out0,
                               int dim0, const void* src1, const float* vec1, __half* out1,
                               int dim1, const int32_t* row_expert, int M, float rs,

@@ -48,9 +48,13 @@ cudaError_t launch_group_rows(const int32_t* row_expert, int m, int E, int R, Ro
 cudaError_t launch_jobs_from_groups(const int32_t* rows_idx, const int32_t* group_expert,
                                     int n_groups, int R, int n_rows, int rows_per_job,
                                     RowJob* jobs, cudaStream_t st);
-cudaError_t launch_swiglu(const __half* gu, int M, int I, __half* h, cudaStream_t st);
+cudaError_t launch_swiglu(const __half* gate, const __half* up, int M, int I, long stride,
+                          __half* h, cudaStream_t st);
 cudaError_t launch_moe_combine(const __half* d16, const float* scores, int T, int top_k, int H,
                                __half* y, cudaStream_t st);
+cudaError_t launch_had128(const float* x, float* out, long nblocks, cudaStream_t st);
+cudaError_t launch_w8a16(const __half* x, const int8_t* w8, const __half* scale, __half* y, int M,
+                         int N, int Kd, cudaStream_t st);
 size_t gemv_mma_part_floats(int njobs, int splits, int OC, int rows_per_job);
 
 }  // namespace escha

@@ -80,14 +80,14 @@ __global__ void jobs_from_groups_kernel(const int32_t* __restrict__ rows_idx,
 // SwiGLU on the fp16-rounded merged gate/up output (ref.py:296-301):
 //   s = f16( g / (1 + exp(-g)) ) computed in f32,   h = f16( s * u )
 // ---------------------------------------------------------------------------
-__global__ void swiglu_kernel(const __half* __restrict__ gu, int M, int I,
-                              __half* __restrict__ h) {
+__global__ void swiglu_kernel(const __half* __restrict__ gate, const __half* __restrict__ up,
+                              int M, int I, long stride, __half* __restrict__ h) {
     const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= static_cast<long>(M) * I) return;
     const long r = idx / I, i = idx - r * I;
-    const float g = __half2float(gu[r * 2 * I + i]);
+    const float g = __half2float(gate[r * stride + i]);
     const __half s = __float2half_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))));
-    h[idx] = __hmul(s, gu[r * 2 * I + I + i]);
+    h[idx] = __hmul(s, up[r * stride + i]);
 }
 
 // ---------------------------------------------------------------------------
@@ -105,7 +105,7 @@ __global__ void moe_combine_kernel(const __half* __restrict__ d16, const float* 
         const long r = t * top_k + s;
         const float w16 = __half2float(__float2half_rn(scores[r]));
         const float contrib = __fmul_rn(__half2float(d16[r * H + c]), w16);
-        acc = s == 0 ? contrib : __fadd_rn(acc, contrib);
+        acc = __fadd_rn(acc, contrib);  // starts from +0 like a sum reduction
     }
     y[idx] = __float2half_rn(acc);
 }
@@ -128,9 +128,10 @@ cudaError_t launch_jobs_from_groups(const int32_t* rows_idx, const int32_t* grou
     return cudaGetLastError();
 }
 
-cudaError_t launch_swiglu(const __half* gu, int M, int I, __half* h, cudaStream_t st) {
+cudaError_t launch_swiglu(const __half* gate, const __half* up, int M, int I, long stride,
+                          __half* h, cudaStream_t st) {
     const long n = static_cast<long>(M) * I;
-    swiglu_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(gu, M, I, h);
+    swiglu_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(gate, up, M, I, stride, h);
     return cudaGetLastError();
 }
 

@@ -1,0 +1,166 @@
+"""The SwitchGLU-style MoE block of the qwen3_5_moe architecture, executing the
+escha trellis-coded routed experts on B200.
+
+Mirror of ``EschaSparseMoeBlock`` in the reference's
+``escha_mlx/models/qwen3_5_moe.py:62-273`` (the checkpoint loader half of that
+file belongs to the mlx-lm model skeleton and is not part of this path).
+
+Routing convention: fp32 logits from the fp16 gate Linear (one f16 round), top-k,
+softmax over the top-k values.  Each (token, slot) pair becomes one GEMV row;
+rows are laid out token-major.  Expert forward per row:
+
+    xh   = f16( H128(x * rin[e]) * RS )
+    mid  = xh @ decode(code[e])                       (f32 accumulate)
+    gu16 = f16( H128(mid) * RS * rout[e] )            -> f16(silu(g)) * u -> h
+    xh2  = f16( H128(h * rin_dn[e]) * RS )
+    d16  = f16( H128(xh2 @ decode_dn) * RS * rout_dn[e] )
+    y[token] = sum over slots, in slot order, of f32(d16) * f32(f16(score))
+
+plus the shared expert (int8 SwiGLU, sigmoid-gated).  The slot sum is a fixed
+order reduction -- never a scatter-add -- so the block is bit-reproducible.
+
+With ``torch.distributed`` initialised and ``expert_parallel=True`` the routed
+experts are sharded over ranks (this rank holds ``gu``/``dn`` for experts
+[e_lo, e_hi)); each rank computes the rows whose expert it owns, the f16 expert
+outputs are all-gathered, and every rank runs the same combine, so the result is
+bit-identical to one GPU.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from .. import envs, moe, msl, quant, sharding
+
+MODEL_TYPE = "qwen3_5_moe"
+RS = msl.RS
+
+
+class EschaSparseMoeBlock(torch.nn.Module):
+    """Drop-in MoE block: router, routed coded experts, shared int8 expert."""
+
+    def __init__(self, hidden_size: int, num_experts: int, top_k: int,
+                 gu: moe.EschaExperts, dn: moe.EschaExperts,
+                 gate_w: np.ndarray, shg_w: np.ndarray, shared: dict,
+                 group_size: int = quant.DEFAULT_GROUP,
+                 expert_range: tuple[int, int] | None = None) -> None:
+        super().__init__()
+        self.top_k = top_k
+        self.num_experts = num_experts
+        self._gu = gu
+        self._dn = dn
+        self._inter = gu.OC // 2
+        dev = gu.code.device
+        self._e_lo, self._e_hi = expert_range or (0, num_experts)
+        if self._e_hi - self._e_lo != gu.E or gu.E != dn.E:
+            raise ValueError(
+                f"expert stacks hold {gu.E}/{dn.E} experts, the block expects "
+                f"{self._e_hi - self._e_lo}")
+        if gu.IC != hidden_size or dn.OC != hidden_size or dn.IC != self._inter:
+            raise ValueError(
+                f"expert shapes {gu.IC}x{gu.OC} / {dn.IC}x{dn.OC} do not form a "
+                f"hidden={hidden_size} SwiGLU expert")
+        self.gate_weight = torch.from_numpy(np.asarray(gate_w).astype(np.float16)).to(dev)
+        self.shared_expert_gate_weight = torch.from_numpy(
+            np.asarray(shg_w).astype(np.float16).reshape(1, hidden_size)).to(dev)
+        self.sh_gate = quant.make_linear(shared["gate_w8"], shared["gate_scale"], group_size, dev)
+        self.sh_up = quant.make_linear(shared["up_w8"], shared["up_scale"], group_size, dev)
+        self.sh_down = quant.make_linear(shared["down_w8"], shared["down_scale"], group_size, dev)
+        self._mode = "fused"
+        self._fused_had = msl.use_fused_had()
+        self._block_env = envs.ESCHA_MLX_BLOCK_R.get()
+
+    # -- expert path ------------------------------------------------------
+
+    def _rows(self, xf: torch.Tensor, ids: torch.Tensor):
+        """Token-major rows: row t*top_k+s is (token t, slot s)."""
+        t = xf.shape[0]
+        row_expert = ids.reshape(t * self.top_k).to(torch.int32)
+        row_token = torch.arange(t, dtype=torch.int32, device=xf.device).repeat_interleave(self.top_k)
+        return row_expert, row_token
+
+    def _blocked_R(self, m: int) -> int:
+        """Rows-per-group policy of the reference (:124-170), kept for callers
+        that query it.  The tensor-core kernel needs no such policy: every
+        expert's stream is read once and shared by all of its rows."""
+        if self._block_env is not None:
+            return self._block_env
+        if m >= 2048:
+            return 12
+        if m >= 1024:
+            return 4
+        if m >= 320:
+            return 3
+        if m >= 128:
+            return 2
+        return 1
+
+    def _gemv(self, xh: torch.Tensor, row_expert: torch.Tensor, ex: moe.EschaExperts,
+              jobs: torch.Tensor | None = None) -> torch.Tensor:
+        return msl.moe_gemv(xh, ex.code, row_expert, ex.K, ex.IC, ex.OC, jobs=jobs)
+
+    def _leg(self, rows: torch.Tensor, row_expert: torch.Tensor, ex: moe.EschaExperts,
+             jobs: torch.Tensor | None) -> torch.Tensor:
+        """One coded projection over expert-indexed rows -> f16 [m, OC]."""
+        xh = msl.scaled_had(rows, ex.rin, row_expert, RS)
+        if msl.gemv_family() == "mma" and self._fused_had:
+            out = torch.zeros((rows.shape[0], ex.OC), dtype=torch.float16, device=rows.device) \
+                if self._sharded() else None
+            return msl.coded_gemv_jobs(xh, ex.code, jobs, ex.rout, ex.K, ex.IC, ex.OC, ex.E,
+                                       out=out)
+        mid = self._gemv(xh, row_expert, ex, jobs)
+        return msl.scaled_had_out(mid, ex.rout, row_expert, RS)
+
+    def _sharded(self) -> bool:
+        return (self._e_hi - self._e_lo) != self.num_experts
+
+    def _expert_path(self, xf: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
+        t = xf.shape[0]
+        row_expert, row_token = self._rows(xf, ids)
+        rows = xf[row_token.long()]
+        owned = None
+        job_expert = row_expert
+        if self._sharded():
+            # rows of experts another rank owns get no job here (expert -1 matches no
+            # local expert); their output rows stay zero and are replaced by the
+            # owner's rows in the ownership-selecting all-gather below
+            owned = (row_expert >= self._e_lo) & (row_expert < self._e_hi)
+            local = row_expert - self._e_lo
+            job_expert = torch.where(owned, local, torch.full_like(local, -1))
+            row_expert = torch.where(owned, local, torch.zeros_like(local))
+        jobs = msl.group_rows(job_expert, self._gu.E) if msl.gemv_family() == "mma" else None
+        gu16 = self._leg(rows, row_expert, self._gu, jobs)
+        h = msl.swiglu(gu16)
+        d16 = self._leg(h, row_expert, self._dn, jobs)
+        if owned is not None:
+            d16 = sharding.all_gather_rows_by_owner(d16, owned)
+        y16 = msl.moe_combine(d16, scores.reshape(t * self.top_k).to(torch.float32).contiguous(),
+                              t, self.top_k)
+        # the routed-expert sum is rounded to f16 before the shared expert is added
+        return y16.float()
+
+    # -- block forward ----------------------------------------------------
+
+    def route(self, xf: torch.Tensor):
+        logits = F.linear(xf, self.gate_weight).float()
+        top, ids = torch.topk(logits, self.top_k, dim=-1)
+        scores = torch.softmax(top, dim=-1)
+        return ids, scores
+
+    def forward(self, x: torch.Tensor, ids: torch.Tensor | None = None,
+                scores: torch.Tensor | None = None) -> torch.Tensor:
+        shape = x.shape
+        hdim = shape[-1]
+        xf = x.reshape(-1, hdim).to(torch.float16).contiguous()
+        if ids is None:
+            ids, scores = self.route(xf)
+        y = self._expert_path(xf, ids, scores)
+
+        g = self.sh_gate(xf).float()
+        u = self.sh_up(xf).float()
+        hh = ((g * torch.sigmoid(g)) * u).to(torch.float16)
+        sh = self.sh_down(hh).float()
+        sgate = torch.sigmoid(F.linear(xf, self.shared_expert_gate_weight).float())
+        out = (y + sh * sgate).to(x.dtype)
+        return out.reshape(shape)

@@ -285,13 +285,15 @@ def _gemv_mma_dense(xh, code, rout, K, IC, OC, splits, rs=RS):
 def coded_gemv_jobs(xh: torch.Tensor, code_u32: torch.Tensor, jobs: torch.Tensor,
                     rout: torch.Tensor | None, K: int, IC: int, OC: int, E: int,
                     splits: int | None = None, rs: float = RS, rows_per_job: int = 8,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
+                    out: torch.Tensor | None = None, policy_rows: int | None = None) -> torch.Tensor:
     """Tensor-core expert GEMV over row jobs (see ``group_rows``).  Returns f32
     mid [m, OC], or f16 y [m, OC] with the output transform fused when ``rout``
-    ([E, OC] f32) is given."""
+    ([E, OC] f32) is given.  ``policy_rows`` is the row count the split policy is
+    evaluated at (default: the rows of ``xh``)."""
     m = xh.shape[0]
     njobs = jobs.shape[0]
-    s = split_k_for(m, OC, IC // 16, expected_jobs(m, E)) if splits is None \
+    pr = m if policy_rows is None else policy_rows
+    s = split_k_for(pr, OC, IC // 16, expected_jobs(pr, E)) if splits is None \
         else max(1, min(int(splits), IC // 128))
     if out is None:
         out = torch.empty((m, OC), dtype=torch.float32 if rout is None else torch.float16,
@@ -418,7 +420,7 @@ def moe_gemm_rows(xh: torch.Tensor, code_u32: torch.Tensor, rows_idx: torch.Tens
     E = code_u32.shape[0]
     out = torch.zeros((n_rows + 1, OC), dtype=torch.float32, device=xh.device)
     coded_gemv_jobs(xh, code_u32, jobs, None, K, IC, OC, E, None, rows_per_job=rows_per_job,
-                    out=out)
+                    out=out, policy_rows=n_rows)
     return out
 
 
@@ -430,8 +432,22 @@ def swiglu(gu16: torch.Tensor) -> torch.Tensor:
     """gu16 [m, 2I] f16 (gate first) -> f16(f16(silu(g)) * u) [m, I]
     (models/qwen3_5_moe.py:221-223 of the reference)."""
     m, two_i = gu16.shape
-    h = torch.empty((m, two_i // 2), dtype=torch.float16, device=gu16.device)
-    check(lib.escha_swiglu(ptr(gu16, torch.float16), m, two_i // 2, ptr(h), stream()))
+    inter = two_i // 2
+    h = torch.empty((m, inter), dtype=torch.float16, device=gu16.device)
+    base = ptr(gu16, torch.float16)
+    check(lib.escha_swiglu(base, ctypes.c_void_p(base.value + 2 * inter), m, inter, two_i, ptr(h),
+                           stream()))
+    return h
+
+
+def swiglu_pair(gate16: torch.Tensor, up16: torch.Tensor) -> torch.Tensor:
+    """Same stage for gate and up held in two [m, I] f16 tensors (a dense MLP)."""
+    m, inter = gate16.shape
+    if up16.shape != gate16.shape:
+        raise ValueError("swiglu_pair needs gate and up of equal shape")
+    h = torch.empty((m, inter), dtype=torch.float16, device=gate16.device)
+    check(lib.escha_swiglu(ptr(gate16, torch.float16), ptr(up16, torch.float16), m, inter, inter,
+                           ptr(h), stream()))
     return h
 
 

@@ -1,0 +1,92 @@
+"""int8 dense linears (per-output-row fp16 scale) of the escha exports.
+
+Counterpart of the reference's ``escha_mlx/quant.py``.  The reference repacks the
+export's ``weight_int8 [N, K]`` + ``weight_scale [N]`` into MLX's affine-Q8 group
+layout (``pack_q8`` :82-97, ``validate_pack`` :100-122) because that is the
+format ``mx.quantized_matmul`` consumes; that repack is exact, so the arithmetic
+contract is the un-repacked one, ``ref.w8a16`` (escha_mlx/ref.py:308-311):
+
+    y = f16( f32(x) @ f32( f16( f32(w8) * f32(scale) ) )^T )
+
+On B200 the kernel reads the export's own layout, so there is nothing to repack;
+``pack_q8``/``validate_pack`` are kept as exact, trivially invertible
+passthroughs so loader code written against the reference keeps working, and
+``group_size`` arguments are accepted and ignored (the reference documents group
+size as numerically free, tests/test_mlx_cpu.py:19-41).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ._lib import check, lib, ptr, stream
+
+DEFAULT_GROUP = 64
+
+
+def fit_group(k: int, group_size: int = DEFAULT_GROUP) -> int:
+    """Largest supported group size dividing ``k`` (reference :68-79); informational."""
+    for g in (group_size, 128, 64, 32):
+        if g <= group_size and k % g == 0:
+            return g
+    raise ValueError(f"no supported group size divides K={k}")
+
+
+def pack_q8(w8: np.ndarray, scale: np.ndarray, group_size: int = DEFAULT_GROUP):
+    """Validate and return the int8 matrix and its f16 row scales in kernel layout."""
+    w8 = np.ascontiguousarray(w8)
+    scale = np.asarray(scale)
+    if w8.dtype != np.int8 or w8.ndim != 2:
+        raise ValueError(f"weight_int8 must be a 2-D int8 array, got {w8.dtype} {w8.shape}")
+    if scale.shape != (w8.shape[0],):
+        raise ValueError(f"weight_scale must have shape ({w8.shape[0]},), got {scale.shape}")
+    if w8.shape[1] % 16:
+        raise ValueError(f"int8 linear input width must be a multiple of 16, got {w8.shape[1]}")
+    return w8, scale.astype(np.float16)
+
+
+def validate_pack(w8: np.ndarray, scale: np.ndarray, packed) -> None:
+    """Refuse to serve unless the packed form reproduces the export exactly."""
+    pw, ps = packed
+    if not (np.array_equal(pw, w8) and np.array_equal(ps, np.asarray(scale).astype(np.float16))):
+        raise ValueError("int8 repack is not bit-exact")
+
+
+def w8a16(x: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """x [M, K] f16, w8 [N, K] int8, scale [N] f16 -> y [M, N] f16."""
+    m, kd = x.shape
+    n = w8.shape[0]
+    if w8.shape[1] != kd:
+        raise ValueError(f"input has {kd} channels, the int8 linear takes {w8.shape[1]}")
+    y = torch.empty((m, n), dtype=torch.float16, device=x.device)
+    check(lib.escha_w8a16(ptr(x, torch.float16), ptr(w8, torch.int8), ptr(scale, torch.float16),
+                          m, n, kd, ptr(y), stream()))
+    return y
+
+
+class EschaQ8Linear(torch.nn.Module):
+    """An int8-weight linear with per-output-row scale (reference :129-143)."""
+
+    def __init__(self, w8: np.ndarray, scale: np.ndarray, group_size: int = DEFAULT_GROUP,
+                 device=None) -> None:
+        super().__init__()
+        pw, ps = pack_q8(w8, scale, group_size)
+        validate_pack(w8, scale, (pw, ps))
+        dev = device or "cuda"
+        self._w8 = torch.from_numpy(pw).to(dev)
+        self._scale = torch.from_numpy(ps).to(dev)
+        self.out_features, self.in_features = pw.shape
+
+    def arrays(self) -> list[torch.Tensor]:
+        return [self._w8, self._scale]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        rows = x.reshape(-1, shape[-1]).to(torch.float16).contiguous()
+        return w8a16(rows, self._w8, self._scale).reshape(*shape[:-1], self.out_features)
+
+
+def make_linear(w8: np.ndarray, scale: np.ndarray, group_size: int = DEFAULT_GROUP,
+                device=None) -> EschaQ8Linear:
+    """Build the int8 linear module from export leaves (reference :269-308)."""
+    return EschaQ8Linear(w8, scale, group_size, device)

@@ -78,6 +78,18 @@ int escha_scaled_had_out_pair(const float *mid0, const float *mid1, const float 
                               const float *rout1, int M, int OC0, int OC1, float rs, void *out0,
                               void *out1, void *stream);
 
+/* out = H128(x) on nblocks contiguous 128-float blocks, unnormalised, f32 in
+ * and out.  Replaces moe.had_blocks, i.e. mx.hadamard_transform(scale=1.0)
+ * (escha_mlx/moe.py:19-27); bit-identical to ref.h128 (ref.py:204-218). */
+int escha_had128(const float *x, long nblocks, float *out, void *stream);
+
+/* int8-weight linear  y = f16( f32(x) @ f32( f16( f32(w8) * f32(scale) ) )^T ):
+ * x [M,Kd] binary16, w8 [N,Kd] int8, scale [N] binary16, y [M,N] binary16,
+ * Kd a multiple of 16.  Replaces EschaQ8Linear's mx.quantized_matmul call
+ * (escha_mlx/quant.py:129-143) and follows ref.w8a16 (ref.py:308-311). */
+int escha_w8a16(const void *x, const void *w8, const void *scale, int M, int N, int Kd, void *y,
+                void *stream);
+
 /* Per-row coded GEMV in the reference kernels' exact accumulation order
  * (bit-identical to them for a given input):
  *     mid[r,:] = f32(xh[r,:]) @ f32(decode(code[row_expert[r]]))      f32 [M,OC]
@@ -156,10 +168,13 @@ int escha_coded_gemv_jobs(const void *xh, const void *code, const float *rout, c
                           int splits, float rs, void *workspace, size_t workspace_bytes, void *out,
                           void *stream);
 
-/* h = f16( f16(silu(g)) * u ) on gu [M,2I] binary16 (gate = first I channels).
- * Replaces the elementwise stage at models/qwen3_5_moe.py:221-223
+/* h[r,i] = f16( f16(silu(g)) * u ), g = gate[r*stride+i], u = up[r*stride+i]
+ * (binary16; 2-byte aligned pointers suffice).  For the merged [M,2I] layout
+ * pass gate = gu, up = gu + I, stride = 2I; for two separate [M,I] tensors
+ * stride = I.  Replaces the elementwise stage at models/qwen3_5_moe.py:221-223
  * (ref.swiglu, ref.py:296-301). */
-int escha_swiglu(const void *gu, int M, int I, void *h, void *stream);
+int escha_swiglu(const void *gate, const void *up, int M, int I, long stride, void *h,
+                 void *stream);
 
 /* y[t,:] = f16( sum over slots s, ascending, of f32(d16[t*top_k+s,:]) *
  * f32(f16(scores[t*top_k+s])) ) -- the fixed-order combine at

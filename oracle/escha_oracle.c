@@ -521,7 +521,7 @@ int esc_moe_routed(const uint16_t *x, const int32_t *ids, const float *scores, i
                 int r = t * top_k + s;
                 float w16 = esc_h2f(esc_f2h(scores[r]));
                 float contrib = esc_h2f(d16[(size_t)r * H + c]) * w16;
-                acc = (s == 0) ? contrib : acc + contrib;
+                acc = acc + contrib; /* starts from +0 like a sum reduction */
             }
             y16[(size_t)t * H + c] = esc_f2h(acc);
         }

@@ -1,0 +1,274 @@
+"""GPU parity of the routed-expert path: row grouping, expert-indexed GEMV,
+row-blocked GEMM, elementwise stages, int8 linear and the whole MoE block,
+through the C ABI, against the CPU oracle and the golden vectors.  Mirrors
+tests/test_metal.py:46-72, tests/test_blocked.py, tests/test_moe_determinism.py
+and tests/test_mlx_cpu.py:55-132 of the reference."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from cases import MOE_CASE, bits, moe_inputs, rel_err
+from escha_mlx_b200 import moe, msl, quant, synth
+from escha_mlx_b200.models.qwen3_5_moe import EschaSparseMoeBlock
+
+pytestmark = pytest.mark.gpu
+
+RS = msl.RS
+GEMV_TOL = 1e-3
+
+
+def dev(a, device):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+def set_env(monkeypatch, **kv):
+    for k, v in kv.items():
+        if v is None:
+            monkeypatch.delenv(k, raising=False)
+        else:
+            monkeypatch.setenv(k, str(v))
+
+
+def parse_jobs(jobs):
+    out = []
+    for rec in host(jobs):
+        e, n = int(rec[0]), int(rec[1])
+        out.append((e, [int(r) for r in rec[2:2 + n]]))
+    return out
+
+
+# --------------------------------------------------------------------------- grouping
+
+@pytest.mark.parametrize("R", [8, 16])
+@pytest.mark.parametrize("m,E,skew", [(8, 256, "uniform"), (64, 256, "uniform"), (512, 256, "uniform"),
+                                      (40, 16, "one_expert"), (16, 16, "one_each"), (1, 4, "uniform"),
+                                      (100, 8, "with_foreign")])
+def test_group_rows_model(cuda, m, E, skew, R):
+    rng = np.random.default_rng(m * 31 + E + R)
+    if skew == "one_expert":
+        re = np.full(m, 5, np.int32)
+    elif skew == "one_each":
+        re = rng.permutation(E).astype(np.int32)[:m]
+    elif skew == "with_foreign":   # rows of experts this shard does not own are marked -1
+        re = rng.integers(-1, E, size=m).astype(np.int32)
+    else:
+        re = rng.integers(0, E, size=m).astype(np.int32)
+    jobs = parse_jobs(msl.group_rows(dev(re, cuda), E, R))
+    assert len(jobs) == msl.jobs_bound(m, E, R)
+    seen, last_e, done = [], -1, False
+    for e, rows in jobs:
+        if not rows:
+            done = True
+            continue
+        assert not done, "a real job after an empty one"
+        assert 1 <= len(rows) <= R and e >= last_e
+        assert all(re[r] == e for r in rows) and rows == sorted(rows)
+        last_e = e
+        seen.extend(rows)
+    assert sorted(seen) == [i for i in range(m) if re[i] >= 0]
+    # jobs of one expert are full except its last
+    by_e = {}
+    for e, rows in jobs:
+        if rows:
+            by_e.setdefault(e, []).append(len(rows))
+    assert all(all(n == R for n in v[:-1]) for v in by_e.values())
+
+
+@pytest.mark.parametrize("R", [2, 4, 12])
+def test_build_groups_matches_oracle(cuda, oracle, R):
+    rng = np.random.default_rng(R)
+    E, m = 16, 53
+    re = rng.integers(0, E, size=m).astype(np.int32)
+    ng = moe.n_groups_bound(m, E, R)
+    assert ng == oracle.n_groups_bound(m, E, R)
+    rows_idx, group_expert = moe.build_groups(dev(re, cuda), E, R, ng)
+    want_rows, want_ge = oracle.build_groups(re, E, R, ng)
+    assert np.array_equal(host(rows_idx), want_rows)
+    assert np.array_equal(host(group_expert), want_ge)
+    full = moe.build_groups(dev(re, cuda), E, R, ng, with_sorted=True)
+    order, src_row0, n_valid = (host(t) for t in full[2:])
+    assert np.array_equal(order, np.argsort(re, kind="stable"))
+    for g in range(ng):
+        e = want_ge[g]
+        real = want_rows[g * R:(g + 1) * R]
+        real = real[real < m]
+        assert n_valid[g] == len(real)
+        if e >= 0:
+            assert np.array_equal(order[src_row0[g]:src_row0[g] + n_valid[g]], real)
+
+
+# --------------------------------------------------------------------------- expert GEMV
+
+def _stack(rng, K, IC, OC, E, M):
+    code, _, _ = synth.coded_projection(rng, IC, OC, K, E)
+    xh = (rng.standard_normal((M, IC)) * 0.05).astype(np.float16)
+    re = rng.integers(0, E, size=M).astype(np.int32)
+    re[0], re[-1] = 0, E - 1
+    return code, xh, re
+
+
+@pytest.mark.parametrize("family", ["mma", "reforder"])
+@pytest.mark.parametrize("K,IC,OC,E,M", [(2, 512, 256, 4, 8), (3, 256, 384, 4, 8), (2, 256, 128, 6, 40),
+                                         (3, 384, 256, 3, 1)])
+def test_moe_gemv_expert_offsets(cuda, oracle, monkeypatch, family, K, IC, OC, E, M):
+    set_env(monkeypatch, ESCHA_MLX_GEMV=family, ESCHA_MLX_SPLITK=None)
+    code, xh, re = _stack(np.random.default_rng(K + IC + M), K, IC, OC, E, M)
+    mid = host(msl.moe_gemv(dev(xh, cuda), msl.code_tensor(code, cuda), dev(re, cuda), K, IC, OC))
+    assert rel_err(mid, oracle.gemv_f64(xh, code, re, K, IC, OC)) < GEMV_TOL
+    want = oracle.gemv_ref_order(xh, code, re, K, IC, OC)
+    if family == "reforder":
+        assert np.array_equal(bits(mid), bits(want))
+    else:
+        assert rel_err(mid, want) < 2e-5
+
+
+@pytest.mark.parametrize("R", [2, 4, 12])
+@pytest.mark.parametrize("skew", ["uniform", "one_expert", "one_each", "single_row"])
+def test_row_blocked_gemm_bit_identical_to_per_row(cuda, monkeypatch, R, skew):
+    """moe_gemm_rows over build_groups output == per-row moe_gemv, every f32 bit,
+    incl. all-one-expert / one-per-expert / single-row skews
+    (tests/test_blocked.py:69-161)."""
+    set_env(monkeypatch, ESCHA_MLX_GEMV="mma", ESCHA_MLX_SPLITK=None)
+    rng = np.random.default_rng(R * 7 + len(skew))
+    K, IC, OC, E = 2, 512, 256, 8
+    m = {"uniform": 37, "one_expert": 21, "one_each": 8, "single_row": 1}[skew]
+    code, _, _ = synth.coded_projection(rng, IC, OC, K, E)
+    xh = (rng.standard_normal((m, IC)) * 0.05).astype(np.float16)
+    re = {"uniform": rng.integers(0, E, size=m), "one_expert": np.full(m, 3),
+          "one_each": rng.permutation(E), "single_row": np.array([E - 1])}[skew].astype(np.int32)
+    c, x, r = msl.code_tensor(code, cuda), dev(xh, cuda), dev(re, cuda)
+    per_row = msl.moe_gemv(x, c, r, K, IC, OC)
+    ng = moe.n_groups_bound(m, E, R)
+    rows_idx, group_expert = moe.build_groups(r, E, R, ng)
+    x_pad = torch.cat([x, torch.zeros((1, IC), dtype=x.dtype, device=cuda)])
+    blocked = msl.moe_gemm_rows(x_pad, c, rows_idx, group_expert, K, IC, OC, R, m)
+    assert blocked.shape == (m + 1, OC)
+    assert torch.equal(blocked[:m], per_row)
+    assert torch.count_nonzero(blocked[m]) == 0
+    set_env(monkeypatch, ESCHA_MLX_GEMV="reforder")
+    ref_rows = msl.moe_gemm_rows(x_pad, c, rows_idx, group_expert, K, IC, OC, R, m)
+    assert torch.equal(ref_rows[:m], msl.moe_gemv(x, c, r, K, IC, OC))
+
+
+def test_expert_gemv_reproducible(cuda, monkeypatch):
+    set_env(monkeypatch, ESCHA_MLX_GEMV="mma", ESCHA_MLX_SPLITK=None)
+    code, xh, re = _stack(np.random.default_rng(3), 2, 1024, 256, 16, 64)
+    c, x, r = msl.code_tensor(code, cuda), dev(xh, cuda), dev(re, cuda)
+    first = msl.moe_gemv(x, c, r, 2, 1024, 256)
+    for _ in range(16):
+        assert torch.equal(msl.moe_gemv(x, c, r, 2, 1024, 256), first)
+
+
+# --------------------------------------------------------------------------- elementwise + int8
+
+def test_had_blocks_bit_exact(cuda, oracle):
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((5, 384)).astype(np.float32) * 3
+    assert np.array_equal(bits(host(moe.had_blocks(dev(x, cuda)))), bits(oracle.h128(x)))
+    with pytest.raises(ValueError, match="divisible by 128"):
+        moe.had_blocks(torch.zeros((2, 100), device=cuda))
+
+
+def test_swiglu_and_combine(cuda, oracle, seeded_linear):
+    gu = seeded_linear["swiglu_in"]
+    got = host(msl.swiglu(dev(gu, cuda)))
+    diff = np.abs(bits(got).astype(np.int32) - bits(seeded_linear["swiglu_out"]).astype(np.int32))
+    assert diff.max() <= 1 and (diff > 0).mean() < 0.01     # expf: one f16 ulp on rare elements
+    inter = gu.shape[1] // 2
+    pair = host(msl.swiglu_pair(dev(gu[:, :inter], cuda), dev(gu[:, inter:], cuda)))
+    assert np.array_equal(bits(pair), bits(got))
+    rng = np.random.default_rng(2)
+    T, k, H = 5, 8, 256
+    d16 = rng.standard_normal((T * k, H)).astype(np.float16)
+    scores = rng.random((T, k)).astype(np.float32)
+    want = np.zeros((T, H), np.float32)
+    for s in range(k):   # ascending slot order, f32
+        want = want + d16[s::k].astype(np.float32) * scores[:, s].astype(np.float16).astype(np.float32)[:, None]
+    y = host(msl.moe_combine(dev(d16, cuda), dev(scores.reshape(-1), cuda), T, k))
+    assert np.array_equal(bits(y), bits(want.astype(np.float16)))
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 19])
+def test_w8a16(cuda, oracle, ref_w8a16, M):
+    g = ref_w8a16
+    y = host(quant.w8a16(dev(g["x"], cuda), dev(g["w8"], cuda), dev(g["scale"].astype(np.float16), cuda)))
+    assert rel_err(y, g["expected"]) < 2e-3          # the reference's bar, tests/test_mlx_cpu.py:55-65
+    rng = np.random.default_rng(M)
+    w8, sc = synth.int8_linear(rng, 200, 512)
+    x = synth.activations(rng, M, 512)
+    lin = quant.make_linear(w8, sc, device=cuda)
+    got = host(lin(dev(x, cuda)))
+    assert got.shape == (M, 200)
+    assert rel_err(got, oracle.w8a16(x, w8, sc)) < 2e-3
+    with pytest.raises(ValueError, match="multiple of 16"):
+        quant.make_linear(w8[:, :100], sc, device=cuda)
+
+
+# --------------------------------------------------------------------------- whole block
+
+def _block(w, cuda, top_k, Kd_check=3):
+    gu = moe.EschaExperts(w["gu_code"], w["gu_rin"], w["gu_rout"], device=cuda)
+    dn = moe.EschaExperts(w["dn_code"], w["dn_rin"], w["dn_rout"], device=cuda)
+    shared = {k[3:]: v for k, v in w.items() if k.startswith("sh_")}
+    E, H = w["gate_w"].shape
+    return EschaSparseMoeBlock(H, E, top_k, gu, dn, w["gate_w"], w["shg_w"], shared)
+
+
+@pytest.mark.parametrize("family", ["mma", "reforder"])
+def test_moe_block_vs_reference_and_oracle(cuda, oracle, seeded_moe_block, monkeypatch, family):
+    set_env(monkeypatch, ESCHA_MLX_GEMV=family, ESCHA_MLX_SPLITK=None)
+    w, x = moe_inputs()
+    blk = _block(w, cuda, MOE_CASE["top_k"])
+    xd = dev(x, cuda)
+    ids, scores = blk.route(xd)
+    assert np.array_equal(np.sort(host(ids), axis=-1), np.sort(seeded_moe_block["ids"], axis=-1))
+    ref_ids, ref_scores = dev(seeded_moe_block["ids"], cuda), dev(seeded_moe_block["scores"], cuda)
+    out = host(blk(xd.reshape(1, *x.shape), ref_ids, ref_scores))[0]
+    assert rel_err(out, seeded_moe_block["out"]) < 5e-3      # ref.moe_block's own output
+    routed = host(blk._expert_path(xd, ref_ids, ref_scores))
+    want = oracle.moe_routed(x, seeded_moe_block["ids"], seeded_moe_block["scores"],
+                             w["gu_code"], w["gu_rin"], w["gu_rout"], 2,
+                             w["dn_code"], w["dn_rin"], w["dn_rout"], 3).astype(np.float32)
+    assert rel_err(routed, want) < (2e-3 if family == "mma" else 1e-3)
+    again = host(blk(xd.reshape(1, *x.shape), ref_ids, ref_scores))[0]
+    assert np.array_equal(bits(again), bits(out))
+
+
+def test_rows_are_token_major(cuda):
+    w, x = moe_inputs()
+    blk = _block(w, cuda, MOE_CASE["top_k"])
+    ids = torch.arange(8, device=cuda).reshape(4, 2) % 8
+    row_expert, row_token = blk._rows(dev(x, cuda), ids)
+    assert host(row_token).tolist() == [0, 0, 1, 1, 2, 2, 3, 3]
+    assert host(row_expert).tolist() == host(ids).reshape(-1).tolist()
+
+
+@pytest.mark.parametrize("T", [1, 8, 64])
+def test_full_size_moe_layer(cuda, oracle, monkeypatch, T):
+    """35B-A3B-class shapes (E=256, top-8, H=2048, I=512, 2-bit): the routed path
+    against the oracle where the oracle finishes in seconds (T <= 8), and for
+    every T bit-reproducibility plus agreement with the independent
+    reference-order kernels."""
+    set_env(monkeypatch, ESCHA_MLX_GEMV="mma", ESCHA_MLX_SPLITK=None)
+    cfg = synth.MOE_35B
+    rng = np.random.default_rng(35)
+    w = synth.moe_weights(rng, cfg["E"], cfg["H"], cfg["I"], cfg["Kg"], cfg["Kd"])
+    x = synth.activations(rng, T, cfg["H"])
+    ids, scores = synth.topk_softmax(synth.router_logits(rng, T, cfg["E"]), cfg["top_k"])
+    blk = _block(w, cuda, cfg["top_k"])
+    xd, idd, scd = dev(x, cuda), dev(ids, cuda), dev(scores, cuda)
+    y = blk._expert_path(xd, idd, scd)
+    for _ in range(4):
+        assert torch.equal(blk._expert_path(xd, idd, scd), y)
+    if T <= 8:
+        want = oracle.moe_routed(x, ids, scores, w["gu_code"], w["gu_rin"], w["gu_rout"], cfg["Kg"],
+                                 w["dn_code"], w["dn_rin"], w["dn_rout"], cfg["Kd"]).astype(np.float32)
+        assert rel_err(host(y), want) < 2e-3
+    set_env(monkeypatch, ESCHA_MLX_GEMV="reforder")
+    assert rel_err(host(y), host(blk._expert_path(xd, idd, scd))) < 2e-3
