@@ -55,7 +55,13 @@ int check_shape(const char* fn, int K, int IC, int OC, int mult) {
 
 cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
-size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+// The workspace starts with a fixed-size counter region (one int32 per (job,
+// output block)); split-K partials follow it.  Keeping the boundary fixed means
+// memory that ever holds partials is never read as a counter, so the "counters
+// are zero between launches" invariant survives launches of different shapes
+// sharing one workspace.
+constexpr size_t kCounterBytes = size_t(1) << 20;
+constexpr size_t kMaxCounters = kCounterBytes / sizeof(int32_t);
 
 }  // namespace
 
@@ -200,8 +206,8 @@ int escha_gemv_ref(const void* xh, const void* code, const int32_t* row_expert,
 
 size_t escha_coded_gemv_workspace_bytes(int njobs, int OC, int splits, int rows_per_job) {
     if (njobs < 1 || OC < 128 || rows_per_job < 1) return 0;
-    const size_t counters = align_up(static_cast<size_t>(njobs) * (OC / 128) * sizeof(int32_t), 256);
-    return counters + escha::gemv_mma_part_floats(njobs, splits, OC, rows_per_job) * sizeof(float);
+    if (splits <= 1) return 0;
+    return kCounterBytes + escha::gemv_mma_part_floats(njobs, splits, OC / 128, rows_per_job) * sizeof(float);
 }
 
 int escha_coded_gemv_splits(int IC, int OC, int njobs, int sm_count) {
@@ -224,42 +230,104 @@ int escha_coded_gemv_splits(int IC, int OC, int njobs, int sm_count) {
     return static_cast<int>(s);
 }
 
-int escha_coded_gemv(const void* xh, const void* code, const float* rout, int M, int IC, int OC,
-                     int K, int splits, float rs, void* workspace, size_t workspace_bytes,
-                     void* out, void* stream) {
-    if (int rc = check_shape(__func__, K, IC, OC, 128)) return rc;
+int escha_coded_projections(const void* x, const void* const* x_proj, const void* x_up,
+                            long x_stride, int x_row_div, int input_mode,
+                            int nproj, const void* const* code, const float* const* rin,
+                            const float* const* rout, void* const* out, const int* OC,
+                            const void* jobs, int njobs, int rows_per_job, int M, int E, int IC,
+                            int K, const int* splits, float rs, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+    REQUIRE(nproj >= 1 && nproj <= escha::kMaxProblems, "%s: nproj=%d outside [1, %d]", __func__,
+            nproj, escha::kMaxProblems);
+    REQUIRE(code && rout && out && OC, "%s: NULL projection table", __func__);
+    REQUIRE(input_mode >= 0 && input_mode <= 2, "%s: unknown input mode %d", __func__, input_mode);
     REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
-    REQUIRE_PTR(xh);
-    REQUIRE_PTR(code);
-    REQUIRE_PTR(out);
-    OPTIONAL_PTR(rout);
-    const int rows_per_job = M <= 8 ? 8 : 16;
-    const int njobs = (M + rows_per_job - 1) / rows_per_job;
-    REQUIRE(njobs <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
-    if (splits <= 0) splits = escha_coded_gemv_splits(IC, OC, njobs, 0);
-    REQUIRE(splits <= IC / 128, "%s: splits=%d exceeds the %d input blocks", __func__, splits,
-            IC / 128);
+    REQUIRE(E >= 1, "%s: needs at least one expert stream, got E=%d", __func__, E);
+    REQUIRE_PTR(x);
+    if (input_mode == escha::kInputSwiglu) REQUIRE_PTR(x_up);
+    if (x_stride <= 0) x_stride = IC;
+    REQUIRE(x_stride >= IC && x_stride % 8 == 0, "%s: row stride %ld must be >= IC=%d and a multiple of 8",
+            __func__, x_stride, IC);
     escha::GemvMmaParams p{};
-    p.x = static_cast<const __half*>(xh);
-    p.code = static_cast<const uint32_t*>(code);
-    p.rout = rout;
-    p.jobs = nullptr;
-    p.out = out;
-    p.M = M; p.IC = IC; p.OC = OC; p.K = K;
-    p.splits = splits;
+    int total_ocb = 0;
+    for (int i = 0; i < nproj; ++i) {
+        if (int rc = check_shape(__func__, K, IC, OC[i], 128)) return rc;
+        REQUIRE_PTR(code[i]);
+        REQUIRE_PTR(out[i]);
+        OPTIONAL_PTR(rout[i]);
+        if (input_mode != escha::kInputTransformed) {
+            REQUIRE(rin != nullptr, "%s: a fused input transform needs rin", __func__);
+            REQUIRE_PTR(rin[i]);
+        }
+        p.prob[i].code = static_cast<const uint32_t*>(code[i]);
+        if (x_proj && x_proj[i]) {
+            REQUIRE_PTR(x_proj[i]);
+            p.prob[i].x = static_cast<const __half*>(x_proj[i]);
+        }
+        p.prob[i].rin =input_mode != escha::kInputTransformed ? rin[i] : nullptr;
+        p.prob[i].rout = rout[i];
+        p.prob[i].out = out[i];
+        p.prob[i].OC = OC[i];
+        p.prob[i].ocb0 = total_ocb;
+        total_ocb += OC[i] / 128;
+    }
+    p.nprob = nproj;
+    p.total_ocb = total_ocb;
+    if (jobs) {
+        REQUIRE_PTR(jobs);
+        REQUIRE(rows_per_job == 8 || rows_per_job == 16, "%s: rows per job must be 8 or 16, got %d",
+                __func__, rows_per_job);
+        REQUIRE(njobs >= 1, "%s: njobs=%d", __func__, njobs);
+    } else {
+        rows_per_job = M <= 8 ? 8 : 16;
+        njobs = (M + rows_per_job - 1) / rows_per_job;
+    }
+    REQUIRE(njobs <= 65535, "%s: %d row jobs exceed the launch grid", __func__, njobs);
+    int smax = 1;
+    for (int i = 0; i < nproj; ++i) {
+        int si = splits ? splits[i] : 0;
+        if (si <= 0) {
+            REQUIRE(jobs == nullptr, "%s: with row jobs pass the split factor explicitly", __func__);
+            si = escha_coded_gemv_splits(IC, OC[i], 1, 0);
+        }
+        REQUIRE(si <= IC / 128 && si <= 65535, "%s: splits=%d exceeds the %d input blocks", __func__,
+                si, IC / 128);
+        p.prob[i].splits = si;
+        if (si > smax) smax = si;
+    }
+    p.x = static_cast<const __half*>(x);
+    p.x_up = static_cast<const __half*>(x_up);
+    p.x_stride = x_stride;
+    p.x_row_div = x_row_div < 1 ? 1 : x_row_div;
+    p.jobs = static_cast<const escha::RowJob*>(jobs);
+    p.M = M; p.IC = IC; p.K = K;
+    p.splits = smax;
     p.rows_per_job = rows_per_job;
     p.njobs = njobs;
+    p.input = input_mode;
     p.rs = rs;
-    if (splits > 1) {
-        const size_t need = escha_coded_gemv_workspace_bytes(njobs, OC, splits, rows_per_job);
+    if (smax > 1) {
+        const size_t need =
+            escha_coded_gemv_workspace_bytes(njobs, total_ocb * 128, smax, rows_per_job);
         REQUIRE_PTR(workspace);
         REQUIRE(workspace_bytes >= need, "%s: workspace of %zu bytes is smaller than the %zu needed",
                 __func__, workspace_bytes, need);
-        const size_t counters = align_up(static_cast<size_t>(njobs) * (OC / 128) * sizeof(int32_t), 256);
+        REQUIRE(static_cast<size_t>(njobs) * total_ocb <= kMaxCounters,
+                "%s: %d jobs x %d output blocks exceed the %zu split-K counters", __func__, njobs,
+                total_ocb, kMaxCounters);
         p.counters = static_cast<int32_t*>(workspace);
-        p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters);
+        p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + kCounterBytes);
     }
-    return cuda_result(escha::launch_gemv_mma(p, as_stream(stream)), "escha_coded_gemv");
+    return cuda_result(escha::launch_gemv_mma(p, as_stream(stream)), __func__);
+}
+
+int escha_coded_gemv(const void* xh, const void* code, const float* rout, int M, int IC, int OC,
+                     int K, int splits, float rs, void* workspace, size_t workspace_bytes,
+                     void* out, void* stream) {
+    return escha_coded_projections(xh, nullptr, nullptr, IC, 1, escha::kInputTransformed, 1, &code,
+                                   nullptr,
+                                   &rout, &out, &OC, nullptr, 0, 0, M, 1, IC, K, &splits, rs,
+                                   workspace, workspace_bytes, stream);
 }
 
 int escha_moe_jobs_bound(int m, int E, int R) {
@@ -303,39 +371,12 @@ int escha_coded_gemv_jobs(const void* xh, const void* code, const float* rout, c
                           int njobs, int rows_per_job, int M, int E, int IC, int OC, int K,
                           int splits, float rs, void* workspace, size_t workspace_bytes, void* out,
                           void* stream) {
-    if (int rc = check_shape(__func__, K, IC, OC, 128)) return rc;
-    REQUIRE(M >= 1 && E >= 1, "%s: needs M >= 1 and E >= 1, got M=%d E=%d", __func__, M, E);
-    REQUIRE(njobs >= 1 && njobs <= 65535, "%s: njobs=%d outside [1, 65535]", __func__, njobs);
-    REQUIRE(rows_per_job == 8 || rows_per_job == 16, "%s: rows per job must be 8 or 16, got %d",
-            __func__, rows_per_job);
-    REQUIRE(splits >= 1 && splits <= IC / 128, "%s: splits=%d outside [1, %d]", __func__, splits,
-            IC / 128);
-    REQUIRE_PTR(xh);
-    REQUIRE_PTR(code);
-    REQUIRE_PTR(jobs);
-    REQUIRE_PTR(out);
-    OPTIONAL_PTR(rout);
-    escha::GemvMmaParams p{};
-    p.x = static_cast<const __half*>(xh);
-    p.code = static_cast<const uint32_t*>(code);
-    p.rout = rout;
-    p.jobs = static_cast<const escha::RowJob*>(jobs);
-    p.out = out;
-    p.M = M; p.IC = IC; p.OC = OC; p.K = K;
-    p.splits = splits;
-    p.rows_per_job = rows_per_job;
-    p.njobs = njobs;
-    p.rs = rs;
-    if (splits > 1) {
-        const size_t need = escha_coded_gemv_workspace_bytes(njobs, OC, splits, rows_per_job);
-        REQUIRE_PTR(workspace);
-        REQUIRE(workspace_bytes >= need, "%s: workspace of %zu bytes is smaller than the %zu needed",
-                __func__, workspace_bytes, need);
-        const size_t counters = align_up(static_cast<size_t>(njobs) * (OC / 128) * sizeof(int32_t), 256);
-        p.counters = static_cast<int32_t*>(workspace);
-        p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters);
-    }
-    return cuda_result(escha::launch_gemv_mma(p, as_stream(stream)), "escha_coded_gemv_jobs");
+    REQUIRE(jobs != nullptr, "%s: jobs is NULL", __func__);
+    REQUIRE(splits >= 1, "%s: splits=%d; pass the policy's value explicitly", __func__, splits);
+    return escha_coded_projections(xh, nullptr, nullptr, IC, 1, escha::kInputTransformed, 1, &code,
+                                   nullptr,
+                                   &rout, &out, &OC, jobs, njobs, rows_per_job, M, E, IC, K,
+                                   &splits, rs, workspace, workspace_bytes, stream);
 }
 
 int escha_swiglu(const void* gate, const void* up, int M, int I, long stride, void* h,

@@ -64,17 +64,20 @@ struct LaneK2 {
 };
 
 __device__ __forceinline__ void states_k2(uint32_t w0, uint32_t w1, uint32_t sel, uint32_t s[8]) {
-    uint32_t wv = prmt(w1, w0, sel);
-    uint32_t y1 = wv >> 2, y2 = wv >> 4, y3 = wv >> 6;
-    // state j is the 16-bit window at bit 2*(7-j); byte-aligned after the shifts
-    s[7] = prmt(wv, 0u, 0x4410u);
-    s[3] = prmt(wv, 0u, 0x4421u);
-    s[6] = prmt(y1, 0u, 0x4410u);
-    s[2] = prmt(y1, 0u, 0x4421u);
-    s[5] = prmt(y2, 0u, 0x4410u);
-    s[1] = prmt(y2, 0u, 0x4421u);
-    s[4] = prmt(y3, 0u, 0x4410u);
-    s[0] = prmt(y3, 0u, 0x4421u);
+    const uint32_t wv = prmt(w1, w0, sel);
+    // State j is the 16-bit window of wv at bit 2*(7-j).  Left shifts (which the
+    // compiler can issue on the multiply pipe, leaving the integer pipe to the
+    // byte permutes) bring every window to a byte boundary; the permute then
+    // extracts it zero-extended, so no separate mask is needed.
+    const uint32_t z1 = wv << 2, z2 = wv << 4, z3 = wv << 6;
+    s[7] = prmt(wv, 0u, 0x4410u);   // bit 0
+    s[3] = prmt(wv, 0u, 0x4421u);   // bit 8
+    s[6] = prmt(z3, 0u, 0x4421u);   // bit 2  -> 8
+    s[2] = prmt(z3, 0u, 0x4432u);   // bit 10 -> 16
+    s[5] = prmt(z2, 0u, 0x4421u);   // bit 4  -> 8
+    s[1] = prmt(z2, 0u, 0x4432u);   // bit 12 -> 16
+    s[4] = prmt(z1, 0u, 0x4421u);   // bit 6  -> 8
+    s[0] = prmt(z1, 0u, 0x4432u);   // bit 14 -> 16
 }
 
 struct LaneK3 {
@@ -93,16 +96,18 @@ struct LaneK3 {
 
 __device__ __forceinline__ void states_k3(uint32_t whi, uint32_t wlo, uint32_t sh, uint32_t s[8]) {
     uint64_t merged = (static_cast<uint64_t>(whi) << 32) | static_cast<uint64_t>(wlo);
-    uint32_t w7 = static_cast<uint32_t>(merged >> sh);
-    uint32_t w3 = static_cast<uint32_t>(merged >> (sh + 12u));
-    s[0] = (w3 >> 9) & 0xFFFFu;
-    s[1] = (w3 >> 6) & 0xFFFFu;
-    s[2] = (w3 >> 3) & 0xFFFFu;
-    s[3] = w3 & 0xFFFFu;
-    s[4] = (w7 >> 9) & 0xFFFFu;
-    s[5] = (w7 >> 6) & 0xFFFFu;
-    s[6] = (w7 >> 3) & 0xFFFFu;
-    s[7] = w7 & 0xFFFFu;
+    const uint32_t w7 = static_cast<uint32_t>(merged >> sh);
+    const uint32_t w3 = static_cast<uint32_t>(merged >> (sh + 12u));
+    // windows at bits 9, 6, 3, 0 of each word: left-shift to a byte boundary
+    // (9 -> 16, 6 -> 8, 3 -> 8), then a zero-extending byte permute
+    s[0] = prmt(w3 << 7, 0u, 0x4432u);
+    s[1] = prmt(w3 << 2, 0u, 0x4421u);
+    s[2] = prmt(w3 << 5, 0u, 0x4421u);
+    s[3] = prmt(w3, 0u, 0x4410u);
+    s[4] = prmt(w7 << 7, 0u, 0x4432u);
+    s[5] = prmt(w7 << 2, 0u, 0x4421u);
+    s[6] = prmt(w7 << 5, 0u, 0x4421u);
+    s[7] = prmt(w7, 0u, 0x4410u);
 }
 
 template <int K>

@@ -1,11 +1,14 @@
-// Tensor-core coded GEMV / small-batch GEMM with split-K and a fused output
-// transform.  This is the fast path behind moe_gemv / dense_gemv /
-// dense_gemm_rows[_direct[_out]] / moe_gemm_rows of the reference's kernel layer
-// (escha_mlx/msl.py:1366-1478, :1785-1870): the same product
+// Tensor-core coded GEMV / small-batch GEMM with split-K, optional fused input
+// transform (incl. SwiGLU) and fused output transform, for one or several
+// projections of the same input per launch.  This is the fast path behind
+// moe_gemv / dense_gemv / dense_gemm_rows[_direct[_out]] / dense_gemm_pair[_out] /
+// moe_gemm_rows of the reference's kernel layer (escha_mlx/msl.py:1366-1478,
+// :1785-1950): the same product
 //
 //     mid[r, :] = f32(xh[r, :]) @ f32(decode(code[expert(r)]))
 //
-// optionally followed in the same kernel by  y = f16((H128(mid) * RS) * rout).
+// optionally preceded in the same kernel by  xh = f16(H128(x * rin) * RS)  and
+// followed by  y = f16((H128(mid) * RS) * rout).
 //
 // Why it looks the way it does on B200:
 //  * The reference's lane -> tile-position map (ref.lane_positions) is exactly
@@ -14,17 +17,17 @@
 //    core; the activations are the B operand (up to 8 rows per mma column
 //    block), accumulation is fp32.  No cvt, no FMA chain, no shuffle reduction,
 //    and up to 16 rows share one decode for free.
-//  * Each decoded weight is kept as (w, w) in one register (a single HADD2 of
-//    the hash's two halves with half-select operands) and multiplied against
-//    (x, 0): this trades an idle half of the tensor core for two byte-permute
-//    instructions per weight pair on the integer pipe, which is the pipe that
-//    limits this kernel.
+//  * The kernel is bound by instruction issue, not by HBM: integer-pipe ops
+//    (byte permute, logic) and multiply-pipe ops (IMAD, HADD2) both issue at half
+//    rate on this part, and a decoded weight needs two of each.  So each weight
+//    is kept as (w, w) in one register -- one HADD2 with half-select operands --
+//    and multiplied against (x, 0): that spends an idle half of the tensor core
+//    instead of two more byte permutes per weight pair.
 //  * The code stream is read exactly once, as 16-byte cp.async copies into a
-//    warp-private shared-memory ring (6 stages x 8 tiles per warp); the main
-//    loop has no block-wide barrier except when the activation chunk is
-//    re-staged every 1024 input channels.
+//    warp-private shared-memory ring; the main loop has no block-wide barrier
+//    except when the activation chunk is re-staged every 512 input channels.
 //  * 128 output channels per CTA = one Hadamard block, so the CTA that
-//    completes a block can run the output transform with warp butterflies.
+//    completes a block runs the output transform with warp butterflies.
 //  * Split-K over 128-channel input blocks fills the 148 SMs for any shape.
 //    Partials go to caller-provided scratch; the CTA that arrives last for an
 //    output block sums them in ascending split order (no float atomics), so the
@@ -37,7 +40,7 @@ namespace escha {
 namespace {
 
 constexpr int NS = 6;              // cp.async ring depth (8-kt blocks) per warp
-constexpr int XC = 8;              // 128-channel blocks of activations staged at a time
+constexpr int XC = 4;              // 128-channel blocks of activations staged at a time
 constexpr int XS = XC * 128 + 8;   // words per staged row; +8 keeps LDS.64 conflict-free
 
 template <int K>
@@ -80,44 +83,112 @@ __device__ __forceinline__ void finalize_row(float v[4], uint32_t lane, const fl
     }
 }
 
+__device__ __forceinline__ __half swiglu_half(__half g16, __half u16) {
+    const float g = __half2float(g16);
+    const __half s = __float2half_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))));
+    return __hmul(s, u16);
+}
+
+// Stage `cnt` 128-channel blocks (starting at block blk0) of the job's rows into
+// shared memory as (x, 0) word pairs, applying the input transform when fused.
+__device__ __forceinline__ void stage_activations(const GemvMmaParams& p, const __half* xsrc, const float* rin,
+                                                  const int* s_rows, int nrows, uint32_t blk0,
+                                                  uint32_t cnt, uint32_t* s_x, uint32_t tid) {
+    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    if (p.input == kInputTransformed) {
+        const uint32_t vec_per_row = cnt * 16u;  // 8-half vectors per row
+        const uint32_t total = static_cast<uint32_t>(nrows) * vec_per_row;
+        for (uint32_t idx = tid; idx < total; idx += 256u) {
+            const uint32_t r = idx / vec_per_row, v = idx - r * vec_per_row;
+            const uint4 raw = *reinterpret_cast<const uint4*>(
+                xsrc + static_cast<size_t>(s_rows[r] / p.x_row_div) * p.x_stride + blk0 * 128u +
+                v * 8u);
+            uint4* dst = reinterpret_cast<uint4*>(s_x + r * XS + v * 8u);
+            dst[0] = make_uint4(raw.x & 0xFFFFu, raw.x >> 16, raw.y & 0xFFFFu, raw.y >> 16);
+            dst[1] = make_uint4(raw.z & 0xFFFFu, raw.z >> 16, raw.w & 0xFFFFu, raw.w >> 16);
+        }
+        return;
+    }
+    // fused input transform: one warp per (row, block), butterflies in registers
+    const uint32_t units = static_cast<uint32_t>(nrows) * cnt;
+    for (uint32_t u = warp; u < units; u += 8u) {
+        const uint32_t r = u / cnt, b = u - r * cnt;
+        const size_t xoff = static_cast<size_t>(s_rows[r] / p.x_row_div) * p.x_stride +
+                            (blk0 + b) * 128u + lane * 4u;
+        uint2 raw = *reinterpret_cast<const uint2*>(xsrc + xoff);
+        if (p.input == kInputSwiglu) {
+            const uint2 up = *reinterpret_cast<const uint2*>(p.x_up + xoff);
+            const __half2 g0 = as_half2(raw.x), g1 = as_half2(raw.y);
+            const __half2 u0 = as_half2(up.x), u1 = as_half2(up.y);
+            raw.x = as_u32(__halves2half2(swiglu_half(__low2half(g0), __low2half(u0)),
+                                          swiglu_half(__high2half(g0), __high2half(u0))));
+            raw.y = as_u32(__halves2half2(swiglu_half(__low2half(g1), __low2half(u1)),
+                                          swiglu_half(__high2half(g1), __high2half(u1))));
+        }
+        const float4 sc = *reinterpret_cast<const float4*>(rin + (blk0 + b) * 128u + lane * 4u);
+        const float2 a = __half22float2(as_half2(raw.x)), c = __half22float2(as_half2(raw.y));
+        float v[4] = {__fmul_rn(a.x, sc.x), __fmul_rn(a.y, sc.y), __fmul_rn(c.x, sc.z),
+                      __fmul_rn(c.y, sc.w)};
+        wht128_warp(v, lane);
+        uint4 w;
+        w.x = __half_as_ushort(__float2half_rn(__fmul_rn(v[0], p.rs)));
+        w.y = __half_as_ushort(__float2half_rn(__fmul_rn(v[1], p.rs)));
+        w.z = __half_as_ushort(__float2half_rn(__fmul_rn(v[2], p.rs)));
+        w.w = __half_as_ushort(__float2half_rn(__fmul_rn(v[3], p.rs)));
+        *reinterpret_cast<uint4*>(s_x + r * XS + b * 128u + lane * 4u) = w;
+    }
+}
+
 template <int K, int MT>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, 3)
 gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     constexpr int WPT = 8 * K;
     constexpr int STAGE_WORDS = 8 * WPT;
     constexpr int ROWS = 8 * MT;
     extern __shared__ __align__(16) uint32_t smem[];
     uint32_t* const s_code = smem;                       // [8 warps][NS][STAGE_WORDS]
-    uint32_t* const s_x = smem + 8 * NS * STAGE_WORDS;   // [rows][XS] as (x, 0) pairs
+    uint32_t* const s_x = smem + 8 * NS * STAGE_WORDS;   // [rows + 1][XS] as (x, 0) pairs
     __shared__ int s_rows[16];
     __shared__ int s_last;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint32_t ocb = blockIdx.x, split = blockIdx.y, job = blockIdx.z;
-    const uint32_t TN = p.OC >> 4, OCB = p.OC >> 7, nblk = p.IC >> 7;
+    const uint32_t gocb = blockIdx.x, split = blockIdx.y, job = blockIdx.z;
+    const uint32_t nblk = p.IC >> 7;
 
-    int expert = 0, nrows;
+    // which projection of the launch this output block belongs to (uniform per CTA)
+    int pi = 0;
+#pragma unroll
+    for (int q = 1; q < kMaxProblems; ++q)
+        if (q < p.nprob && gocb >= static_cast<uint32_t>(p.prob[q].ocb0)) pi = q;
+    const GemvProblem& pr = p.prob[pi];
+    const uint32_t ocb = gocb - pr.ocb0;
+    const uint32_t OC = pr.OC, TN = OC >> 4;
+
+    int expert = 0, nrows, xrows;
     if (p.jobs) {
         const RowJob* jb = p.jobs + job;
         expert = jb->expert;
         nrows = jb->nrows;
+        xrows = ROWS;
         if (tid < 16) s_rows[tid] = jb->rows[tid];
     } else {
         const int r0 = static_cast<int>(job) * ROWS;
         nrows = min(ROWS, p.M - r0);
+        xrows = min(ROWS, p.M);
         if (tid < 16) s_rows[tid] = r0 + static_cast<int>(tid);
     }
-    if (nrows <= 0) return;  // uniform for the CTA
+    // this CTA's range of 128-channel input blocks; projections of one launch may
+    // use different split factors (each keeps the factor it has when launched alone)
+    const uint32_t S = pr.splits, SMAX = p.splits;
+    if (nrows <= 0 || split >= S) return;  // uniform for the CTA
 
-    // this CTA's range of 128-channel input blocks
-    const uint32_t S = p.splits;
     const uint32_t bbase = nblk / S, brem = nblk % S;
     const uint32_t b0 = split * bbase + min(split, brem);
     const uint32_t nb = bbase + (split < brem ? 1u : 0u);
 
     const uint32_t tile_row_words = TN * WPT;  // words between kt and kt+1 of one tile column
-    const uint32_t* gtile = p.code + static_cast<size_t>(expert) * (p.IC >> 4) * tile_row_words +
+    const uint32_t* gtile = pr.code + static_cast<size_t>(expert) * (p.IC >> 4) * tile_row_words +
                             (ocb * 8u + warp) * WPT;
     uint32_t* const my_stages = s_code + warp * (NS * STAGE_WORDS);
     const CodeFetch<K> fetch(lane, tile_row_words);
@@ -132,36 +203,33 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
         cp_async_commit();
     }
 
-    float d[MT][4];
+    // zero row: B columns past the job's last row read it instead of branching
+    uint32_t* const zero_row = s_x + static_cast<uint32_t>(xrows) * XS;
+    for (uint32_t i = tid; i < static_cast<uint32_t>(XS); i += 256u) zero_row[i] = 0u;
+
+    // two independent accumulator sets per column block: the two mma of a tile
+    // do not wait on each other, and each chain advances once per tile
+    float dA[MT][4], dB[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) d[mt][i] = 0.0f;
+        for (int i = 0; i < 4; ++i) dA[mt][i] = dB[mt][i] = 0.0f;
 
-    bool row_ok[MT];
     const uint32_t* xrow[MT];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-        row_ok[mt] = static_cast<int>(g) + 8 * mt < nrows;
-        xrow[mt] = s_x + (g + 8u * mt) * XS + 2u * t;
+        const int slot = static_cast<int>(g) + 8 * mt;
+        xrow[mt] = (slot < nrows ? s_x + slot * XS : zero_row) + 2u * t;
     }
+    const float* rin = pr.rin ? pr.rin + static_cast<size_t>(expert) * p.IC : nullptr;
+    const __half* xsrc = pr.x ? pr.x : p.x;
 
     for (uint32_t i = 0; i < nb; ++i) {
         const uint32_t cblk = i % XC;
         if (cblk == 0) {
-            // (re)stage activations for blocks [b0+i, b0+i+cnt) as (x, 0) word pairs
             __syncthreads();
-            const uint32_t cnt = min(static_cast<uint32_t>(XC), nb - i);
-            const uint32_t vec_per_row = cnt * 16u;  // 8-half vectors per row
-            const uint32_t total = static_cast<uint32_t>(nrows) * vec_per_row;
-            for (uint32_t idx = tid; idx < total; idx += 256u) {
-                const uint32_t r = idx / vec_per_row, v = idx - r * vec_per_row;
-                const uint4 raw = *reinterpret_cast<const uint4*>(
-                    p.x + static_cast<size_t>(s_rows[r]) * p.IC + (b0 + i) * 128u + v * 8u);
-                uint4* dst = reinterpret_cast<uint4*>(s_x + r * XS + v * 8u);
-                dst[0] = make_uint4(raw.x & 0xFFFFu, raw.x >> 16, raw.y & 0xFFFFu, raw.y >> 16);
-                dst[1] = make_uint4(raw.z & 0xFFFFu, raw.z >> 16, raw.w & 0xFFFFu, raw.w >> 16);
-            }
+            stage_activations(p, xsrc, rin, s_rows, nrows, b0 + i, min(static_cast<uint32_t>(XC), nb - i),
+                              s_x, tid);
             __syncthreads();
         }
         cp_async_wait<NS - 2>();
@@ -174,24 +242,22 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
             cp_async_commit();
         }
         const uint32_t* stage = my_stages + (i % NS) * STAGE_WORDS;
-#pragma unroll
+        const uint32_t kbase = cblk * 128u;
+#pragma unroll 2
         for (int kk = 0; kk < 8; ++kk) {
             const uint32_t* tw = stage + kk * WPT;
             uint32_t s[8], a[8];
             lc.states(tw[lc.ia()], tw[lc.ib()], s);
 #pragma unroll
             for (int j = 0; j < 8; ++j) a[j] = cba_decode_dup(s[j]);
-            const uint32_t koff = (cblk * 8u + kk) * 16u;
+            const uint32_t koff = kbase + kk * 16u;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                uint2 b01 = make_uint2(0u, 0u), b23 = make_uint2(0u, 0u);
-                if (row_ok[mt]) {
-                    b01 = *reinterpret_cast<const uint2*>(xrow[mt] + koff);
-                    b23 = *reinterpret_cast<const uint2*>(xrow[mt] + koff + 8u);
-                }
+                const uint2 b01 = *reinterpret_cast<const uint2*>(xrow[mt] + koff);
+                const uint2 b23 = *reinterpret_cast<const uint2*>(xrow[mt] + koff + 8u);
                 // value j sits at (channel g + 8*(j>=4), input 2t + (j&1) + 8*((j>>1)&1))
-                mma16816(d[mt], a[0], a[4], a[2], a[6], b01.x, b23.x);
-                mma16816(d[mt], a[1], a[5], a[3], a[7], b01.y, b23.y);
+                mma16816(dA[mt], a[0], a[4], a[2], a[6], b01.x, b23.x);
+                mma16816(dB[mt], a[1], a[5], a[3], a[7], b01.y, b23.y);
             }
         }
     }
@@ -203,38 +269,39 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         const uint32_t ch = warp * 16u + g, n0 = 2u * t + 8u * mt;
-        s_acc[n0 * 128u + ch] = d[mt][0];
-        s_acc[(n0 + 1u) * 128u + ch] = d[mt][1];
-        s_acc[n0 * 128u + ch + 8u] = d[mt][2];
-        s_acc[(n0 + 1u) * 128u + ch + 8u] = d[mt][3];
+        s_acc[n0 * 128u + ch] = __fadd_rn(dA[mt][0], dB[mt][0]);
+        s_acc[(n0 + 1u) * 128u + ch] = __fadd_rn(dA[mt][1], dB[mt][1]);
+        s_acc[n0 * 128u + ch + 8u] = __fadd_rn(dA[mt][2], dB[mt][2]);
+        s_acc[(n0 + 1u) * 128u + ch + 8u] = __fadd_rn(dA[mt][3], dB[mt][3]);
     }
     __syncthreads();
 
     const float* rout_blk =
-        p.rout ? p.rout + static_cast<size_t>(expert) * p.OC + ocb * 128u : nullptr;
+        pr.rout ? pr.rout + static_cast<size_t>(expert) * OC + ocb * 128u : nullptr;
 
     if (S == 1) {
         for (uint32_t r = warp; r < static_cast<uint32_t>(nrows); r += 8u) {
             const float4 a4 = *reinterpret_cast<const float4*>(s_acc + r * 128u + lane * 4u);
             float v[4] = {a4.x, a4.y, a4.z, a4.w};
-            const size_t off = static_cast<size_t>(s_rows[r]) * p.OC + ocb * 128u + lane * 4u;
-            if (p.rout) finalize_row<true>(v, lane, rout_blk, p.out, off, p.rs);
-            else finalize_row<false>(v, lane, rout_blk, p.out, off, p.rs);
+            const size_t off = static_cast<size_t>(s_rows[r]) * OC + ocb * 128u + lane * 4u;
+            if (pr.rout) finalize_row<true>(v, lane, rout_blk, pr.out, off, p.rs);
+            else finalize_row<false>(v, lane, rout_blk, pr.out, off, p.rs);
         }
         return;
     }
 
     // split-K: publish this CTA's partial, last arriver reduces in split order
     const size_t unit_floats = static_cast<size_t>(ROWS) * 128u;
+    const size_t nocb = static_cast<size_t>(p.total_ocb);
     float* const my_part =
-        p.part + ((static_cast<size_t>(job) * S + split) * OCB + ocb) * unit_floats;
+        p.part + ((static_cast<size_t>(job) * SMAX + split) * nocb + gocb) * unit_floats;
     for (uint32_t r = warp; r < static_cast<uint32_t>(nrows); r += 8u)
         __stcg(reinterpret_cast<float4*>(my_part + r * 128u + lane * 4u),
                *reinterpret_cast<const float4*>(s_acc + r * 128u + lane * 4u));
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        int32_t* ctr = p.counters + static_cast<size_t>(job) * OCB + ocb;
+        int32_t* ctr = p.counters + static_cast<size_t>(job) * nocb + gocb;
         const int prev = atomicAdd(ctr, 1);
         const int last = prev == static_cast<int>(S) - 1;
         if (last) *ctr = 0;  // every split has arrived: leave the counter clean for the next launch
@@ -243,28 +310,30 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    const float* const part0 = p.part + (static_cast<size_t>(job) * S * OCB + ocb) * unit_floats;
+    const float* const part0 =
+        p.part + (static_cast<size_t>(job) * SMAX * nocb + gocb) * unit_floats;
     for (uint32_t r = warp; r < static_cast<uint32_t>(nrows); r += 8u) {
         float v[4];
         for (uint32_t s = 0; s < S; ++s) {
             const float4 q = __ldcg(reinterpret_cast<const float4*>(
-                part0 + static_cast<size_t>(s) * OCB * unit_floats + r * 128u + lane * 4u));
+                part0 + static_cast<size_t>(s) * nocb * unit_floats + r * 128u + lane * 4u));
             if (s == 0) { v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
             else {
                 v[0] = __fadd_rn(v[0], q.x); v[1] = __fadd_rn(v[1], q.y);
                 v[2] = __fadd_rn(v[2], q.z); v[3] = __fadd_rn(v[3], q.w);
             }
         }
-        const size_t off = static_cast<size_t>(s_rows[r]) * p.OC + ocb * 128u + lane * 4u;
-        if (p.rout) finalize_row<true>(v, lane, rout_blk, p.out, off, p.rs);
-        else finalize_row<false>(v, lane, rout_blk, p.out, off, p.rs);
+        const size_t off = static_cast<size_t>(s_rows[r]) * OC + ocb * 128u + lane * 4u;
+        if (pr.rout) finalize_row<true>(v, lane, rout_blk, pr.out, off, p.rs);
+        else finalize_row<false>(v, lane, rout_blk, pr.out, off, p.rs);
     }
 }
 
 template <int K, int MT>
 cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
     constexpr int STAGE_WORDS = 8 * 8 * K;
-    const size_t smem = (static_cast<size_t>(8 * NS * STAGE_WORDS) + static_cast<size_t>(xrows) * XS) * 4u;
+    const size_t smem =
+        (static_cast<size_t>(8 * NS * STAGE_WORDS) + static_cast<size_t>(xrows + 1) * XS) * 4u;
     static size_t configured[64] = {0};  // per device: largest size already enabled
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -276,16 +345,16 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    dim3 grid(p.OC / 128, p.splits, p.njobs), block(256);
+    dim3 grid(p.total_ocb, p.splits, p.njobs), block(256);
     gemv_mma_kernel<K, MT><<<grid, block, smem, st>>>(p);
     return cudaGetLastError();
 }
 
 }  // namespace
 
-size_t gemv_mma_part_floats(int njobs, int splits, int OC, int rows_per_job) {
+size_t gemv_mma_part_floats(int njobs, int splits, int total_ocb, int rows_per_job) {
     if (splits <= 1) return 0;
-    return static_cast<size_t>(njobs) * splits * (OC / 128) * rows_per_job * 128u;
+    return static_cast<size_t>(njobs) * splits * total_ocb * rows_per_job * 128u;
 }
 
 cudaError_t launch_gemv_mma(const GemvMmaParams& p, cudaStream_t st) {

@@ -16,18 +16,45 @@ struct RowJob {
     int32_t rows[16];
 };
 
+constexpr int kMaxProblems = 4;
+
+// One projection inside a (possibly multi-projection) launch.  All projections
+// of a launch share the input rows, IC and K; each has its own stream, vectors
+// and output.
+struct GemvProblem {
+    const uint32_t* code;   // [E?, TK, TN, 8K]
+    const __half* x;        // this projection's own input rows, or nullptr for the shared ones
+    const float* rin;      // [E?, IC]; read only when the input transform is fused
+    const float* rout;      // nullptr -> write f32 mid; else [E?, OC] and write f16 y
+    void* out;              // f32 [M, OC] or f16 [M, OC]
+    int OC;
+    int ocb0;               // index of this projection's first 128-channel block in the grid
+    int splits;             // split-K factor of this projection (<= GemvMmaParams::splits)
+};
+
+enum GemvInput : int {
+    kInputTransformed = 0,  // x is xh = f16(H128(x * rin) * RS), ready for the product
+    kInputRaw = 1,          // x is the raw f16 activation; the kernel applies rin, H128, RS
+    kInputSwiglu = 2,       // raw input is f16(f16(silu(x)) * x_up); then as kInputRaw
+};
+
 struct GemvMmaParams {
-    const __half* x;          // [*, IC] f16: transformed rows xh
-    const uint32_t* code;     // [E?, TK, TN, 8K]
-    const float* rout;        // nullptr -> write f32 mid; else [E?, OC] and write f16 y
+    GemvProblem prob[kMaxProblems];
+    int nprob;
+    int total_ocb;            // grid.x
+    const __half* x;          // [*, x_stride]
+    const __half* x_up;       // second operand for kInputSwiglu
+    long x_stride;            // elements between consecutive rows of x / x_up
+    int x_row_div;            // output row r reads input row r / x_row_div (top_k for the
+                              // first expert leg, where rows are (token, slot) pairs); >= 1
     const RowJob* jobs;       // nullptr -> dense implicit jobs
-    void* out;                // f32 [M, OC] or f16 [M, OC]
     float* part;              // split-K partials (unused when splits == 1)
     int32_t* counters;        // one per (job, output block); zero on entry, zero on exit
-    int M, IC, OC, K;
-    int splits;               // >= 1
+    int M, IC, K;
+    int splits;               // grid.y: the largest per-projection split factor
     int rows_per_job;         // 8 or 16
     int njobs;                // grid.z
+    int input;                // GemvInput
     float rs;
 };
 
@@ -55,6 +82,6 @@ cudaError_t launch_moe_combine(const __half* d16, const float* scores, int T, in
 cudaError_t launch_had128(const float* x, float* out, long nblocks, cudaStream_t st);
 cudaError_t launch_w8a16(const __half* x, const int8_t* w8, const __half* scale, __half* y, int M,
                          int N, int Kd, cudaStream_t st);
-size_t gemv_mma_part_floats(int njobs, int splits, int OC, int rows_per_job);
+size_t gemv_mma_part_floats(int njobs, int splits, int total_ocb, int rows_per_job);
 
 }  // namespace escha

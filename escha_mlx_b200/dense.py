@@ -202,6 +202,12 @@ class EschaLinear(torch.nn.Module):
         if rows.dtype != torch.float16:
             rows = rows.to(torch.float16)
         rows = rows.contiguous()
+        if self._single_launch(rows.shape[0]):
+            # input transform, product and output transform in one kernel
+            w = self._w
+            y = msl.coded_projections(rows, [w.code], [w.rin], [w.rout], w.K, w.IC, [w.OC],
+                                      input_mode=msl.INPUT_RAW, rs=RS)[0]
+            return self._finish(y, shape, x.dtype)
         xh = self._input_rows(rows)
         if self._fused_had:
             y = msl.dense_gemm_rows_direct_out(
@@ -209,37 +215,79 @@ class EschaLinear(torch.nn.Module):
                 msl.dense_block_r(rows.shape[0], self._block_r_pin), RS)
         else:
             y = self._output_rows(self._gemv(xh))
+        return self._finish(y, shape, x.dtype)
+
+    def _single_launch(self, m: int) -> bool:
+        """Whether a forward over m rows runs as one fused kernel (small decode
+        batches on the tensor-core family with fused transforms)."""
+        return (self._fused_had and msl.gemv_family() == "mma"
+                and m <= msl.FUSE_INPUT_MAX_ROWS)
+
+    def _finish(self, y: torch.Tensor, shape, dtype) -> torch.Tensor:
         if self.bias is not None:
             # the transform output is rounded to f16 before the correction is added
             y = (y.float() + self.bias.float()).to(torch.float16)
-        return y.reshape(*shape[:-1], self._w.OC).to(x.dtype)
+        return y.reshape(*shape[:-1], self._w.OC).to(dtype)
+
+
+def project_many(linears, x: torch.Tensor):
+    """Evaluate up to four coded projections of the same input (Q/K/V, gate/up) in
+    as few launches as their rates allow.  Outputs equal ``[lin(x) for lin in
+    linears]`` bit for bit: every projection keeps the split factor and the
+    summation order it has when called alone."""
+    linears = list(linears)
+    shape = x.shape
+    rows = x.reshape(-1, shape[-1])
+    first = linears[0]
+    joint = (
+        1 < len(linears) <= 4
+        and msl.gemv_family() == "mma"
+        and all(lin._fused_had for lin in linears)
+        and all(lin._w.IC == rows.shape[-1] and lin.K == first.K for lin in linears)
+        and rows.dtype == torch.float16
+    )
+    if not joint:
+        return [lin(x) for lin in linears]
+    rows = rows.contiguous()
+    ws = [lin._w for lin in linears]
+    codes, routs, ocs = [w.code for w in ws], [w.rout for w in ws], [w.OC for w in ws]
+    if first._single_launch(rows.shape[0]):
+        outs = msl.coded_projections(rows, codes, [w.rin for w in ws], routs, first.K, first._w.IC,
+                                     ocs, input_mode=msl.INPUT_RAW, rs=RS)
+    else:
+        xhs = [lin._input_rows(rows) for lin in linears] if len(linears) != 2 else list(
+            msl.dense_scaled_had_pair(rows, ws[0].rin, ws[1].rin, RS))
+        outs = msl.coded_projections(xhs[0], codes, None, routs, first.K, first._w.IC, ocs,
+                                     rs=RS, xs=xhs)
+    return [lin._finish(y, shape, x.dtype) for lin, y in zip(linears, outs)]
 
 
 def project_pair(first: EschaLinear, second: EschaLinear, x: torch.Tensor):
-    """Evaluate two coded projections of the same input (gate/up, K/V) with the
-    paired launches (:365-437).  Outputs equal ``first(x), second(x)`` bit for bit."""
-    shape = x.shape
-    rows = x.reshape(-1, shape[-1])
-    compatible = (
-        first._w.IC == second._w.IC == rows.shape[-1]
-        and first._fused_had and second._fused_had
-        and rows.dtype == torch.float16
-    )
-    if not compatible:
-        return first(x), second(x)
-    rows = rows.contiguous()
-    r = msl.dense_block_r(rows.shape[0], first._block_r_pin)
-    xh0, xh1 = msl.dense_scaled_had_pair(rows, first._w.rin, second._w.rin, RS)
-    out0, out1 = msl.dense_gemm_pair_out(
-        xh0, xh1, first._w.code, second._w.code, first._w.rout, second._w.rout,
-        first.K, second.K, first._w.IC, first._w.OC, second._w.OC, r, RS)
+    """Evaluate two coded projections of the same input (gate/up, K/V) with one
+    GEMM dispatch (:365-437).  Outputs equal ``first(x), second(x)`` bit for bit;
+    a mixed-rate pair falls back to two calls."""
+    a, b = project_many([first, second], x)
+    return a, b
 
-    def finish(linear, value):
-        if linear.bias is not None:
-            value = (value.float() + linear.bias.float()).to(torch.float16)
-        return value.reshape(*shape[:-1], linear._w.OC).to(x.dtype)
 
-    return finish(first, out0), finish(second, out1)
+def swiglu_project(down: EschaLinear, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``down(f16(f16(silu(gate)) * up))`` -- the tail of a SwiGLU MLP.  For small
+    decode batches the activation, the input transform, the product and the
+    output transform run as one kernel; the result equals the unfused chain bit
+    for bit."""
+    shape = gate.shape
+    g = gate.reshape(-1, shape[-1]).contiguous()
+    u = up.reshape(-1, shape[-1]).contiguous()
+    if g.shape != u.shape or g.shape[-1] != down._w.IC:
+        raise ValueError(f"gate/up of shape {tuple(gate.shape)}/{tuple(up.shape)} do not feed a "
+                         f"{down._w.IC}-channel projection")
+    if down._single_launch(g.shape[0]) and g.dtype == torch.float16 and u.dtype == torch.float16:
+        w = down._w
+        y = msl.coded_projections(g, [w.code], [w.rin], [w.rout], w.K, w.IC, [w.OC],
+                                  input_mode=msl.INPUT_SWIGLU, x_up=u, rs=RS)[0]
+        return down._finish(y, shape, gate.dtype)
+    h = msl.swiglu_pair(g.to(torch.float16), u.to(torch.float16))
+    return down(h.reshape(*shape[:-1], down._w.IC).to(gate.dtype))
 
 
 def build(group: dict, device=None) -> EschaLinear:

@@ -118,7 +118,7 @@ class EschaSparseMoeBlock(torch.nn.Module):
     def _expert_path(self, xf: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
         t = xf.shape[0]
         row_expert, row_token = self._rows(xf, ids)
-        rows = xf[row_token.long()]
+        m = row_expert.shape[0]
         owned = None
         job_expert = row_expert
         if self._sharded():
@@ -129,10 +129,28 @@ class EschaSparseMoeBlock(torch.nn.Module):
             local = row_expert - self._e_lo
             job_expert = torch.where(owned, local, torch.full_like(local, -1))
             row_expert = torch.where(owned, local, torch.zeros_like(local))
-        jobs = msl.group_rows(job_expert, self._gu.E) if msl.gemv_family() == "mma" else None
-        gu16 = self._leg(rows, row_expert, self._gu, jobs)
-        h = msl.swiglu(gu16)
-        d16 = self._leg(h, row_expert, self._dn, jobs)
+        gu, dn = self._gu, self._dn
+        if msl.gemv_family() == "mma" and self._fused_had:
+            # two launches: each leg's input transform (with the token gather, resp.
+            # the SwiGLU), product and output transform in one kernel
+            jobs = msl.group_rows(job_expert, gu.E)
+            zeros = (lambda oc: [torch.zeros((m, oc), dtype=torch.float16, device=xf.device)]) \
+                if owned is not None else (lambda oc: None)
+            gu16 = msl.coded_projections(xf, [gu.code], [gu.rin], [gu.rout], gu.K, gu.IC, [gu.OC],
+                                         input_mode=msl.INPUT_RAW, jobs=jobs, E=gu.E, rows=m,
+                                         x_stride=gu.IC, x_row_div=self.top_k,
+                                         outs=zeros(gu.OC))[0]
+            inter = self._inter
+            d16 = msl.coded_projections(gu16[:, :inter], [dn.code], [dn.rin], [dn.rout], dn.K,
+                                        dn.IC, [dn.OC], input_mode=msl.INPUT_SWIGLU,
+                                        x_up=gu16[:, inter:], jobs=jobs, E=dn.E, rows=m,
+                                        x_stride=2 * inter, outs=zeros(dn.OC))[0]
+        else:
+            jobs = msl.group_rows(job_expert, gu.E) if msl.gemv_family() == "mma" else None
+            rows = xf[row_token.long()]
+            gu16 = self._leg(rows, row_expert, gu, jobs)
+            h = msl.swiglu(gu16)
+            d16 = self._leg(h, row_expert, dn, jobs)
         if owned is not None:
             d16 = sharding.all_gather_rows_by_owner(d16, owned)
         y16 = msl.moe_combine(d16, scores.reshape(t * self.top_k).to(torch.float32).contiguous(),

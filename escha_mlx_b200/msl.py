@@ -282,6 +282,87 @@ def _gemv_mma_dense(xh, code, rout, K, IC, OC, splits, rs=RS):
     return out
 
 
+INPUT_TRANSFORMED, INPUT_RAW, INPUT_SWIGLU = 0, 1, 2
+
+#: Up to this many rows the dense modules fuse the input transform into the GEMV
+#: launch (every output block's CTA redoes it for its slice of the input, which is
+#: noise at decode batch sizes and a real cost beyond them).
+FUSE_INPUT_MAX_ROWS = 4
+
+
+def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
+                      input_mode: int = INPUT_TRANSFORMED, x_up: torch.Tensor | None = None,
+                      jobs: torch.Tensor | None = None, E: int = 1, splits: int | None = None,
+                      rs: float = RS, rows_per_job: int = 8, outs=None,
+                      policy_rows: int | None = None, xs=None, rows: int | None = None,
+                      x_stride: int | None = None, x_row_div: int = 1):
+    """One launch of the tensor-core kernel for 1..4 projections of the same rows.
+
+    ``codes``/``rins``/``routs``/``OCs`` are equal-length sequences (rins may be
+    None for ``INPUT_TRANSFORMED``; a rout of None yields that projection's f32
+    mid instead of its f16 output).  ``input_mode`` selects what ``x`` is: the
+    transformed rows, the raw activation (input transform fused), or the gate
+    half of a SwiGLU whose up half is ``x_up``.  Returns the list of outputs.
+    Bit-identical to running the stages as separate launches.
+
+    ``rows`` (default: the rows of ``x``) is the number of output rows; output row
+    r reads input row ``r // x_row_div`` at ``x_stride`` elements per row, which
+    lets the first expert leg read token rows directly and the second read the
+    gate/up halves of one merged tensor.
+    """
+    n = len(codes)
+    m = x.shape[0] if rows is None else rows
+    if rins is None:
+        rins = [None] * n
+    dense = jobs is None
+    pr = m if policy_rows is None else policy_rows
+    total_oc = sum(OCs)
+    # every projection keeps the split factor it has when launched alone, so a
+    # joint launch changes no output bit
+    if splits is None:
+        est = 1 if dense else expected_jobs(pr, E)
+        per = [split_k_for(pr, oc, IC // 16, est) for oc in OCs]
+    else:
+        per = [max(1, min(int(splits), IC // 128))] * n
+    s = max(per)
+    if dense:
+        rows_per_job = 8 if m <= 8 else 16
+        njobs = (m + rows_per_job - 1) // rows_per_job
+    else:
+        njobs = jobs.shape[0]
+    if outs is None:
+        outs = [torch.empty((m, oc), dtype=torch.float32 if ro is None else torch.float16,
+                            device=x.device) for oc, ro in zip(OCs, routs)]
+    ws, nbytes = None, 0
+    if s > 1:
+        nbytes = int(lib.escha_coded_gemv_workspace_bytes(njobs, total_oc, s, rows_per_job))
+        ws = workspaces.get(nbytes, x.device)
+        nbytes = ws.numel()
+    vp = ctypes.c_void_p * n
+
+    def table(ts, dtype=None):
+        return vp(*[None if t is None else ptr(t, dtype).value for t in ts])
+
+    for c in codes:
+        _check_code(c)
+    if x.dtype != torch.float16 or not x.is_cuda:
+        raise ValueError("coded_projections takes a CUDA float16 activation tensor")
+    # x / x_up may be column slices of one row-major tensor (merged gate/up)
+    x_ptr = ctypes.c_void_p(x.data_ptr())
+    up_ptr = None if x_up is None else ctypes.c_void_p(x_up.data_ptr())
+    if x_stride is None:
+        x_stride = IC if x.shape[0] == 1 else x.stride(0)
+    if x.stride(-1) != 1 or (x_up is not None and x_up.stride(-1) != 1):
+        raise ValueError("activation rows must be contiguous along the channel axis")
+    check(lib.escha_coded_projections(
+        x_ptr, None if xs is None else table(xs, torch.float16), up_ptr,
+        x_stride, x_row_div, input_mode, n, table(codes), table(rins, torch.float32),
+        table(routs, torch.float32), table(outs), (ctypes.c_int * n)(*OCs),
+        None if dense else ptr(jobs, torch.int32), njobs, rows_per_job, m, E, IC, K,
+        (ctypes.c_int * n)(*per), float(rs), ptr(ws), ctypes.c_size_t(nbytes), stream()))
+    return outs
+
+
 def coded_gemv_jobs(xh: torch.Tensor, code_u32: torch.Tensor, jobs: torch.Tensor,
                     rout: torch.Tensor | None, K: int, IC: int, OC: int, E: int,
                     splits: int | None = None, rs: float = RS, rows_per_job: int = 8,
@@ -380,6 +461,9 @@ def dense_gemm_pair(xh0, xh1, code0, code1, K0: int, K1: int, IC: int, OC0: int,
     """Two coded projections with the same input geometry (:1909-1950)."""
     if xh0.shape != xh1.shape or xh0.shape[0] < 1:
         raise ValueError("dense_gemm_pair requires matching non-empty input rows")
+    if K0 == K1 and gemv_family() == "mma":   # one launch; a mixed-rate pair takes two
+        return tuple(coded_projections(xh0, [code0, code1], None, [None, None], K0, IC,
+                                       [OC0, OC1], xs=[xh0, xh1]))
     return (dense_gemv(xh0, code0, K0, IC, OC0), dense_gemv(xh1, code1, K1, IC, OC1))
 
 
@@ -388,6 +472,9 @@ def dense_gemm_pair_out(xh0, xh1, code0, code1, rout0, rout1, K0: int, K1: int, 
     """Mixed-K projection pair with both output transforms fused (:1873-1906)."""
     if xh0.shape != xh1.shape or xh0.shape[0] < 1:
         raise ValueError("dense_gemm_pair_out requires matching non-empty input rows")
+    if K0 == K1 and gemv_family() == "mma":
+        return tuple(coded_projections(xh0, [code0, code1], None, [rout0, rout1], K0, IC,
+                                       [OC0, OC1], rs=rs, xs=[xh0, xh1]))
     return (dense_gemm_rows_direct_out(xh0, code0, rout0, K0, IC, OC0, R, rs),
             dense_gemm_rows_direct_out(xh1, code1, rout1, K1, IC, OC1, R, rs))
 

@@ -107,10 +107,12 @@ int escha_gemv_ref(const void *xh, const void *code, const int32_t *row_expert,
                    const int32_t *row_map, int slots, const void *lut, int M, int IC, int OC,
                    int K, int splits, float *part, float *mid, void *stream);
 
-/* Workspace the tensor-core GEMV needs for a given launch shape, in bytes
- * (counters + split-K partials).  The caller allocates it once, zero-filled;
- * every launch leaves the counter region zero again.  njobs = number of row
- * groups (escha_coded_gemv: (M + rows_per_job - 1) / rows_per_job). */
+/* Workspace the tensor-core GEMV needs for a given launch shape, in bytes: a
+ * fixed 1 MiB counter region followed by the split-K partials (0 when
+ * splits <= 1).  The caller allocates it once, zero-filled; every launch leaves
+ * the counter region zero again, so one workspace serves launches of any shape
+ * as long as they do not overlap on the GPU.  njobs = number of row groups
+ * (escha_coded_gemv: (M + rows_per_job - 1) / rows_per_job). */
 size_t escha_coded_gemv_workspace_bytes(int njobs, int OC, int splits, int rows_per_job);
 
 /* Split policy: how many ways the kernel splits the input dimension so that the
@@ -131,6 +133,42 @@ int escha_coded_gemv_splits(int IC, int OC, int njobs, int sm_count);
 int escha_coded_gemv(const void *xh, const void *code, const float *rout, int M, int IC, int OC,
                      int K, int splits, float rs, void *workspace, size_t workspace_bytes,
                      void *out, void *stream);
+
+/* General form of the tensor-core kernel: nproj (1..4) projections of the SAME
+ * rows in one launch, with the transforms around the product optionally fused.
+ * Replaces, per launch, one of the reference's pair/fused dispatches:
+ * msl.dense_gemm_pair[_out] (msl.py:1873-1950) for gate/up and K/V, preceded by
+ * msl.dense_scaled_had[_pair] (msl.py:1481-1504) when the input transform is
+ * fused, and the SwiGLU stage (models/qwen3_5_moe.py:221-223) for a down
+ * projection.  Every fusion is bit-identical to running the stages separately.
+ *   input_mode 0: x is xh, already transformed.
+ *              1: x is the raw binary16 activation; the kernel computes
+ *                 xh = f16(H128(x * rin[i]) * rs) per projection i.
+ *              2: as 1 on h = f16(f16(silu(x)) * x_up)  (x = gate, x_up = up).
+ *   x_proj: NULL, or a host array of nproj row pointers: a non-NULL entry gives
+ *     that projection its own input rows (mode 0: each projection has its own
+ *     xh because each has its own rin); NULL entries use x.
+ *   x_stride: elements between rows of x (and x_up); <= 0 means IC.
+ *   x_row_div: output row r reads input row r / x_row_div (<= 1: the same row).
+ *     With (token, slot) rows laid out token-major, top_k here replaces the
+ *     xf[row_token] gather of models/qwen3_5_moe.py:112-114.
+ *   code/rin/rout/out/OC: host arrays of nproj entries.  rin[i] is [IC] (or
+ *     [E,IC] with jobs) and only read for input_mode != 0; rout[i] NULL makes
+ *     out[i] f32 mid [M,OC[i]], otherwise out[i] is binary16 [M,OC[i]].
+ *   jobs NULL: dense streams, rows 0..M-1 (njobs/rows_per_job/E ignored).
+ *   jobs given: E-stacked streams indexed by each job's expert.
+ *   splits: host array of nproj split factors (NULL or an entry <= 0 selects
+ *     escha_coded_gemv_splits(IC, OC[i], 1)); each projection keeps the factor
+ *     it has when launched alone, so a joint launch changes no output bit.
+ *   workspace: escha_coded_gemv_workspace_bytes(njobs, sum(OC), max(splits),
+ *     rows_per_job). */
+int escha_coded_projections(const void *x, const void *const *x_proj, const void *x_up,
+                            long x_stride, int x_row_div, int input_mode,
+                            int nproj, const void *const *code, const float *const *rin,
+                            const float *const *rout, void *const *out, const int *OC,
+                            const void *jobs, int njobs, int rows_per_job, int M, int E, int IC,
+                            int K, const int *splits, float rs, void *workspace,
+                            size_t workspace_bytes, void *stream);
 
 /* ---- routed experts (E-stacked streams) ---------------------------------- */
 

@@ -67,5 +67,5 @@ def test_pure_helpers():
     assert lib.escha_coded_gemv_splits(4096, 4096, 1, 148) == 10
     # never fewer than two 128-channel blocks per split
     assert lib.escha_coded_gemv_splits(512, 128, 1, 148) == 2
-    assert lib.escha_coded_gemv_workspace_bytes(1, 4096, 1, 8) == 256
-    assert lib.escha_coded_gemv_workspace_bytes(1, 4096, 4, 8) == 256 + 4 * 32 * 8 * 128 * 4
+    assert lib.escha_coded_gemv_workspace_bytes(1, 4096, 1, 8) == 0
+    assert lib.escha_coded_gemv_workspace_bytes(1, 4096, 4, 8) == (1 << 20) + 4 * 32 * 8 * 128 * 4

@@ -307,3 +307,59 @@ def test_full_size_projection_properties(cuda, monkeypatch, name, IC, OC, K):
     kt = (IC // 16) // 2
     band = msl.decode_tiles(c[kt:kt + 1].contiguous(), K, 16, OC)
     assert torch.equal(band, w[kt * 16:(kt + 1) * 16])
+
+
+# --------------------------------------------------------------------------- launch fusion
+
+@pytest.mark.parametrize("K,IC,OC", [(2, 640, 256), (3, 1152, 384)])
+@pytest.mark.parametrize("M", [1, 2, 4, 5, 9])
+def test_single_launch_linear_bit_identical_to_three_stage(cuda, monkeypatch, K, IC, OC, M):
+    """Input transform + product + output transform in one kernel (M <= 4) equals
+    the three separate kernels, 0 differing f16 bits; beyond 4 rows the module
+    uses the separate input transform and must agree too."""
+    rng = np.random.default_rng(K * 10 + M)
+    code, rin, rout = synth.coded_projection(rng, IC, OC, K)
+    x = dev(synth.activations(rng, M, IC), cuda)
+    set_env(monkeypatch, ESCHA_MLX_GEMV="mma", ESCHA_MLX_FUSED_HAD=1, ESCHA_MLX_SPLITK=None)
+    fused = dense.EschaLinear(dense.EschaWeight(code, rin, rout, device=cuda))
+    assert fused._single_launch(M) == (M <= msl.FUSE_INPUT_MAX_ROWS)
+    y = fused(x)
+    set_env(monkeypatch, ESCHA_MLX_FUSED_HAD=0)
+    staged = dense.EschaLinear(dense.EschaWeight(code, rin, rout, device=cuda))
+    assert not staged._single_launch(M)
+    assert torch.equal(y, staged(x))
+
+
+@pytest.mark.parametrize("M", [1, 3, 6])
+def test_project_many_equals_separate_calls(cuda, monkeypatch, M):
+    """Q/K/V-style joint launch: each projection keeps its own split factor, so
+    the joint outputs equal the separate calls bit for bit."""
+    set_env(monkeypatch, ESCHA_MLX_GEMV="mma", ESCHA_MLX_FUSED_HAD=1, ESCHA_MLX_SPLITK=None)
+    rng = np.random.default_rng(M)
+    lins = [dense.EschaLinear(dense.EschaWeight(*synth.coded_projection(rng, 1024, oc, 2), device=cuda))
+            for oc in (768, 128, 128)]
+    x = dev(synth.activations(rng, M, 1024), cuda)
+    outs = dense.project_many(lins, x)
+    for lin, y in zip(lins, outs):
+        assert torch.equal(y, lin(x))
+    # a mixed-rate group falls back to separate calls and still agrees
+    mixed = lins[:1] + [dense.EschaLinear(dense.EschaWeight(
+        *synth.coded_projection(rng, 1024, 256, 3), device=cuda))]
+    for lin, y in zip(mixed, dense.project_many(mixed, x)):
+        assert torch.equal(y, lin(x))
+
+
+@pytest.mark.parametrize("M", [1, 4, 7])
+def test_swiglu_project_equals_unfused_chain(cuda, oracle, monkeypatch, M):
+    set_env(monkeypatch, ESCHA_MLX_GEMV="mma", ESCHA_MLX_FUSED_HAD=1, ESCHA_MLX_SPLITK=None)
+    rng = np.random.default_rng(40 + M)
+    IC, OC, K = 1408, 256, 3
+    code, rin, rout = synth.coded_projection(rng, IC, OC, K)
+    down = dense.EschaLinear(dense.EschaWeight(code, rin, rout, device=cuda))
+    g = dev((rng.standard_normal((M, IC)) * 2).astype(np.float16), cuda)
+    u = dev(synth.activations(rng, M, IC), cuda)
+    y = dense.swiglu_project(down, g, u)
+    assert torch.equal(y, down(msl.swiglu_pair(g, u)))
+    ri, ro = oracle.fold_scales(rin, rout)
+    h = oracle.swiglu(np.concatenate([host(g), host(u)], axis=-1))
+    assert rel_err(host(y), oracle.dense_linear(h, code, ri, ro, K)) < 2e-3

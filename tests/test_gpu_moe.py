@@ -259,6 +259,11 @@ def test_full_size_moe_layer(cuda, oracle, monkeypatch, T):
     cfg = synth.MOE_35B
     rng = np.random.default_rng(35)
     w = synth.moe_weights(rng, cfg["E"], cfg["H"], cfg["I"], cfg["Kg"], cfg["Kd"])
+    # two chained linears with ~0.02 scale vectors put the outputs in the fp16
+    # subnormal range, where one ulp is percents of the value; scaling the output
+    # vectors by an exact power of two keeps the comparison about the kernels
+    w["gu_rout"] = (w["gu_rout"].astype(np.float32) * 32).astype(np.float16)
+    w["dn_rout"] = (w["dn_rout"].astype(np.float32) * 32).astype(np.float16)
     x = synth.activations(rng, T, cfg["H"])
     ids, scores = synth.topk_softmax(synth.router_logits(rng, T, cfg["E"]), cfg["top_k"])
     blk = _block(w, cuda, cfg["top_k"])
@@ -272,3 +277,20 @@ def test_full_size_moe_layer(cuda, oracle, monkeypatch, T):
         assert rel_err(host(y), want) < 2e-3
     set_env(monkeypatch, ESCHA_MLX_GEMV="reforder")
     assert rel_err(host(y), host(blk._expert_path(xd, idd, scd))) < 2e-3
+
+
+@pytest.mark.parametrize("T", [1, 5, 33])
+def test_fused_expert_legs_bit_identical_to_staged(cuda, monkeypatch, T):
+    """The two-launch expert path (gather + input transform + product + output
+    transform per leg, SwiGLU inside the second) equals the staged kernels."""
+    rng = np.random.default_rng(T)
+    E, H, I, top_k = 16, 512, 256, 4
+    w = synth.moe_weights(rng, E, H, I, 2, 3)
+    x = dev(synth.activations(rng, T, H), cuda)
+    ids, scores = synth.topk_softmax(synth.router_logits(rng, T, E), top_k)
+    idd, scd = dev(ids, cuda), dev(scores, cuda)
+    set_env(monkeypatch, ESCHA_MLX_GEMV="mma", ESCHA_MLX_FUSED_HAD=1, ESCHA_MLX_SPLITK=None)
+    fused = _block(w, cuda, top_k)._expert_path(x, idd, scd)
+    set_env(monkeypatch, ESCHA_MLX_FUSED_HAD=0)
+    staged = _block(w, cuda, top_k)._expert_path(x, idd, scd)
+    assert torch.equal(fused, staged)
