@@ -274,16 +274,22 @@ def main() -> None:
         return sharding.all_gather_columns(y)
 
     def layer_step(layer, x):
-        q = gather(layer["q_proj"](x))
-        k, v = dense.project_pair(layer["k_proj"], layer["v_proj"], x)
-        k, v = gather(k), gather(v)
+        q, k, v = dense.project_many([layer["q_proj"], layer["k_proj"], layer["v_proj"]], x)
+        q, k, v = gather(q), gather(k), gather(v)
         o = gather(layer["o_proj"](x))
         g, u = dense.project_pair(layer["gate_proj"], layer["up_proj"], x)
-        h = gather(msl.swiglu_pair(g, u))
-        d = gather(layer["down_proj"](h))
+        if world == 1:
+            d = dense.swiglu_project(layer["down_proj"], g, u)
+        else:   # down needs the full SwiGLU output: gather the shards first
+            d = gather(layer["down_proj"](gather(msl.swiglu_pair(g, u))))
         return q, k, v, o, d
 
-    launches_per_step = 13  # 5 transforms (2 paired) + 7 GEMV + swiglu, all kernels of this library
+    # launches of this library's kernels per step: fused small-batch path = q/k/v, o,
+    # gate/up, swiglu+down (4); larger batches add the separate input transforms
+    if M <= msl.FUSE_INPUT_MAX_ROWS:
+        launches_per_step = 4 if world == 1 else 6
+    else:
+        launches_per_step = 11   # q/k/v 3+1, o 1+1, gate/up 1+1, swiglu 1, down 1+1
 
     x0 = torch.randn((M, HIDDEN), device=device, generator=gen).half()
 

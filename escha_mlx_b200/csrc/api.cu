@@ -299,6 +299,9 @@ int escha_coded_projections(const void* x, const void* const* x_proj, const void
     p.x_up = static_cast<const __half*>(x_up);
     p.x_stride = x_stride;
     p.x_row_div = x_row_div < 1 ? 1 : x_row_div;
+    p.hash_mask = 0x8FFF8FFFu;
+    p.hash_xor = 0x3B603B60u;
+    p.mul2 = 2u; p.mul4 = 4u; p.mul16 = 16u; p.mul32 = 32u; p.mul64 = 64u; p.mul128 = 128u;
     p.jobs = static_cast<const escha::RowJob*>(jobs);
     p.M = M; p.IC = IC; p.K = K;
     p.splits = smax;

@@ -41,6 +41,18 @@ __device__ __forceinline__ uint32_t cba_decode_dup(uint32_t state16) {
     return as_u32(__hadd2(__low2half2(h), __high2half2(h)));
 }
 
+// Hot-loop form of the decode.  With both 32-bit constants written as literals
+// the compiler emits two logic instructions per weight (an AND-immediate and an
+// XOR-immediate; a three-input logic op takes only one immediate), and the
+// integer pipe is what limits the GEMV.  Taking the mask and the xor value as
+// run-time registers makes it one three-input op: (p & mask) ^ x = LUT 0x6A.
+__device__ __forceinline__ uint32_t cba_decode_dup(uint32_t state16, uint32_t mask, uint32_t x) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(state16 * 0xCBAC1FEDu), "r"(mask), "r"(x));
+    __half2 h = as_half2(r);
+    return as_u32(__hadd2(__low2half2(h), __high2half2(h)));
+}
+
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
@@ -53,6 +65,20 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 // Produces the lane's eight 16-bit states, zero-extended.
 // ---------------------------------------------------------------------------
 
+// Left shift that stays on the integer pipe (funnel-shift form).
+__device__ __forceinline__ uint32_t shl_alu(uint32_t a, uint32_t n) {
+    uint32_t d;
+    asm("shf.l.wrap.b32 %0, %1, %1, %2;" : "=r"(d) : "r"(a), "r"(n));
+    return d;   // rotate; callers only use bits that a plain shift would also produce
+}
+
+// Multipliers 2^k handed to the hot loop as run-time values: `x * m` with an
+// opaque m is always an IMAD (multiply pipe), whereas `x << k` may be placed on
+// the integer pipe, which the decode saturates first.
+struct ShiftMuls {
+    uint32_t m2, m4, m16, m32, m64, m128;
+};
+
 struct LaneK2 {
     uint32_t i0, i1, sel;  // word indices and the byte selector that forms the window
     __device__ __forceinline__ explicit LaneK2(uint32_t lane) {
@@ -63,12 +89,11 @@ struct LaneK2 {
     }
 };
 
+// State j is the 16-bit window of wv at bit 2*(7-j).  Left shifts bring every
+// window to a byte boundary; the byte permute then extracts it zero-extended, so
+// no separate mask is needed.
 __device__ __forceinline__ void states_k2(uint32_t w0, uint32_t w1, uint32_t sel, uint32_t s[8]) {
     const uint32_t wv = prmt(w1, w0, sel);
-    // State j is the 16-bit window of wv at bit 2*(7-j).  Left shifts (which the
-    // compiler can issue on the multiply pipe, leaving the integer pipe to the
-    // byte permutes) bring every window to a byte boundary; the permute then
-    // extracts it zero-extended, so no separate mask is needed.
     const uint32_t z1 = wv << 2, z2 = wv << 4, z3 = wv << 6;
     s[7] = prmt(wv, 0u, 0x4410u);   // bit 0
     s[3] = prmt(wv, 0u, 0x4421u);   // bit 8
@@ -79,9 +104,28 @@ __device__ __forceinline__ void states_k2(uint32_t w0, uint32_t w1, uint32_t sel
     s[4] = prmt(z1, 0u, 0x4421u);   // bit 6  -> 8
     s[0] = prmt(z1, 0u, 0x4432u);   // bit 14 -> 16
 }
+__device__ __forceinline__ void states_k2(uint32_t w0, uint32_t w1, uint32_t sel,
+                                          const ShiftMuls& m, uint32_t s[8]) {
+    const uint32_t wv = prmt(w1, w0, sel);
+    const uint32_t z1 = wv * m.m4, z2 = wv * m.m16, z3 = wv * m.m64;
+    s[7] = prmt(wv, 0u, 0x4410u);
+    s[3] = prmt(wv, 0u, 0x4421u);
+    s[6] = prmt(z3, 0u, 0x4421u);
+    s[2] = prmt(z3, 0u, 0x4432u);
+    s[5] = prmt(z2, 0u, 0x4421u);
+    s[1] = prmt(z2, 0u, 0x4432u);
+    s[4] = prmt(z1, 0u, 0x4421u);
+    s[0] = prmt(z1, 0u, 0x4432u);
+}
 
+// K = 3: the reference forms merged = (w[i0] << 32) | w[i2] and takes 32-bit
+// windows at bit sh and sh + 12 (ref.py:78-93).  i0 is always the word before i2
+// and sh is always a multiple of 8 (it cycles 8, 16, 24, 0 with the lane), so
+// u = merged >> sh is a byte selection; the eight states are the 16-bit windows
+// of u at bits 21, 18, 15, 12, 9, 6, 3, 0.
 struct LaneK3 {
-    uint32_t i0, i2, sh;  // word indices (mod 24) and the funnel shift
+    uint32_t i0, i2, sh;    // word indices (mod 24) and the window shift
+    uint32_t selA, selB;    // byte selectors: A = u[0:32), B = u[16:48)
     __device__ __forceinline__ explicit LaneK3(uint32_t lane) {
         uint32_t b1 = (lane * 8u + 257u) * 3u;
         uint32_t b0 = b1 - 16u;
@@ -91,6 +135,9 @@ struct LaneK3 {
         sh = ((j2 + 1u) << 5) - b2;
         i0 = j0 % 24u;
         i2 = j2 % 24u;
+        const uint32_t b = sh >> 3;
+        selA = b | ((b + 1u) << 4) | ((b + 2u) << 8) | ((b + 3u) << 12);
+        selB = (b + 2u) | ((b + 3u) << 4) | ((b + 4u) << 8) | (min(b + 5u, 7u) << 12);
     }
 };
 
@@ -109,6 +156,21 @@ __device__ __forceinline__ void states_k3(uint32_t whi, uint32_t wlo, uint32_t s
     s[6] = prmt(w7 << 5, 0u, 0x4421u);
     s[7] = prmt(w7, 0u, 0x4410u);
 }
+// Hot-loop form: two byte selections instead of 64-bit shifts, four shifts as
+// multiplies (multiply pipe) and three as funnel shifts (integer pipe), which
+// splits the work about evenly between the two half-rate pipes.
+__device__ __forceinline__ void states_k3(uint32_t whi, uint32_t wlo, uint32_t selA,
+                                          uint32_t selB, const ShiftMuls& m, uint32_t s[8]) {
+    const uint32_t A = prmt(wlo, whi, selA), B = prmt(wlo, whi, selB);
+    s[7] = prmt(A, 0u, 0x4410u);                 // bit 0
+    s[6] = prmt(A * m.m32, 0u, 0x4421u);         // bit 3  -> 8
+    s[5] = prmt(A * m.m4, 0u, 0x4421u);          // bit 6  -> 8
+    s[4] = prmt(A * m.m128, 0u, 0x4432u);        // bit 9  -> 16
+    s[3] = prmt(A * m.m16, 0u, 0x4432u);         // bit 12 -> 16
+    s[2] = prmt(shl_alu(A, 1u), 0u, 0x4432u);    // bit 15 -> 16
+    s[1] = prmt(shl_alu(B, 6u), 0u, 0x4421u);    // bit 18 = bit 2 of B -> 8
+    s[0] = prmt(shl_alu(B, 3u), 0u, 0x4421u);    // bit 21 = bit 5 of B -> 8
+}
 
 template <int K>
 struct LaneConsts;
@@ -120,6 +182,10 @@ struct LaneConsts<2> : LaneK2 {
     __device__ __forceinline__ void states(uint32_t wa, uint32_t wb, uint32_t s[8]) const {
         states_k2(wa, wb, sel, s);
     }
+    __device__ __forceinline__ void states(uint32_t wa, uint32_t wb, const ShiftMuls& m,
+                                           uint32_t s[8]) const {
+        states_k2(wa, wb, sel, m, s);
+    }
 };
 template <>
 struct LaneConsts<3> : LaneK3 {
@@ -128,6 +194,10 @@ struct LaneConsts<3> : LaneK3 {
     __device__ __forceinline__ uint32_t ib() const { return i2; }
     __device__ __forceinline__ void states(uint32_t wa, uint32_t wb, uint32_t s[8]) const {
         states_k3(wa, wb, sh, s);
+    }
+    __device__ __forceinline__ void states(uint32_t wa, uint32_t wb, const ShiftMuls& m,
+                                           uint32_t s[8]) const {
+        states_k3(wa, wb, selA, selB, m, s);
     }
 };
 
@@ -171,6 +241,53 @@ __device__ __forceinline__ void cp_async_commit() {
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+
+// ---------------------------------------------------------------------------
+// mbarrier + bulk-copy (TMA, untiled) helpers.  Every wait is bounded: a wait
+// that gives up returns false and the caller records an error and leaves, so a
+// logic error can never spin a GPU forever.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+constexpr uint32_t kMbarWaitLimit = 1u << 22;  // try_wait attempts before giving up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < kMbarWaitLimit; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// global -> shared bulk copy (16-byte aligned addresses, size a multiple of 16),
+// completion signalled on an mbarrier of this CTA.  No multicast.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                              uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // mma.sync m16n8k16, f16 x f16 -> f32 accumulate.

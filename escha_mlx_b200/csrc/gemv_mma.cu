@@ -23,9 +23,12 @@
 //    is kept as (w, w) in one register -- one HADD2 with half-select operands --
 //    and multiplied against (x, 0): that spends an idle half of the tensor core
 //    instead of two more byte permutes per weight pair.
-//  * The code stream is read exactly once, as 16-byte cp.async copies into a
-//    warp-private shared-memory ring; the main loop has no block-wide barrier
-//    except when the activation chunk is re-staged every 512 input channels.
+//  * The code stream is read exactly once: a producer warp issues bulk copies
+//    (cp.async.bulk, the untiled TMA form, no multicast) of whole eight-tile rows
+//    into a shared-memory ring guarded by full/empty mbarriers, so the eight
+//    decode warps spend no instruction on address generation; their main loop
+//    has no block-wide barrier except when the activation chunk is re-staged (every 256 to 2048 input
+//    channels, depending on how many rows share the decode).
 //  * 128 output channels per CTA = one Hadamard block, so the CTA that
 //    completes a block runs the output transform with warp butterflies.
 //  * Split-K over 128-channel input blocks fills the 148 SMs for any shape.
@@ -39,31 +42,16 @@ namespace escha {
 
 namespace {
 
-constexpr int NS = 6;              // cp.async ring depth (8-kt blocks) per warp
-constexpr int XC = 4;              // 128-channel blocks of activations staged at a time
-constexpr int XS = XC * 128 + 8;   // words per staged row; +8 keeps LDS.64 conflict-free
+constexpr int NS = 6;              // bulk-copy ring depth (128-channel blocks) per CTA
+constexpr int kXBudgetBytes = 32 * 1024;  // shared memory spent on staged activations
 
-template <int K>
-struct CodeFetch {
-    static constexpr int WPT = 8 * K;
-    static constexpr int PIECES_PER_KT = WPT / 4;    // 16-byte pieces per tile
-    static constexpr int PIECES = 8 * PIECES_PER_KT; // per 8-kt block: 32 (K=2) or 48 (K=3)
-    uint32_t src0, dst0, src1, dst1;                 // word offsets
-    bool has1;
-    __device__ __forceinline__ CodeFetch(uint32_t lane, uint32_t tile_row_words) {
-        uint32_t p = lane;
-        src0 = (p / PIECES_PER_KT) * tile_row_words + (p % PIECES_PER_KT) * 4u;
-        dst0 = p * 4u;
-        p = lane + 32u;
-        has1 = p < PIECES;
-        src1 = (p / PIECES_PER_KT) * tile_row_words + (p % PIECES_PER_KT) * 4u;
-        dst1 = p * 4u;
-    }
-    __device__ __forceinline__ void issue(uint32_t* stage, const uint32_t* gblock) const {
-        cp_async16(stage + dst0, gblock + src0);
-        if (PIECES > 32 && has1) cp_async16(stage + dst1, gblock + src1);
-    }
-};
+// 128-channel blocks of activations staged per chunk: as many as the budget
+// allows for the job's rows (plus the zero row), between 2 and 16.  A staged row
+// is blocks*128 + 16 words; the +16 keeps the LDS.128 fragment loads conflict-free.
+inline int x_chunk_blocks(int xrows) {
+    int b = kXBudgetBytes / ((xrows + 1) * 520);
+    return b > 16 ? 16 : (b < 2 ? 2 : b);
+}
 
 template <bool FUSED_OUT>
 __device__ __forceinline__ void finalize_row(float v[4], uint32_t lane, const float* rout_blk,
@@ -90,22 +78,30 @@ __device__ __forceinline__ __half swiglu_half(__half g16, __half u16) {
 }
 
 // Stage `cnt` 128-channel blocks (starting at block blk0) of the job's rows into
-// shared memory as (x, 0) word pairs, applying the input transform when fused.
+// shared memory as (x, 0) words, applying the input transform when fused.  Within
+// each 16-channel group the words are ordered c0 c8 c1 c9 ... c7 c15, so that one
+// 16-byte load at word 4t hands lane t the B fragments of both mma of a tile:
+// (x[2t], x[2t+8]) and (x[2t+1], x[2t+9]).
 __device__ __forceinline__ void stage_activations(const GemvMmaParams& p, const __half* xsrc, const float* rin,
                                                   const int* s_rows, int nrows, uint32_t blk0,
-                                                  uint32_t cnt, uint32_t* s_x, uint32_t tid) {
+                                                  uint32_t cnt, uint32_t* s_x, uint32_t XS,
+                                                  uint32_t tid) {
     const uint32_t lane = tid & 31u, warp = tid >> 5;
     if (p.input == kInputTransformed) {
-        const uint32_t vec_per_row = cnt * 16u;  // 8-half vectors per row
-        const uint32_t total = static_cast<uint32_t>(nrows) * vec_per_row;
+        const uint32_t grp_per_row = cnt * 8u;  // 16-channel groups per row
+        const uint32_t total = static_cast<uint32_t>(nrows) * grp_per_row;
         for (uint32_t idx = tid; idx < total; idx += 256u) {
-            const uint32_t r = idx / vec_per_row, v = idx - r * vec_per_row;
-            const uint4 raw = *reinterpret_cast<const uint4*>(
+            const uint32_t r = idx / grp_per_row, v = idx - r * grp_per_row;
+            const uint4* src = reinterpret_cast<const uint4*>(
                 xsrc + static_cast<size_t>(s_rows[r] / p.x_row_div) * p.x_stride + blk0 * 128u +
-                v * 8u);
-            uint4* dst = reinterpret_cast<uint4*>(s_x + r * XS + v * 8u);
-            dst[0] = make_uint4(raw.x & 0xFFFFu, raw.x >> 16, raw.y & 0xFFFFu, raw.y >> 16);
-            dst[1] = make_uint4(raw.z & 0xFFFFu, raw.z >> 16, raw.w & 0xFFFFu, raw.w >> 16);
+                v * 16u);
+            const uint4 lo = src[0], hi = src[1];  // channels 0..7 and 8..15 of the group
+            uint4* dst = reinterpret_cast<uint4*>(s_x + r * XS + v * 16u);
+            // staged order c0 c8 c1 c9 ... c7 c15, each as a (x, 0) word
+            dst[0] = make_uint4(lo.x & 0xFFFFu, hi.x & 0xFFFFu, lo.x >> 16, hi.x >> 16);
+            dst[1] = make_uint4(lo.y & 0xFFFFu, hi.y & 0xFFFFu, lo.y >> 16, hi.y >> 16);
+            dst[2] = make_uint4(lo.z & 0xFFFFu, hi.z & 0xFFFFu, lo.z >> 16, hi.z >> 16);
+            dst[3] = make_uint4(lo.w & 0xFFFFu, hi.w & 0xFFFFu, lo.w >> 16, hi.w >> 16);
         }
         return;
     }
@@ -130,24 +126,34 @@ __device__ __forceinline__ void stage_activations(const GemvMmaParams& p, const 
         float v[4] = {__fmul_rn(a.x, sc.x), __fmul_rn(a.y, sc.y), __fmul_rn(c.x, sc.z),
                       __fmul_rn(c.y, sc.w)};
         wht128_warp(v, lane);
-        uint4 w;
-        w.x = __half_as_ushort(__float2half_rn(__fmul_rn(v[0], p.rs)));
-        w.y = __half_as_ushort(__float2half_rn(__fmul_rn(v[1], p.rs)));
-        w.z = __half_as_ushort(__float2half_rn(__fmul_rn(v[2], p.rs)));
-        w.w = __half_as_ushort(__float2half_rn(__fmul_rn(v[3], p.rs)));
-        *reinterpret_cast<uint4*>(s_x + r * XS + b * 128u + lane * 4u) = w;
+        // lane holds channels 4*lane..4*lane+3 of the block: group lane/4, channel
+        // c = 4*(lane%4)+i within it, staged at word 2*(c%8) + c/8
+        uint32_t* dst = s_x + r * XS + b * 128u + (lane >> 2) * 16u + ((lane & 1u) * 8u) +
+                        ((lane >> 1) & 1u);
+        dst[0] = __half_as_ushort(__float2half_rn(__fmul_rn(v[0], p.rs)));
+        dst[2] = __half_as_ushort(__float2half_rn(__fmul_rn(v[1], p.rs)));
+        dst[4] = __half_as_ushort(__float2half_rn(__fmul_rn(v[2], p.rs)));
+        dst[6] = __half_as_ushort(__float2half_rn(__fmul_rn(v[3], p.rs)));
     }
 }
 
+// Error word set by a kernel whose bounded wait gave up (never expected).
+__device__ int g_gemv_status = 0;
+
+constexpr int kConsumerThreads = 256;   // 8 decode warps
+constexpr int kThreads = kConsumerThreads + 32;  // + 1 producer warp
+
 template <int K, int MT>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(kThreads, 3)
 gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     constexpr int WPT = 8 * K;
-    constexpr int STAGE_WORDS = 8 * WPT;
+    constexpr int ROW_WORDS = 8 * WPT;          // one kt row of the CTA's eight tiles
+    constexpr int STAGE_WORDS = 8 * ROW_WORDS;  // eight kt rows = one 128-channel block
     constexpr int ROWS = 8 * MT;
-    extern __shared__ __align__(16) uint32_t smem[];
-    uint32_t* const s_code = smem;                       // [8 warps][NS][STAGE_WORDS]
-    uint32_t* const s_x = smem + 8 * NS * STAGE_WORDS;   // [rows + 1][XS] as (x, 0) pairs
+    extern __shared__ __align__(128) uint32_t smem[];
+    uint32_t* const s_code = smem;                    // [NS][8 kt][8 tiles][WPT]
+    uint32_t* const s_x = smem + NS * STAGE_WORDS;    // [rows + 1][XS] as (x, 0) words
+    __shared__ __align__(8) uint64_t s_full[NS], s_empty[NS];
     __shared__ int s_rows[16];
     __shared__ int s_last;
 
@@ -187,25 +193,47 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     const uint32_t b0 = split * bbase + min(split, brem);
     const uint32_t nb = bbase + (split < brem ? 1u : 0u);
 
-    const uint32_t tile_row_words = TN * WPT;  // words between kt and kt+1 of one tile column
-    const uint32_t* gtile = pr.code + static_cast<size_t>(expert) * (p.IC >> 4) * tile_row_words +
-                            (ocb * 8u + warp) * WPT;
-    uint32_t* const my_stages = s_code + warp * (NS * STAGE_WORDS);
-    const CodeFetch<K> fetch(lane, tile_row_words);
-    const LaneConsts<K> lc(lane);
-
-    // prologue: fill NS-1 stages
+    const uint32_t tile_row_words = TN * WPT;  // words between kt and kt+1 in the stream
+    const uint32_t full0 = smem_u32(s_full), empty0 = smem_u32(s_empty);
+    if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < NS - 1; ++s) {
-        if (static_cast<uint32_t>(s) < nb)
-            fetch.issue(my_stages + s * STAGE_WORDS,
-                        gtile + static_cast<size_t>(b0 + s) * 8u * tile_row_words);
-        cp_async_commit();
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(full0 + 8u * s, 1u);    // the producer's arrive.expect_tx
+            mbar_init(empty0 + 8u * s, 8u);   // one arrival per decode warp
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == 8) {
+        // ---- producer warp: bulk copies (TMA, untiled, no multicast) of the CTA's
+        // eight-tile rows, one copy per kt row, eight rows per stage
+        const uint32_t* grow = pr.code + static_cast<size_t>(expert) * (p.IC >> 4) * tile_row_words +
+                               ocb * ROW_WORDS +
+                               (static_cast<size_t>(b0) * 8u + lane) * tile_row_words;
+        const uint32_t dst0 = smem_u32(s_code) + lane * (ROW_WORDS * 4u);
+        for (uint32_t i = 0; i < nb; ++i) {
+            const uint32_t slot = i % NS;
+            if (i >= NS && !mbar_wait(empty0 + 8u * slot, ((i / NS) - 1u) & 1u)) {
+                if (lane == 0) atomicExch(&g_gemv_status, 1);
+                return;
+            }
+            if (lane == 0) mbar_arrive_expect_tx(full0 + 8u * slot, STAGE_WORDS * 4u);
+            __syncwarp();
+            if (lane < 8)
+                bulk_copy_g2s(dst0 + slot * (STAGE_WORDS * 4u), grow, ROW_WORDS * 4u,
+                              full0 + 8u * slot);
+            grow += static_cast<size_t>(8u) * tile_row_words;
+        }
+        return;
     }
 
+    // ---- decode warps
+    const LaneConsts<K> lc(lane);
+    const uint32_t XCB = p.xcb, XS = XCB * 128u + 16u;  // blocks per chunk, words per staged row
     // zero row: B columns past the job's last row read it instead of branching
     uint32_t* const zero_row = s_x + static_cast<uint32_t>(xrows) * XS;
-    for (uint32_t i = tid; i < static_cast<uint32_t>(XS); i += 256u) zero_row[i] = 0u;
+    for (uint32_t i = tid; i < XS; i += kConsumerThreads) zero_row[i] = 0u;
 
     // two independent accumulator sets per column block: the two mma of a tile
     // do not wait on each other, and each chain advances once per tile
@@ -219,50 +247,56 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         const int slot = static_cast<int>(g) + 8 * mt;
-        xrow[mt] = (slot < nrows ? s_x + slot * XS : zero_row) + 2u * t;
+        xrow[mt] = (slot < nrows ? s_x + slot * XS : zero_row) + 4u * t;
     }
     const float* rin = pr.rin ? pr.rin + static_cast<size_t>(expert) * p.IC : nullptr;
     const __half* xsrc = pr.x ? pr.x : p.x;
+    const uint32_t hmask = p.hash_mask, hxor = p.hash_xor;
+    const ShiftMuls muls{p.mul2, p.mul4, p.mul16, p.mul32, p.mul64, p.mul128};
+    const uint32_t* const wa0 = s_code + warp * WPT + lc.ia();
+    const uint32_t* const wb0 = s_code + warp * WPT + lc.ib();
 
-    for (uint32_t i = 0; i < nb; ++i) {
-        const uint32_t cblk = i % XC;
-        if (cblk == 0) {
-            __syncthreads();
-            stage_activations(p, xsrc, rin, s_rows, nrows, b0 + i, min(static_cast<uint32_t>(XC), nb - i),
-                              s_x, tid);
-            __syncthreads();
-        }
-        cp_async_wait<NS - 2>();
-        __syncwarp();
-        {
-            const uint32_t nxt = i + NS - 1;
-            if (nxt < nb)
-                fetch.issue(my_stages + (nxt % NS) * STAGE_WORDS,
-                            gtile + static_cast<size_t>(b0 + nxt) * 8u * tile_row_words);
-            cp_async_commit();
-        }
-        const uint32_t* stage = my_stages + (i % NS) * STAGE_WORDS;
-        const uint32_t kbase = cblk * 128u;
-#pragma unroll 2
-        for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t* tw = stage + kk * WPT;
-            uint32_t s[8], a[8];
-            lc.states(tw[lc.ia()], tw[lc.ib()], s);
+    bool ok = true;
+    uint32_t slot = 0, phase = 0;
+    for (uint32_t c0 = 0; c0 < nb && ok; c0 += XCB) {
+        const uint32_t cnt = min(XCB, nb - c0);
+        named_barrier_sync(1, kConsumerThreads);
+        stage_activations(p, xsrc, rin, s_rows, nrows, b0 + c0, cnt, s_x, XS, tid);
+        named_barrier_sync(1, kConsumerThreads);
+        for (uint32_t cb = 0; cb < cnt; ++cb) {
+            if (!mbar_wait(full0 + 8u * slot, phase)) { ok = false; break; }
+            const uint32_t* wa = wa0 + slot * STAGE_WORDS;
+            const uint32_t* wb = wb0 + slot * STAGE_WORDS;
+            const uint32_t* xr[MT];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) a[j] = cba_decode_dup(s[j]);
-            const uint32_t koff = kbase + kk * 16u;
+            for (int mt = 0; mt < MT; ++mt) xr[mt] = xrow[mt] + cb * 128u;
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const uint2 b01 = *reinterpret_cast<const uint2*>(xrow[mt] + koff);
-                const uint2 b23 = *reinterpret_cast<const uint2*>(xrow[mt] + koff + 8u);
-                // value j sits at (channel g + 8*(j>=4), input 2t + (j&1) + 8*((j>>1)&1))
-                mma16816(dA[mt], a[0], a[4], a[2], a[6], b01.x, b23.x);
-                mma16816(dB[mt], a[1], a[5], a[3], a[7], b01.y, b23.y);
+            for (int kk = 0; kk < 8; ++kk) {
+                uint32_t s[8], a[8];
+                lc.states(wa[kk * ROW_WORDS], wb[kk * ROW_WORDS], muls, s);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a[j] = cba_decode_dup(s[j], hmask, hxor);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    // (x[2t], x[2t+8], x[2t+1], x[2t+9]) as (x, 0) words
+                    const uint4 b = *reinterpret_cast<const uint4*>(xr[mt] + kk * 16);
+                    // value j sits at (channel g + 8*(j>=4), input 2t + (j&1) + 8*((j>>1)&1))
+                    mma16816(dA[mt], a[0], a[4], a[2], a[6], b.x, b.y);
+                    mma16816(dB[mt], a[1], a[5], a[3], a[7], b.z, b.w);
+                }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8u * slot);  // this warp is done with the slot
+            if (++slot == NS) { slot = 0; phase ^= 1u; }
         }
     }
-    cp_async_wait<0>();
-    __syncthreads();
+    if (!ok) {
+        // a wait gave up: record it, give copies already in flight time to land, leave
+        if (lane == 0) atomicExch(&g_gemv_status, 2);
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        return;
+    }
+    named_barrier_sync(1, kConsumerThreads);
 
     // accumulators -> shared [ROWS][128] (aliases the drained code ring)
     float* const s_acc = reinterpret_cast<float*>(s_code);
@@ -274,7 +308,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
         s_acc[n0 * 128u + ch + 8u] = __fadd_rn(dA[mt][2], dB[mt][2]);
         s_acc[(n0 + 1u) * 128u + ch + 8u] = __fadd_rn(dA[mt][3], dB[mt][3]);
     }
-    __syncthreads();
+    named_barrier_sync(1, kConsumerThreads);
 
     const float* rout_blk =
         pr.rout ? pr.rout + static_cast<size_t>(expert) * OC + ocb * 128u : nullptr;
@@ -299,7 +333,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
         __stcg(reinterpret_cast<float4*>(my_part + r * 128u + lane * 4u),
                *reinterpret_cast<const float4*>(s_acc + r * 128u + lane * 4u));
     __threadfence();
-    __syncthreads();
+    named_barrier_sync(1, kConsumerThreads);
     if (tid == 0) {
         int32_t* ctr = p.counters + static_cast<size_t>(job) * nocb + gocb;
         const int prev = atomicAdd(ctr, 1);
@@ -307,7 +341,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
         if (last) *ctr = 0;  // every split has arrived: leave the counter clean for the next launch
         s_last = last;
     }
-    __syncthreads();
+    named_barrier_sync(1, kConsumerThreads);
     if (!s_last) return;
     __threadfence();
     const float* const part0 =
@@ -331,9 +365,10 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
 
 template <int K, int MT>
 cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
-    constexpr int STAGE_WORDS = 8 * 8 * K;
+    constexpr int STAGE_WORDS = 8 * 8 * 8 * K;
+    const size_t XS = static_cast<size_t>(p.xcb) * 128u + 16u;
     const size_t smem =
-        (static_cast<size_t>(8 * NS * STAGE_WORDS) + static_cast<size_t>(xrows + 1) * XS) * 4u;
+        (static_cast<size_t>(NS * STAGE_WORDS) + static_cast<size_t>(xrows + 1) * XS) * 4u;
     static size_t configured[64] = {0};  // per device: largest size already enabled
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -345,7 +380,7 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    dim3 grid(p.total_ocb, p.splits, p.njobs), block(256);
+    dim3 grid(p.total_ocb, p.splits, p.njobs), block(kThreads);
     gemv_mma_kernel<K, MT><<<grid, block, smem, st>>>(p);
     return cudaGetLastError();
 }
@@ -357,9 +392,11 @@ size_t gemv_mma_part_floats(int njobs, int splits, int total_ocb, int rows_per_j
     return static_cast<size_t>(njobs) * splits * total_ocb * rows_per_job * 128u;
 }
 
-cudaError_t launch_gemv_mma(const GemvMmaParams& p, cudaStream_t st) {
+cudaError_t launch_gemv_mma(const GemvMmaParams& params, cudaStream_t st) {
+    GemvMmaParams p = params;
     const int rows = p.rows_per_job;
     const int xrows = p.jobs ? rows : (p.M < rows ? p.M : rows);
+    p.xcb = x_chunk_blocks(xrows);
     if (p.K == 2) return rows == 8 ? launch_t<2, 1>(p, xrows, st) : launch_t<2, 2>(p, xrows, st);
     return rows == 8 ? launch_t<3, 1>(p, xrows, st) : launch_t<3, 2>(p, xrows, st);
 }

@@ -55,7 +55,13 @@ struct GemvMmaParams {
     int rows_per_job;         // 8 or 16
     int njobs;                // grid.z
     int input;                // GemvInput
+    int xcb;                  // activation blocks staged per chunk (set by the launcher)
     float rs;
+    // codebook constants 0x8FFF8FFF / 0x3B603B60, passed as run-time values so the
+    // decode's (p & mask) ^ x stays a single three-input logic instruction
+    uint32_t hash_mask, hash_xor;
+    // 2^k multipliers {2, 4, 16, 32, 64, 128}: shifts issued as multiplies (see common.cuh)
+    uint32_t mul2, mul4, mul16, mul32, mul64, mul128;
 };
 
 cudaError_t launch_lut_init(__half* lut, cudaStream_t st);
