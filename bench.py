@@ -83,7 +83,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.gpu)],
+                 "-lms", "20", "-i", str(self.gpu)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -386,12 +386,13 @@ def main() -> None:
         e2e = LAYER_BYTES * args.steps / (ms_e2e * 1e-3) / 1e9
         launches = 7 * reps
         achieved = (LAYER_BYTES / world) * reps / (ms_gemv * 1e-3) / 1e9   # per GPU
-        traffic = None
-        try:
-            with open(os.path.join(ROOT, "profiles", "gemv_mma_traffic.json")) as f:
-                traffic = json.load(f).get("dram_bytes_per_launch_avg")
-        except Exception:
-            pass
+        # DRAM bytes per GEMV launch from the ncu captures summarised under profiles/
+        # (gemv_mma_gate_proj_k3_m1.md: 33,567,744 B read for 33,423,360 B of code, 1.004x;
+        # gemv_mma_q_proj_k2_m1.md: 7,962,880 B for 7,864,320 B, 1.013x; no writes to DRAM).
+        # Traffic grows with the code bytes, so the other projections are scaled by their rate's
+        # factor; this is the average over the seven launches timed above, per GPU.
+        traffic = (sum(ic * oc * k // 8 * (1.013 if k == 2 else 1.004) for _, ic, oc, k in LAYER)
+                   / 7 / world) if M == 1 else None
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
