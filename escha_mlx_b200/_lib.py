@@ -36,6 +36,7 @@ SIGNATURES = {
     "escha_coded_gemv_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "escha_coded_gemv_splits": (_i, [_i, _i, _i, _i]),
     "escha_coded_gemv": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
+    "escha_coded_gemv_static": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp]),
     "escha_coded_projections": (_i, [_vp, _vp, _vp, ctypes.c_long, _i, _i, _i, _vp, _vp, _vp, _vp, _vp,
                                      _vp, _i, _i, _i, _i, _i, _i, _vp, _f, _vp, _sz, _vp]),
     "escha_moe_jobs_bound": (_i, [_i, _i, _i]),

@@ -65,6 +65,51 @@ constexpr size_t kMaxCounters = kCounterBytes / sizeof(int32_t);
 
 }  // namespace
 
+namespace escha {
+
+void set_last_error(const char* msg) { g_err = msg; }
+
+int coded_gemv_with_scratch(const void* xh, const void* code, const float* rout, int M, int IC,
+                            int OC, int K, int splits, float rs, int32_t* counters, float* part,
+                            void* out, void* stream) {
+    if (int rc = check_shape(__func__, K, IC, OC, 128)) return rc;
+    REQUIRE(M >= 1 && M <= 16, "%s: M=%d outside [1, 16]", __func__, M);
+    REQUIRE(splits >= 1 && splits <= IC / 128, "%s: splits=%d outside [1, %d]", __func__, splits,
+            IC / 128);
+    REQUIRE_PTR(xh);
+    REQUIRE_PTR(code);
+    REQUIRE_PTR(out);
+    OPTIONAL_PTR(rout);
+    REQUIRE_PTR(counters);
+    REQUIRE_PTR(part);
+    GemvMmaParams p{};
+    p.prob[0].code = static_cast<const uint32_t*>(code);
+    p.prob[0].rout = rout;
+    p.prob[0].out = out;
+    p.prob[0].OC = OC;
+    p.prob[0].ocb0 = 0;
+    p.prob[0].splits = splits;
+    p.nprob = 1;
+    p.total_ocb = OC / 128;
+    p.x = static_cast<const __half*>(xh);
+    p.x_stride = IC;
+    p.x_row_div = 1;
+    p.M = M; p.IC = IC; p.K = K;
+    p.splits = splits;
+    p.rows_per_job = M <= 8 ? 8 : 16;
+    p.njobs = 1;
+    p.input = kInputTransformed;
+    p.rs = rs;
+    p.hash_mask = 0x8FFF8FFFu;
+    p.hash_xor = 0x3B603B60u;
+    p.mul2 = 2u; p.mul4 = 4u; p.mul16 = 16u; p.mul32 = 32u; p.mul64 = 64u; p.mul128 = 128u;
+    p.counters = counters;
+    p.part = part;
+    return cuda_result(launch_gemv_mma(p, as_stream(stream)), "escha_coded_gemv_static");
+}
+
+}  // namespace escha
+
 extern "C" {
 
 int escha_version(void) { return ESCHA_ABI_VERSION; }

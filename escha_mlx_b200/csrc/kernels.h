@@ -90,4 +90,12 @@ cudaError_t launch_w8a16(const __half* x, const int8_t* w8, const __half* scale,
                          int N, int Kd, cudaStream_t st);
 size_t gemv_mma_part_floats(int njobs, int splits, int total_ocb, int rows_per_job);
 
+// Used by the entry point that carries its own scratch (noalloc.cu): record an
+// error message for escha_last_error(), and launch the dense single-projection
+// GEMV with explicit counter / partial pointers.  Returns an ESCHA_* code.
+void set_last_error(const char* msg);
+int coded_gemv_with_scratch(const void* xh, const void* code, const float* rout, int M, int IC,
+                            int OC, int K, int splits, float rs, int32_t* counters, float* part,
+                            void* out, void* stream);
+
 }  // namespace escha

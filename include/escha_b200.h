@@ -134,6 +134,24 @@ int escha_coded_gemv(const void *xh, const void *code, const float *rout, int M,
                      int K, int splits, float rs, void *workspace, size_t workspace_bytes,
                      void *out, void *stream);
 
+/* escha_coded_gemv for callers that cannot allocate device memory and so have no
+ * workspace to pass: a plugin inside a host runtime that owns all device memory
+ * (a server with a pre-sized arena, a fixed memory map), a callback that must
+ * not re-enter the host allocator, a loop that cannot take cudaMalloc's
+ * device-wide synchronisation.  This entry point has no counterpart in the
+ * reference.  Same arguments and results as escha_coded_gemv (bit-identical for
+ * equal splits) minus the workspace: the split-K scratch is a static device
+ * array inside the library (8 MiB of partials + 64 KiB of counters, held by every
+ * GPU that loads the library until the process exits).  It allocates nothing.
+ *  - Limits: 1 <= M <= 16 and splits * (OC/128) * (M <= 8 ? 8 : 16) * 512 bytes
+ *    <= 8 MiB; anything larger returns ESCHA_EINVAL with a message.
+ *  - The array is shared by all calls on a device and keeps the last call's
+ *    contents: calls that can overlap on the GPU race; order them on one stream.
+ *  - The first call on each device does a one-time set-up (resolves the array's
+ *    address, clears its counters): make it before any stream capture. */
+int escha_coded_gemv_static(const void *xh, const void *code, const float *rout, int M, int IC,
+                            int OC, int K, int splits, float rs, void *out, void *stream);
+
 /* General form of the tensor-core kernel: nproj (1..4) projections of the SAME
  * rows in one launch, with the transforms around the product optionally fused.
  * Replaces, per launch, one of the reference's pair/fused dispatches:
