@@ -421,6 +421,12 @@ def main() -> None:
                           f"layer at batch {M} on the CPU oracle (C port of escha_mlx/ref.py)"}
         print(json.dumps(line), flush=True)
     if world > 1:
+        # graphs that captured NCCL collectives pin the communicator: NCCL's teardown
+        # waits for them to be destroyed, so release them before leaving the group
+        torch.cuda.synchronize()
+        for g in step_graphs + gemv_graphs:
+            g.close()
+        torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
 

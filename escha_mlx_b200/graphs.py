@@ -49,6 +49,15 @@ class GraphedCall:
     def replay(self) -> None:
         self._graph.replay()
 
+    def close(self) -> None:
+        """Destroy the captured graph and drop its static tensors.  A graph that
+        captured NCCL collectives keeps a reference on the communicator, and
+        NCCL's communicator teardown waits until every such graph is gone: call
+        this on each graphed call before ``destroy_process_group()``."""
+        self._graph.reset()
+        self._outputs = None
+        self._inputs = []
+
     def __call__(self, *inputs: torch.Tensor):
         for dst, src in zip(self._inputs, inputs):
             dst.copy_(src, non_blocking=True)
