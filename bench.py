@@ -203,6 +203,156 @@ def workload_config(args, n_sets: int) -> dict:
                          f"({n_sets * LAYER_BYTES // args.gpus} B per GPU > L2)"}
 
 
+# --------------------------------------------------------------------------- MoE workloads
+
+MOE_LAYERS = 40
+
+
+def run_moe(args, rank: int, world: int, local_rank: int) -> None:
+    """`--workload moe`: BASELINE.json configs[2], one 35B-A3B-class MoE decode layer
+    (256 routed 2-bit experts, top-8, hidden 2048, expert width 512, int8 shared expert)
+    at `--tokens` tokens.  `--workload step`: configs[3], the 40-layer decode step at
+    batch 32 with the int8 attention projections in front of every MoE block.
+    A step is one layer (moe) or one 40-layer pass (step); 40 layers of distinct
+    weights are resident so no step finds its experts in L2.  N > 1: expert parallel,
+    the router, shared expert and int8 projections replicated."""
+    import torch
+    import torch.distributed as dist
+    from escha_mlx_b200 import graphs, sharding, workloads
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    args.warmup = max(args.warmup, 3)
+    full_step = args.workload == "step"
+    T = 32 if full_step else args.tokens
+    cfg = workloads.MOE_35B
+    er = sharding.expert_range(cfg["experts"], rank, world) if world > 1 else None
+    layers = workloads.moe_stack(MOE_LAYERS, device, attention=full_step, expert_range=er, rank=rank)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(99)
+    x0 = torch.randn((T, cfg["hidden"]), device=device, generator=gen).half()
+
+    def norm(h):
+        h = h.float()
+        return (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6)).half()
+
+    if full_step:
+        def pass_(x):
+            for layer in layers:
+                x = norm(x.float() + layer(x).float())
+            return x
+        steps_per_replay = 1
+    else:
+        def pass_(x):
+            out = None
+            for layer in layers:
+                out = layer(x)
+            return out
+        steps_per_replay = MOE_LAYERS
+    g = graphs.GraphedCall(pass_, [x0])
+
+    # bytes a step touches on this GPU (distinct routed experts of the shard + int8 + router)
+    with torch.no_grad():
+        if full_step:
+            xs, routed = x0, 0
+            for layer in layers:
+                routed += layer.routed_experts(xs)
+                xs = norm(xs.float() + layer(xs).float())
+        else:
+            routed = sum(layer.routed_experts(x0) for layer in layers)
+    torch.cuda.synchronize()
+    lay = layers[0]
+    code_bytes = routed * lay.expert_bytes                       # per 40-layer pass, this GPU
+    other_bytes = MOE_LAYERS * (lay.int8_bytes + lay.router_bytes)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    replays = max(1, -(-args.steps // steps_per_replay))
+    steps = replays * steps_per_replay
+    stream = torch.cuda.current_stream()
+    for _ in range(max(1, -(-args.warmup // steps_per_replay))):
+        g.replay()
+    sync_all()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        sync_all()
+        ev0.record(stream)
+        for _ in range(replays):
+            g.replay()
+        ev1.record(stream)
+        sync_all()
+    ms_total = ev0.elapsed_time(ev1)
+
+    x_host = torch.randn((T, cfg["hidden"])).half().pin_memory()
+    y_host = torch.empty((T, cfg["hidden"]), dtype=torch.float16).pin_memory()
+    for _ in range(2):
+        y_host.copy_(g(x_host), non_blocking=True)
+    sync_all()
+    ee0, ee1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ee0.record(stream)
+    for _ in range(replays):
+        y_host.copy_(g(x_host), non_blocking=True)
+    ee1.record(stream)
+    sync_all()
+    ms_e2e = ee0.elapsed_time(ee1)
+
+    if world > 1:
+        t = torch.tensor([ms_total, ms_e2e, float(code_bytes)], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e, max_code = (float(v) for v in t.tolist())
+        tot = torch.tensor([float(code_bytes)], device=device, dtype=torch.float64)
+        dist.all_reduce(tot)
+        sum_code = float(tot.item())
+    else:
+        max_code = sum_code = float(code_bytes)
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        tokens_per_s = T * steps / (ms_total * 1e-3)
+        passes = replays
+        gbs = (sum_code + world * other_bytes) * passes / (ms_total * 1e-3) / 1e9
+        line = {
+            "metric": "MoE decode-layer tokens/s" if not full_step else "MoE decode-step tokens/s",
+            "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 weights, f32 accumulate", "data": "synthetic",
+            "config": {
+                "workload": (f"moe35b_step_decode_b{T}" if full_step else f"moe35b_layer_decode_t{T}"),
+                "experts": "256 routed 2-bit (2048->1024, 512->2048), top-8, int8 shared expert"
+                           + ("; int8 q/k/v/o 2048->{4096,512,512}, 4096->2048" if full_step else ""),
+                "tokens": T, "layers_resident": MOE_LAYERS,
+                "parallelism": f"ep{world}" if world > 1 else "single GPU",
+                "routed_experts_per_layer_avg": routed / MOE_LAYERS,
+                "max_over_mean_code_bytes_per_gpu": (max_code * world / sum_code) if sum_code else None,
+                "l2_policy": f"{MOE_LAYERS} layers of distinct weights "
+                             f"({int(code_bytes + other_bytes)} B touched per pass per GPU > L2)"},
+            "e2e": {"value": T * steps / (ms_e2e * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": T * cfg["hidden"] * 2 // steps_per_replay,
+                    "d2h_bytes_per_step": T * cfg["hidden"] * 2 // steps_per_replay},
+            "touched_gb_per_s": gbs, "pct_of_hbm_peak": 100.0 * gbs / (peak * world),
+            "gpu_launches": (7 + (4 if full_step else 0)) * MOE_LAYERS * passes,
+            "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s",
+                         "frac": gbs / world / peak, "traffic": None,
+                         "kernel": "whole step: bytes of routed expert streams, int8 matrices and "
+                                   "router weights touched per GPU / step time",
+                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.cuda.synchronize()
+        g.close()
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------------- GPU side
 
 def main() -> None:
@@ -212,6 +362,10 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "step"],
+                    help="dense: 27B-class layer (default, the headline); moe: one 35B-A3B-class "
+                         "MoE layer at --tokens; step: 40-layer MoE decode step at batch 32")
+    ap.add_argument("--tokens", type=int, default=8, help="tokens per step for --workload moe")
     ap.add_argument("--cpu-seconds", type=float, default=10.0,
                     help="bounded CPU-baseline sample (rank 0, N=1)")
     ap.add_argument("--only", default=None,
@@ -223,6 +377,9 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload != "dense":
+        run_moe(args, rank, world, local_rank)
         return
 
     import torch

@@ -252,6 +252,17 @@ __device__ __forceinline__ void cp_async_wait() {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+// Programmatic dependent launch.  launch_dependents: the next kernel in the stream
+// may be scheduled once every CTA of this grid has executed it (or exited).  wait:
+// blocks until the kernels this grid depends on have completed and their writes are
+// visible; a no-op for a grid launched without a programmatic dependency.
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }

@@ -35,6 +35,9 @@
 //    Partials go to caller-provided scratch; the CTA that arrives last for an
 //    output block sums them in ascending split order (no float atomics), so the
 //    result is bit-reproducible run to run for a given (shape, splits).
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -171,6 +174,16 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     const uint32_t ocb = gocb - pr.ocb0;
     const uint32_t OC = pr.OC, TN = OC >> 4;
 
+    // Programmatic dependent launch: let the next kernel of the stream be scheduled
+    // as soon as every CTA of this one has started, so that its start-up overlaps
+    // this kernel's tail.  Everything a launch reads that an earlier kernel may have
+    // written sits behind grid_dependency_wait(): the row jobs right here, the
+    // activations below.  With kPdlPrefetch the producer warp of a dense launch does
+    // not wait: it streams weights (which nothing in flight writes) while the
+    // previous kernel drains.
+    if (p.pdl != kPdlOff) grid_launch_dependents();
+    if (p.pdl == kPdlWaitFirst || (p.pdl == kPdlPrefetch && p.jobs)) grid_dependency_wait();
+
     int expert = 0, nrows, xrows;
     if (p.jobs) {
         const RowJob* jb = p.jobs + job;
@@ -255,6 +268,8 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     const ShiftMuls muls{p.mul2, p.mul4, p.mul16, p.mul32, p.mul64, p.mul128};
     const uint32_t* const wa0 = s_code + warp * WPT + lc.ia();
     const uint32_t* const wb0 = s_code + warp * WPT + lc.ib();
+
+    if (p.pdl == kPdlPrefetch && !p.jobs) grid_dependency_wait();
 
     bool ok = true;
     uint32_t slot = 0, phase = 0;
@@ -380,12 +395,35 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    dim3 grid(p.total_ocb, p.splits, p.njobs), block(kThreads);
-    gemv_mma_kernel<K, MT><<<grid, block, smem, st>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.total_ocb, p.splits, p.njobs);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl != kPdlOff ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<K, MT>, p);
 }
 
 }  // namespace
+
+// ESCHA_B200_PDL = off | wait (default) | prefetch: how launches use programmatic
+// dependent launch; read once per process.  "prefetch" lets a dense launch read its
+// weight stream before the previous kernel of the stream has finished, so it is only
+// for callers whose weights are not written by work still in flight.
+static int pdl_mode() {
+    static const int mode = [] {
+        const char* v = std::getenv("ESCHA_B200_PDL");
+        if (!v) return static_cast<int>(kPdlWaitFirst);
+        if (!std::strcmp(v, "off")) return static_cast<int>(kPdlOff);
+        if (!std::strcmp(v, "prefetch")) return static_cast<int>(kPdlPrefetch);
+        return static_cast<int>(kPdlWaitFirst);
+    }();
+    return mode;
+}
 
 size_t gemv_mma_part_floats(int njobs, int splits, int total_ocb, int rows_per_job) {
     if (splits <= 1) return 0;
@@ -397,6 +435,7 @@ cudaError_t launch_gemv_mma(const GemvMmaParams& params, cudaStream_t st) {
     const int rows = p.rows_per_job;
     const int xrows = p.jobs ? rows : (p.M < rows ? p.M : rows);
     p.xcb = x_chunk_blocks(xrows);
+    p.pdl = pdl_mode();
     if (p.K == 2) return rows == 8 ? launch_t<2, 1>(p, xrows, st) : launch_t<2, 2>(p, xrows, st);
     return rows == 8 ? launch_t<3, 1>(p, xrows, st) : launch_t<3, 2>(p, xrows, st);
 }

@@ -38,6 +38,14 @@ enum GemvInput : int {
     kInputSwiglu = 2,       // raw input is f16(f16(silu(x)) * x_up); then as kInputRaw
 };
 
+// How a launch uses programmatic dependent launch (the next kernel of a stream is
+// scheduled while the previous one drains).
+enum GemvPdl : int {
+    kPdlOff = 0,        // ordinary stream order
+    kPdlWaitFirst = 1,  // early scheduling only: every thread waits for the previous kernel first
+    kPdlPrefetch = 2,   // dense launches also stream weights before that wait
+};
+
 struct GemvMmaParams {
     GemvProblem prob[kMaxProblems];
     int nprob;
@@ -56,6 +64,7 @@ struct GemvMmaParams {
     int njobs;                // grid.z
     int input;                // GemvInput
     int xcb;                  // activation blocks staged per chunk (set by the launcher)
+    int pdl;                  // GemvPdl (set by the launcher)
     float rs;
     // codebook constants 0x8FFF8FFF / 0x3B603B60, passed as run-time values so the
     // decode's (p & mask) ^ x stays a single three-input logic instruction

@@ -76,24 +76,39 @@ class EschaExperts:
     """Container for one projection's E-stacked arrays (kept off the module
     parameter tree via leading-underscore attributes on the owner)."""
 
-    def __init__(self, code_i16: np.ndarray, rin: np.ndarray, rout: np.ndarray,
-                 device=None) -> None:
-        if np.ndim(code_i16) != 4:
-            raise ValueError(f"E-stacked code must be [E, TK, TN, 16K], got shape {np.shape(code_i16)}")
-        e, tk, tn, wpt2 = code_i16.shape
-        if wpt2 % 16:
-            raise ValueError(f"escha code last dim must be 16*K, got {wpt2}")
-        self.K = wpt2 // 16
+    def __init__(self, code_i16, rin, rout, device=None) -> None:
+        if isinstance(code_i16, torch.Tensor):
+            # already packed and resident: [E, TK, TN, 8K] 32-bit words with f32
+            # [E, IC] / [E, OC] vectors on the same device
+            if code_i16.dim() != 4 or code_i16.dtype != torch.int32 or code_i16.shape[-1] % 8:
+                raise ValueError("packed E-stacked code must be an int32 [E, TK, TN, 8K] tensor, "
+                                 f"got {code_i16.dtype} {tuple(code_i16.shape)}")
+            e, tk, tn, wpt = code_i16.shape
+            self.K = wpt // 8
+            packed = code_i16
+        else:
+            if np.ndim(code_i16) != 4:
+                raise ValueError(f"E-stacked code must be [E, TK, TN, 16K], got shape {np.shape(code_i16)}")
+            e, tk, tn, wpt2 = code_i16.shape
+            if wpt2 % 16:
+                raise ValueError(f"escha code last dim must be 16*K, got {wpt2}")
+            self.K = wpt2 // 16
+            packed = None
         if self.K not in (2, 3):
             raise ValueError(f"escha code implies K={self.K}; this runtime implements K in [2, 3]")
         self.E, self.IC, self.OC = e, tk * 16, tn * 16
         if self.IC % 128 or self.OC % 128:
             raise ValueError(
                 f"escha expert dimensions must be multiples of 128, got {self.IC}x{self.OC}")
-        if np.shape(rin) != (e, self.IC) or np.shape(rout) != (e, self.OC):
+        if tuple(np.shape(rin)) != (e, self.IC) or tuple(np.shape(rout)) != (e, self.OC):
             raise ValueError(
-                f"transform vectors {np.shape(rin)}/{np.shape(rout)} do not match the "
+                f"transform vectors {tuple(np.shape(rin))}/{tuple(np.shape(rout))} do not match the "
                 f"E-stacked stream's ({e}, {self.IC})/({e}, {self.OC})")
+        if packed is not None:
+            self.code = packed.contiguous()
+            self.rin = rin.to(device=packed.device, dtype=torch.float32).contiguous()
+            self.rout = rout.to(device=packed.device, dtype=torch.float32).contiguous()
+            return
         self.code = msl.code_tensor(code_i16, device)                     # [E, TK, TN, 8K] words
         dev = self.code.device
         self.rin = torch.from_numpy(np.asarray(rin).astype(np.float32)).to(dev)    # [E, IC] f32

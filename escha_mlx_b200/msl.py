@@ -89,8 +89,8 @@ def split_k_for(m: int, oc: int, tk: int, njobs: int = 1) -> int:
     """Split factor for an [m, tk*16] x [tk*16, oc] coded product (:1191-1226).
 
     ``ESCHA_MLX_SPLITK``: an integer pins it, ``auto`` (default) fills the GPU:
-    enough splits for two resident CTAs per SM, at least two 128-channel blocks
-    per split.  Depends on the shape only -- never on the data and, for a dense
+    as many splits as fit the three resident CTAs per SM without exceeding them,
+    at least two 128-channel blocks per split.  Depends on the shape only -- never on the data and, for a dense
     stream, not on m -- so results are reproducible and batch-invariant.
     """
     setting = envs.ESCHA_MLX_SPLITK.get()

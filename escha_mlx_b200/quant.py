@@ -67,9 +67,19 @@ def w8a16(x: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor) -> torch.Tenso
 class EschaQ8Linear(torch.nn.Module):
     """An int8-weight linear with per-output-row scale (reference :129-143)."""
 
-    def __init__(self, w8: np.ndarray, scale: np.ndarray, group_size: int = DEFAULT_GROUP,
-                 device=None) -> None:
+    def __init__(self, w8, scale, group_size: int = DEFAULT_GROUP, device=None) -> None:
         super().__init__()
+        if isinstance(w8, torch.Tensor):
+            # leaves already resident: int8 [N, K] and one scale per output row
+            if w8.dtype != torch.int8 or w8.dim() != 2 or w8.shape[1] % 16:
+                raise ValueError("weight_int8 must be a 2-D int8 tensor with a multiple of 16 "
+                                 f"input channels, got {w8.dtype} {tuple(w8.shape)}")
+            if tuple(scale.shape) != (w8.shape[0],):
+                raise ValueError(f"weight_scale must have shape ({w8.shape[0]},), got {tuple(scale.shape)}")
+            self._w8 = w8.contiguous()
+            self._scale = scale.to(device=w8.device, dtype=torch.float16).contiguous()
+            self.out_features, self.in_features = w8.shape
+            return
         pw, ps = pack_q8(w8, scale, group_size)
         validate_pack(w8, scale, (pw, ps))
         dev = device or "cuda"

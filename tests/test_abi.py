@@ -63,8 +63,12 @@ def test_pure_helpers():
     from escha_mlx_b200._lib import lib
     assert lib.escha_moe_jobs_bound(512, 256, 8) == (512 + 256 * 7) // 8
     assert lib.escha_moe_jobs_bound(8, 256, 8) == 8
-    # 4096x4096: 32 output blocks -> ceil(296/32) = 10 splits on a 148-SM part
-    assert lib.escha_coded_gemv_splits(4096, 4096, 1, 148) == 10
+    # 4096x4096: 32 output blocks -> floor(3*148/32) = 13 splits fill a 148-SM part's
+    # 444 resident-CTA slots without exceeding them
+    assert lib.escha_coded_gemv_splits(4096, 4096, 1, 148) == 13
+    assert lib.escha_coded_gemv_splits(5120, 17408, 1, 148) == 3
+    assert lib.escha_coded_gemv_splits(17408, 5120, 1, 148) == 11
+    assert lib.escha_coded_gemv_splits(5120, 17408 * 4, 1, 148) == 1
     # never fewer than two 128-channel blocks per split
     assert lib.escha_coded_gemv_splits(512, 128, 1, 148) == 2
     assert lib.escha_coded_gemv_workspace_bytes(1, 4096, 1, 8) == 0
