@@ -64,6 +64,9 @@ cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 // sharing one workspace.
 constexpr size_t kCounterBytes = size_t(1) << 20;
 constexpr size_t kMaxCounters = kCounterBytes / sizeof(int32_t);
+// escha_moe_route's counters (one per tile of 8 tokens + one) at the end of the region
+constexpr size_t kRouteTiles = 4096;
+constexpr size_t kRouteCounters = kRouteTiles + 1;
 
 }  // namespace
 
@@ -216,6 +219,17 @@ int escha_w8a16(const void* x, const void* w8, const void* scale, int M, int N, 
     REQUIRE_PTR(w8);
     REQUIRE(scale != nullptr && y != nullptr, "%s: NULL pointer", __func__);
     REQUIRE((M + 7) / 8 <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
+    if (escha::w8a16_mma_supports(N, Kd)) {
+        escha::Q8Params q{};
+        q.x = static_cast<const __half*>(x);
+        q.w8 = static_cast<const int8_t*>(w8);
+        q.scale = static_cast<const __half*>(scale);
+        q.y = static_cast<__half*>(y);
+        q.M = M; q.N = N; q.Kd = Kd;
+        q.input = escha::kQ8InputPlain;
+        q.epilogue = escha::kQ8StorePlain;
+        return cuda_result(escha::launch_w8a16_mma(q, as_stream(stream)), "escha_w8a16");
+    }
     return cuda_result(
         escha::launch_w8a16(static_cast<const __half*>(x), static_cast<const int8_t*>(w8),
                             static_cast<const __half*>(scale), static_cast<__half*>(y), M, N, Kd,
@@ -368,7 +382,8 @@ int escha_coded_projections(const void* x, const void* const* x_proj, const void
         REQUIRE_PTR(workspace);
         REQUIRE(workspace_bytes >= need, "%s: workspace of %zu bytes is smaller than the %zu needed",
                 __func__, workspace_bytes, need);
-        REQUIRE(static_cast<size_t>(njobs) * total_ocb <= kMaxCounters,
+        // the tail of the counter region belongs to escha_moe_route
+        REQUIRE(static_cast<size_t>(njobs) * total_ocb <= kMaxCounters - kRouteCounters,
                 "%s: %d jobs x %d output blocks exceed the %zu split-K counters", __func__, njobs,
                 total_ocb, kMaxCounters);
         p.counters = static_cast<int32_t*>(workspace);
@@ -457,6 +472,82 @@ int escha_moe_combine(const void* d16, const float* scores, int T, int top_k, in
     return cuda_result(escha::launch_moe_combine(static_cast<const __half*>(d16), scores, T, top_k,
                                                  H, static_cast<__half*>(y), as_stream(stream)),
                        "escha_moe_combine");
+}
+
+int escha_moe_route(const void* x, const void* gate_w, const void* shg_w, const int32_t* ids_in,
+                    int T, int H, int E, int top_k, int e_lo, int e_hi, int rows_per_job,
+                    int32_t* ids, float* scores, float* shared_gate_logit, float* logits_scratch,
+                    void* jobs, int njobs_cap, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+    REQUIRE(T >= 1 && E >= 1 && top_k >= 1, "%s: empty input (T=%d E=%d top_k=%d)", __func__, T, E,
+            top_k);
+    REQUIRE(H >= 8 && H % 8 == 0, "%s: hidden size must be a positive multiple of 8, got %d",
+            __func__, H);
+    REQUIRE(top_k <= 16 && top_k <= E, "%s: top_k=%d outside [1, min(16, E)]", __func__, top_k);
+    REQUIRE(E <= 1024, "%s: E=%d exceeds 1024", __func__, E);
+    REQUIRE(static_cast<size_t>((T + 7) / 8) <= kRouteTiles, "%s: T=%d exceeds %zu tokens", __func__,
+            T, kRouteTiles * 8);
+    REQUIRE(0 <= e_lo && e_lo < e_hi && e_hi <= E, "%s: expert range [%d, %d) outside [0, %d)",
+            __func__, e_lo, e_hi, E);
+    REQUIRE_PTR(x);
+    if (ids_in == nullptr) {
+        REQUIRE_PTR(gate_w);
+        REQUIRE(ids && scores && logits_scratch,
+                "%s: ids, scores and logits_scratch are required when ids_in is NULL", __func__);
+    }
+    if (shg_w) REQUIRE(shared_gate_logit != nullptr, "%s: shared_gate_logit is NULL", __func__);
+    if (jobs) {
+        REQUIRE(rows_per_job == 8 || rows_per_job == 16, "%s: rows per job must be 8 or 16, got %d",
+                __func__, rows_per_job);
+        REQUIRE(njobs_cap >= escha_moe_jobs_bound(T * top_k, e_hi - e_lo, rows_per_job),
+                "%s: njobs_cap=%d is below the bound %d", __func__, njobs_cap,
+                escha_moe_jobs_bound(T * top_k, e_hi - e_lo, rows_per_job));
+        REQUIRE(escha::route_shared_bytes(T, top_k, e_lo, e_hi) <= 200 * 1024,
+                "%s: %d rows exceed the grouping phase's shared memory", __func__, T * top_k);
+    }
+    REQUIRE_PTR(workspace);
+    REQUIRE(workspace_bytes >= kCounterBytes, "%s: workspace of %zu bytes is smaller than the %zu "
+            "counter region", __func__, workspace_bytes, kCounterBytes);
+    escha::RouteParams p{};
+    p.x = static_cast<const __half*>(x);
+    p.gate_w = static_cast<const __half*>(gate_w);
+    p.shg_w = static_cast<const __half*>(shg_w);
+    p.ids_in = ids_in;
+    p.T = T; p.H = H; p.E = E; p.top_k = top_k;
+    p.e_lo = e_lo; p.e_hi = e_hi;
+    p.R = rows_per_job;
+    p.ids = ids; p.scores = scores; p.slog = shared_gate_logit; p.logits = logits_scratch;
+    p.jobs = static_cast<escha::RowJob*>(jobs);
+    p.njobs_cap = njobs_cap;
+    p.counter = static_cast<int32_t*>(workspace) + (kMaxCounters - kRouteCounters);
+    return cuda_result(escha::launch_moe_route(p, as_stream(stream)), "escha_moe_route");
+}
+
+int escha_moe_shared_finish(const void* gu, const void* w8, const void* scale, const void* d16,
+                            const float* scores, const float* shared_gate_logit, int T, int top_k,
+                            int H, int I, void* out, void* stream) {
+    REQUIRE(T >= 1 && top_k >= 1, "%s: empty input (T=%d top_k=%d)", __func__, T, top_k);
+    REQUIRE(escha::w8a16_mma_supports(H, I), "%s: needs H %% 16 == 0 and I %% 64 == 0, got H=%d I=%d",
+            __func__, H, I);
+    REQUIRE_PTR(gu);
+    REQUIRE_PTR(w8);
+    REQUIRE_PTR(d16);
+    REQUIRE_PTR(out);
+    REQUIRE(scale && scores && shared_gate_logit, "%s: NULL pointer", __func__);
+    REQUIRE((T + 31) / 32 <= 65535, "%s: T=%d exceeds the launch grid", __func__, T);
+    escha::Q8Params q{};
+    q.x = static_cast<const __half*>(gu);
+    q.w8 = static_cast<const int8_t*>(w8);
+    q.scale = static_cast<const __half*>(scale);
+    q.y = static_cast<__half*>(out);
+    q.M = T; q.N = H; q.Kd = I;
+    q.input = escha::kQ8InputSwiglu;
+    q.epilogue = escha::kQ8StoreGatedAdd;
+    q.d16 = static_cast<const __half*>(d16);
+    q.scores = scores;
+    q.gate_logit = shared_gate_logit;
+    q.top_k = top_k;
+    return cuda_result(escha::launch_w8a16_mma(q, as_stream(stream)), "escha_moe_shared_finish");
 }
 
 }  // extern "C"

@@ -73,6 +73,42 @@ struct GemvMmaParams {
     uint32_t mul2, mul4, mul16, mul32, mul64, mul128;
 };
 
+// Router + grouping launch (route.cu).
+struct RouteParams {
+    const __half* x;         // [T, H]
+    const __half* gate_w;    // [E, H]; unused when ids_in is given
+    const __half* shg_w;     // [H] shared expert's gate vector, or nullptr
+    const int32_t* ids_in;   // [T, top_k] routing decided by the caller, or nullptr
+    int T, H, E, top_k;
+    int e_lo, e_hi;          // this rank's experts; rows of other experts get no job
+    int R;                   // rows per job (8 or 16)
+    int32_t* ids;            // out [T, top_k] (unused with ids_in)
+    float* scores;           // out [T, top_k] (unused with ids_in)
+    float* slog;             // out [T] f32(f16(x . shg_w)) (unused without shg_w)
+    float* logits;           // scratch [T, E] f32 (unused with ids_in)
+    RowJob* jobs;            // out [njobs_cap], or nullptr to skip the grouping
+    int njobs_cap;
+    int32_t* counter;        // one int32, zero on entry, zero on exit
+};
+
+enum Q8Input : int { kQ8InputPlain = 0, kQ8InputSwiglu = 1 };
+enum Q8Store : int { kQ8StorePlain = 0, kQ8StoreGatedAdd = 1 };
+
+// int8 linear launch (w8a16_mma.cu).
+struct Q8Params {
+    const __half* x;          // [M, Kd], or the merged gate/up rows [M, 2 Kd] for kQ8InputSwiglu
+    const int8_t* w8;         // [N, Kd]
+    const __half* scale;      // [N]
+    __half* y;                // [M, N]
+    int M, N, Kd;
+    int input, epilogue;
+    // kQ8StoreGatedAdd only:
+    const __half* d16;        // [M * top_k, N] expert outputs, (token, slot) rows token-major
+    const float* scores;      // [M * top_k]
+    const float* gate_logit;  // [M]
+    int top_k;
+};
+
 cudaError_t launch_lut_init(__half* lut, cudaStream_t st);
 cudaError_t launch_decode_tiles(const uint32_t* code, int K, int IC, int OC, const __half* lut,
                                 __half* w, cudaStream_t st);
@@ -106,5 +142,10 @@ void set_last_error(const char* msg);
 int coded_gemv_with_scratch(const void* xh, const void* code, const float* rout, int M, int IC,
                             int OC, int K, int splits, float rs, int32_t* counters, float* part,
                             void* out, void* stream);
+
+cudaError_t launch_moe_route(const RouteParams& p, cudaStream_t st);
+size_t route_shared_bytes(int T, int top_k, int e_lo, int e_hi);
+bool w8a16_mma_supports(int N, int Kd);
+cudaError_t launch_w8a16_mma(const Q8Params& p, cudaStream_t st);
 
 }  // namespace escha

@@ -1,0 +1,231 @@
+// Router of the MoE block in one launch: gate logits, top-k, softmax over the k
+// values, the shared expert's gate logit, and the grouping of (token, slot) rows
+// into per-expert jobs for the expert GEMV.
+//
+// Reference: EschaSparseMoeBlock.__call__ / route (escha_mlx/models/
+// qwen3_5_moe.py:255-273; ref.py:326-331): fp32 logits from the fp16 gate linear
+// rounded once through binary16, top-k, softmax over the selected values; and
+// moe.build_groups (escha_mlx/moe.py:30-83) for the grouping.  The reference
+// issues these as half a dozen framework ops; at decode batch sizes each of them
+// costs more to launch than to run, so here they are one kernel:
+//
+//   phase 1 (grid: gate rows x tiles of 8 tokens)  one CTA per (row, tile): its 8
+//                        warps split the hidden dimension, so every lane issues all of
+//                        its loads at once; partial sums meet in shared memory and
+//                        are added in warp order, rounded through binary16.
+//   phase 2 (the last CTA to finish a tile)  one warp per token: k rounds of warp
+//                        arg-max (ties to the lower expert index, i.e. a stable
+//                        descending sort), softmax over the k values.
+//   phase 3 (the last tile to finish)  rows -> RowJobs (ascending expert, ascending
+//                        row inside an expert), restricted to this rank's experts
+//                        [e_lo, e_hi) under expert parallelism.
+//
+// "Last" is decided with one counter per tile plus one for the launch, all zero on
+// entry and left zero.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace escha {
+
+namespace {
+
+constexpr int kMaxExpertsPerLane = 32;  // E <= 1024
+
+__device__ __forceinline__ float round_through_half(float v) {
+    return __half2float(__float2half_rn(v));
+}
+
+__device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc) {
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w}, xx[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 a = __half22float2(as_half2(ww[i])), b = __half22float2(as_half2(xx[i]));
+        acc = __fmaf_rn(a.x, b.x, acc);
+        acc = __fmaf_rn(a.y, b.y, acc);
+    }
+    return acc;
+}
+
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const RouteParams p) {
+    extern __shared__ int32_t s_dyn[];  // phase 3: [El + 1] job offsets, then [m] local experts
+    __shared__ float s_part[8][8];
+    __shared__ int s_flag;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_gate = p.ids_in ? 0 : p.E;
+    const int n_rows = n_gate + (p.shg_w ? 1 : 0);
+    const int r = blockIdx.x, tile = blockIdx.y, t0 = tile * 8;
+    const int n_tiles = gridDim.y;
+
+    // ---- phase 1: this CTA's row against the tile's tokens
+    if (r < n_rows) {
+        const __half* wrow = r < n_gate ? p.gate_w + static_cast<size_t>(r) * p.H : p.shg_w;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+        for (int k = tid * 8; k < p.H; k += 2048) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int tok = min(t0 + j, p.T - 1);
+                const uint4 xv = *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(tok) * p.H + k);
+                acc[j] = dot8(wv, xv, acc[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float a = acc[j];
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, m));
+            if (lane == 0) s_part[warp][j] = a;
+        }
+        __syncthreads();
+        if (tid < 8 && t0 + tid < p.T) {
+            float a = s_part[0][tid];
+#pragma unroll
+            for (int w = 1; w < 8; ++w) a = __fadd_rn(a, s_part[w][tid]);
+            const float v = round_through_half(a);
+            if (r < n_gate) p.logits[static_cast<size_t>(t0 + tid) * p.E + r] = v;
+            else p.slog[t0 + tid] = v;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int32_t* ctr = p.counter + 1 + tile;
+        const int prev = atomicAdd(ctr, 1);
+        const int last = prev == static_cast<int>(gridDim.x) - 1;
+        if (last) *ctr = 0;
+        s_flag = last;
+    }
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+
+    // ---- phase 2: top-k and softmax for the tile's tokens, one warp per token
+    const int tok = t0 + warp;
+    if (!p.ids_in && tok < p.T) {
+        const int per_lane = (p.E + 31) / 32;
+        float v[kMaxExpertsPerLane];
+#pragma unroll
+        for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+            const int e = lane + 32 * i;
+            v[i] = (i < per_lane && e < p.E) ? __ldcg(p.logits + static_cast<size_t>(tok) * p.E + e)
+                                             : -INFINITY;
+        }
+        float my_v = 0.0f, top_v = 0.0f;  // lane s keeps the s-th selection
+        int my_e = 0;
+        for (int s = 0; s < p.top_k; ++s) {
+            float bv = -INFINITY;
+            int be = 0x7FFFFFFF;
+#pragma unroll
+            for (int i = 0; i < kMaxExpertsPerLane; ++i)
+                if (i < per_lane && v[i] > bv) { bv = v[i]; be = lane + 32 * i; }
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) {
+                const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, m);
+                const int oe = __shfl_xor_sync(0xFFFFFFFFu, be, m);
+                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+            }
+            if (s == 0) top_v = bv;
+            if (lane == s) { my_v = bv; my_e = be; }
+            if ((be & 31) == lane) {
+#pragma unroll
+                for (int i = 0; i < kMaxExpertsPerLane; ++i)
+                    if (i == (be >> 5)) v[i] = -INFINITY;
+            }
+        }
+        // softmax over the k selected values: exp(v - max), summed in selection order
+        const float ex = lane < p.top_k ? expf(__fsub_rn(my_v, top_v)) : 0.0f;
+        float sum = 0.0f;
+        for (int s = 0; s < p.top_k; ++s) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, ex, s));
+        if (lane < p.top_k) {
+            p.ids[static_cast<size_t>(tok) * p.top_k + lane] = my_e;
+            p.scores[static_cast<size_t>(tok) * p.top_k + lane] = __fdiv_rn(ex, sum);
+        }
+    }
+    if (!p.jobs) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(p.counter, 1);
+        const int last = prev == n_tiles - 1;
+        if (last) *p.counter = 0;
+        s_flag = last;
+    }
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+
+    // ---- phase 3: rows -> jobs.  Rows are counted per expert with shared-memory
+    // atomics; then thread e owns local expert e and emits its rows in ascending
+    // order, so jobs ascend by expert and rows ascend inside a job -- the stable order
+    // moe.build_groups produces -- whatever order the atomics ran in.
+    const int32_t* row_ids = p.ids_in ? p.ids_in : p.ids;
+    const int m = p.T * p.top_k, El = p.e_hi - p.e_lo, R = p.R;
+    int32_t* s_off = s_dyn;            // [El + 1]
+    int32_t* s_loc = s_dyn + El + 1;   // [m] local expert of each row, -1 if another rank's
+    for (int e = tid; e <= El; e += blockDim.x) s_off[e] = 0;
+    __syncthreads();
+    for (int i = tid; i < m; i += blockDim.x) {
+        const int e = __ldcg(row_ids + i);
+        const int loc = (e >= p.e_lo && e < p.e_hi) ? e - p.e_lo : -1;
+        s_loc[i] = loc;
+        if (loc >= 0) atomicAdd(&s_off[loc + 1], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int e = 0; e < El; ++e) {
+            run += (s_off[e + 1] + R - 1) / R;
+            s_off[e + 1] = run;
+        }
+    }
+    __syncthreads();
+    const int total = s_off[El];
+    for (int e = tid; e < El; e += blockDim.x) {
+        const int base = s_off[e], njobs_e = s_off[e + 1] - base;
+        if (njobs_e == 0) continue;
+        int k = 0;
+        for (int i = 0; i < m; ++i) {
+            if (s_loc[i] != e) continue;
+            const int j = base + k / R;
+            if (j < p.njobs_cap) {
+                p.jobs[j].rows[k % R] = i;
+                if (k % R == 0) p.jobs[j].expert = e;
+                p.jobs[j].nrows = k % R + 1;  // ascending k: the last write is the count
+            }
+            ++k;
+        }
+    }
+    for (int j = total + tid; j < p.njobs_cap; j += blockDim.x) {
+        p.jobs[j].expert = 0;
+        p.jobs[j].nrows = 0;
+    }
+}
+
+}  // namespace
+
+size_t route_shared_bytes(int T, int top_k, int e_lo, int e_hi) {
+    return (static_cast<size_t>(e_hi - e_lo) + 1 + static_cast<size_t>(T) * top_k) * sizeof(int32_t);
+}
+
+cudaError_t launch_moe_route(const RouteParams& p, cudaStream_t st) {
+    const int n_rows = (p.ids_in ? 0 : p.E) + (p.shg_w ? 1 : 0);
+    const dim3 grid(n_rows > 0 ? n_rows : 1, (p.T + 7) / 8);
+    const size_t smem = route_shared_bytes(p.T, p.top_k, p.e_lo, p.e_hi);
+    static size_t configured[64] = {0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || smem > configured[dev])) {
+        e = cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = smem;
+    }
+    moe_route_kernel<<<grid, 256, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace escha

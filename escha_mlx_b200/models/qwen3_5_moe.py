@@ -67,6 +67,9 @@ class EschaSparseMoeBlock(torch.nn.Module):
         self.sh_gate = quant.make_linear(shared["gate_w8"], shared["gate_scale"], group_size, dev)
         self.sh_up = quant.make_linear(shared["up_w8"], shared["up_scale"], group_size, dev)
         self.sh_down = quant.make_linear(shared["down_w8"], shared["down_scale"], group_size, dev)
+        # gate and up of the shared expert as one [2I, H] matrix: one launch, merged output
+        self._sh_gu_w8 = torch.cat([self.sh_gate._w8, self.sh_up._w8]).contiguous()
+        self._sh_gu_scale = torch.cat([self.sh_gate._scale, self.sh_up._scale]).contiguous()
         self._mode = "fused"
         self._fused_had = msl.use_fused_had()
         self._block_env = envs.ESCHA_MLX_BLOCK_R.get()
@@ -115,9 +118,13 @@ class EschaSparseMoeBlock(torch.nn.Module):
     def _sharded(self) -> bool:
         return (self._e_hi - self._e_lo) != self.num_experts
 
-    def _expert_path(self, xf: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
-        t = xf.shape[0]
-        row_expert, row_token = self._rows(xf, ids)
+    def _expert_rows(self, xf: torch.Tensor, ids: torch.Tensor,
+                     jobs: torch.Tensor | None = None) -> torch.Tensor:
+        """Expert outputs d16 [T*top_k, H] f16 for the (token, slot) rows, complete on
+        every rank (under expert parallelism the owners' rows are all-gathered).
+        ``jobs`` are the row jobs of this rank's experts when the router launch has
+        already built them."""
+        row_expert = ids.reshape(xf.shape[0] * self.top_k).to(torch.int32)
         m = row_expert.shape[0]
         owned = None
         job_expert = row_expert
@@ -133,7 +140,8 @@ class EschaSparseMoeBlock(torch.nn.Module):
         if msl.gemv_family() == "mma" and self._fused_had:
             # two launches: each leg's input transform (with the token gather, resp.
             # the SwiGLU), product and output transform in one kernel
-            jobs = msl.group_rows(job_expert, gu.E)
+            if jobs is None:
+                jobs = msl.group_rows(job_expert, gu.E)
             zeros = (lambda oc: [torch.zeros((m, oc), dtype=torch.float16, device=xf.device)]) \
                 if owned is not None else (lambda oc: None)
             gu16 = msl.coded_projections(xf, [gu.code], [gu.rin], [gu.rout], gu.K, gu.IC, [gu.OC],
@@ -147,12 +155,18 @@ class EschaSparseMoeBlock(torch.nn.Module):
                                         x_stride=2 * inter, outs=zeros(dn.OC))[0]
         else:
             jobs = msl.group_rows(job_expert, gu.E) if msl.gemv_family() == "mma" else None
+            _, row_token = self._rows(xf, ids)
             rows = xf[row_token.long()]
             gu16 = self._leg(rows, row_expert, gu, jobs)
             h = msl.swiglu(gu16)
             d16 = self._leg(h, row_expert, dn, jobs)
         if owned is not None:
             d16 = sharding.all_gather_rows_by_owner(d16, owned)
+        return d16
+
+    def _expert_path(self, xf: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
+        t = xf.shape[0]
+        d16 = self._expert_rows(xf, ids)
         y16 = msl.moe_combine(d16, scores.reshape(t * self.top_k).to(torch.float32).contiguous(),
                               t, self.top_k)
         # the routed-expert sum is rounded to f16 before the shared expert is added
@@ -166,11 +180,32 @@ class EschaSparseMoeBlock(torch.nn.Module):
         scores = torch.softmax(top, dim=-1)
         return ids, scores
 
+    def _single_pass(self) -> bool:
+        """Whether the block runs as router -> two expert legs -> shared gate/up ->
+        tail (six launches) instead of the op-by-op composition."""
+        return (msl.gemv_family() == "mma" and self._fused_had
+                and self.num_experts <= msl.ROUTE_MAX_EXPERTS and self.top_k <= msl.ROUTE_MAX_TOP_K
+                and self._sh_gu_w8.shape[1] % 64 == 0 and self.sh_down.in_features % 64 == 0
+                and self.sh_down.out_features % 16 == 0 and self._sh_gu_w8.shape[0] % 16 == 0)
+
     def forward(self, x: torch.Tensor, ids: torch.Tensor | None = None,
                 scores: torch.Tensor | None = None) -> torch.Tensor:
         shape = x.shape
         hdim = shape[-1]
         xf = x.reshape(-1, hdim).to(torch.float16).contiguous()
+        if self._single_pass():
+            t = xf.shape[0]
+            ids_r, scores_r, slog, jobs = msl.moe_route(
+                xf, self.gate_weight, self.shared_expert_gate_weight.reshape(-1), self.top_k,
+                self.num_experts, ids=ids, expert_range=(self._e_lo, self._e_hi))
+            if ids is None:
+                scores = scores_r
+            d16 = self._expert_rows(xf, ids_r, jobs)
+            gu_sh = quant.w8a16(xf, self._sh_gu_w8, self._sh_gu_scale)
+            out = msl.moe_shared_finish(
+                gu_sh, self.sh_down._w8, self.sh_down._scale, d16,
+                scores.reshape(t * self.top_k).to(torch.float32).contiguous(), slog, self.top_k)
+            return out.to(x.dtype).reshape(shape)
         if ids is None:
             ids, scores = self.route(xf)
         y = self._expert_path(xf, ids, scores)

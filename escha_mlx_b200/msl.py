@@ -545,3 +545,60 @@ def moe_combine(d16: torch.Tensor, scores: torch.Tensor, T: int, top_k: int) -> 
     check(lib.escha_moe_combine(ptr(d16, torch.float16), ptr(scores, torch.float32), T, top_k, H,
                                 ptr(y), stream()))
     return y
+
+
+ROUTE_MAX_EXPERTS, ROUTE_MAX_TOP_K = 1024, 16
+
+
+def moe_route(x: torch.Tensor, gate_w: torch.Tensor | None, shg_w: torch.Tensor | None, top_k: int,
+              E: int, ids: torch.Tensor | None = None, expert_range: tuple[int, int] | None = None,
+              R: int = 8, group: bool = True):
+    """Router, shared-gate logit and row grouping in one launch
+    (models/qwen3_5_moe.py:255-268 + moe.py:30-83).
+
+    x [T, H] f16.  With ``ids`` None the routing is computed from ``gate_w`` [E, H]:
+    returns ``(ids [T, k] i32, scores [T, k] f32, shared_gate_logit [T] f32 | None,
+    jobs | None)``; with ``ids`` given only the logit and the jobs are produced and
+    ``scores`` comes back None.  ``expert_range`` restricts the jobs to this rank's
+    experts (local indices)."""
+    T, H = x.shape
+    dev = x.device
+    lo, hi = expert_range or (0, E)
+    ids_in = None
+    if ids is not None:
+        ids_in = ids.to(torch.int32).contiguous()
+        out_ids = out_scores = scratch = None
+    else:
+        out_ids = torch.empty((T, top_k), dtype=torch.int32, device=dev)
+        out_scores = torch.empty((T, top_k), dtype=torch.float32, device=dev)
+        scratch = torch.empty((T, E), dtype=torch.float32, device=dev)
+    slog = torch.empty((T,), dtype=torch.float32, device=dev) if shg_w is not None else None
+    jobs, cap = None, 0
+    if group:
+        cap = jobs_bound(T * top_k, hi - lo, R)
+        jobs = torch.empty((cap, JOB_INTS), dtype=torch.int32, device=dev)
+    ws = workspaces.get(1 << 20, dev)
+    check(lib.escha_moe_route(ptr(x, torch.float16),
+                              ptr(gate_w, torch.float16) if gate_w is not None else None,
+                              ptr(shg_w, torch.float16) if shg_w is not None else None,
+                              ptr(ids_in), T, H, E, top_k, lo, hi, R, ptr(out_ids), ptr(out_scores),
+                              ptr(slog), ptr(scratch), ptr(jobs), cap, ptr(ws),
+                              ctypes.c_size_t(ws.numel()), stream()))
+    return (ids_in if ids is not None else out_ids), out_scores, slog, jobs
+
+
+def moe_shared_finish(gu: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor, d16: torch.Tensor,
+                      scores: torch.Tensor, shared_gate_logit: torch.Tensor, top_k: int) -> torch.Tensor:
+    """Shared expert's SwiGLU + down linear, routed-expert combine and the gated add
+    in one launch -> out f16 [T, H] (models/qwen3_5_moe.py:227-273)."""
+    T, two_i = gu.shape
+    H, inter = w8.shape
+    if two_i != 2 * inter or d16.shape != (T * top_k, H):
+        raise ValueError(f"shapes do not form a shared-expert tail: gu {tuple(gu.shape)}, "
+                         f"w8 {tuple(w8.shape)}, d16 {tuple(d16.shape)}, top_k {top_k}")
+    out = torch.empty((T, H), dtype=torch.float16, device=gu.device)
+    check(lib.escha_moe_shared_finish(ptr(gu, torch.float16), ptr(w8, torch.int8),
+                                      ptr(scale, torch.float16), ptr(d16, torch.float16),
+                                      ptr(scores, torch.float32), ptr(shared_gate_logit, torch.float32),
+                                      T, top_k, H, inter, ptr(out), stream()))
+    return out

@@ -72,7 +72,7 @@ def moe_weights(rng: np.random.Generator, E: int, H: int, I: int, Kg: int = 2, K
     return w
 
 
-# The five benchmark configurations (shapes only; see DESIGN.md for the mapping).
+# Shapes of the published benchmark configurations.
 DENSE_LAYER_27B = (
     # name, IC, OC, K
     ("q_proj", 5120, 6144, 2),

@@ -37,7 +37,9 @@ def _experts(E, ic, oc, k, device, gen) -> moe.EschaExperts:
 
 def _q8(n, kd, device, gen) -> quant.EschaQ8Linear:
     w8 = torch.randint(-127, 128, (n, kd), dtype=torch.int8, device=device, generator=gen)
-    scale = (torch.rand((n,), device=device, generator=gen) * 0.01 + 0.002).half()
+    # uniform int8 has rms ~73: scales near 1 / (73 sqrt(kd)) keep the output at the
+    # input's magnitude, so activations stay in range through a stack of layers
+    scale = ((torch.rand((n,), device=device, generator=gen) + 0.5) / (73.0 * kd ** 0.5)).half()
     return quant.EschaQ8Linear(w8, scale)
 
 

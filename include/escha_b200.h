@@ -238,6 +238,42 @@ int escha_swiglu(const void *gate, const void *up, int M, int I, long stride, vo
 int escha_moe_combine(const void *d16, const float *scores, int T, int top_k, int H, void *y,
                       void *stream);
 
+/* The MoE block's router and row grouping in one launch.  Replaces, for x [T,H]
+ * binary16: the gate linear + top-k + softmax of EschaSparseMoeBlock.__call__
+ * (models/qwen3_5_moe.py:255-262; ref.py:326-331: f32 logits rounded once through
+ * binary16, k largest with ties to the lower expert index, softmax over those k),
+ * the shared expert's gate logit f32(f16(x . shg_w)) (models/qwen3_5_moe.py:268),
+ * and moe.build_groups (moe.py:30-83) as RowJobs for escha_coded_gemv_jobs /
+ * escha_coded_projections.
+ *   gate_w [E,H] binary16, shg_w [H] binary16 or NULL (then no gate logit).
+ *   ids_in NULL: ids [T,top_k] int32 and scores [T,top_k] f32 are written;
+ *     logits_scratch is T*E floats of scratch.  ids_in given (routing decided by
+ *     the caller): gate_w/ids/scores/logits_scratch are ignored.
+ *   jobs NULL skips the grouping; otherwise rows (t*top_k+s) whose expert lies in
+ *     [e_lo, e_hi) -- this rank's shard under expert parallelism, [0,E) otherwise
+ *     -- are grouped under the local expert index e - e_lo, rows_per_job (8 or 16)
+ *     per job, njobs_cap >= escha_moe_jobs_bound(T*top_k, e_hi-e_lo, rows_per_job).
+ *   workspace: the zero-initialised split-K workspace (>= 1 MiB); its last counter
+ *     is used and left zero.
+ * Limits: E <= 1024, top_k <= 16, H a multiple of 8. */
+int escha_moe_route(const void *x, const void *gate_w, const void *shg_w, const int32_t *ids_in,
+                    int T, int H, int E, int top_k, int e_lo, int e_hi, int rows_per_job,
+                    int32_t *ids, float *scores, float *shared_gate_logit, float *logits_scratch,
+                    void *jobs, int njobs_cap, void *workspace, size_t workspace_bytes,
+                    void *stream);
+
+/* The MoE block's tail in one launch (models/qwen3_5_moe.py:227-273; ref.py:333-349):
+ *   hh      = f16( (g * sigmoid(g)) * u ),  g, u = gu[t, :I], gu[t, I:]   (f32 math)
+ *   sh      = w8a16(hh, w8, scale)                       shared expert's down linear
+ *   routed  = f16( sum over slots s ascending of f32(d16[t*top_k+s,:]) * f32(f16(scores)) )
+ *   out[t,:] = f16( f32(routed) + f32(sh) * sigmoid(shared_gate_logit[t]) )
+ * gu [T,2I] binary16 (the shared expert's gate and up outputs side by side),
+ * w8 [H,I] int8, scale [H] binary16, d16 [T*top_k,H] binary16, out [T,H] binary16.
+ * H a multiple of 16, I a multiple of 64. */
+int escha_moe_shared_finish(const void *gu, const void *w8, const void *scale, const void *d16,
+                            const float *scores, const float *shared_gate_logit, int T, int top_k,
+                            int H, int I, void *out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -81,7 +81,9 @@ def moe_inputs():
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to an escha-mlx checkout>")
+    root = sys.argv[1]
     ref = load_ref(root)
     data = os.path.join(root, "tests", "data")
 
