@@ -48,7 +48,7 @@ SIGNATURES = {
     "escha_moe_combine": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "escha_moe_route": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
                             _vp, _i, _vp, _sz, _vp]),
-    "escha_moe_shared_finish": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "escha_moe_shared_finish": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
 }
 
 

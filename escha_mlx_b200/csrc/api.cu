@@ -524,8 +524,11 @@ int escha_moe_route(const void* x, const void* gate_w, const void* shg_w, const 
 }
 
 int escha_moe_shared_finish(const void* gu, const void* w8, const void* scale, const void* d16,
-                            const float* scores, const float* shared_gate_logit, int T, int top_k,
-                            int H, int I, void* out, void* stream) {
+                            const int32_t* ids, int experts_per_rank, const float* scores,
+                            const float* shared_gate_logit, int T, int top_k, int H, int I,
+                            void* out, void* stream) {
+    if (ids) REQUIRE(experts_per_rank >= 1, "%s: experts_per_rank=%d with ids given", __func__,
+                     experts_per_rank);
     REQUIRE(T >= 1 && top_k >= 1, "%s: empty input (T=%d top_k=%d)", __func__, T, top_k);
     REQUIRE(escha::w8a16_mma_supports(H, I), "%s: needs H %% 16 == 0 and I %% 64 == 0, got H=%d I=%d",
             __func__, H, I);
@@ -544,6 +547,8 @@ int escha_moe_shared_finish(const void* gu, const void* w8, const void* scale, c
     q.input = escha::kQ8InputSwiglu;
     q.epilogue = escha::kQ8StoreGatedAdd;
     q.d16 = static_cast<const __half*>(d16);
+    q.ids = ids;
+    q.experts_per_rank = experts_per_rank;
     q.scores = scores;
     q.gate_logit = shared_gate_logit;
     q.top_k = top_k;

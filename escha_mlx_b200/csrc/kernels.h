@@ -103,7 +103,10 @@ struct Q8Params {
     int M, N, Kd;
     int input, epilogue;
     // kQ8StoreGatedAdd only:
-    const __half* d16;        // [M * top_k, N] expert outputs, (token, slot) rows token-major
+    const __half* d16;        // [M * top_k, N] expert outputs, (token, slot) rows token-major;
+                              // with ids: [ranks, M * top_k, N], row r taken from its owner's copy
+    const int32_t* ids;       // [M * top_k] routed expert of each row, or nullptr
+    int experts_per_rank;     // owner of row r = ids[r] / experts_per_rank
     const float* scores;      // [M * top_k]
     const float* gate_logit;  // [M]
     int top_k;

@@ -145,7 +145,12 @@ w8a16_mma_kernel(const Q8Params p) {
             for (int s = 0; s < p.top_k; ++s) {
                 const size_t er = static_cast<size_t>(row) * p.top_k + s;
                 const float w16 = __half2float(__float2half_rn(p.scores[er]));
-                comb = __fadd_rn(comb, __fmul_rn(__half2float(p.d16[er * p.N + n0 + rr]), w16));
+                // expert parallel: every rank's rows were gathered side by side; a row
+                // is valid in the copy of the rank that owns its expert
+                const size_t src = p.ids ? static_cast<size_t>(p.ids[er] / p.experts_per_rank) *
+                                               p.M * p.top_k + er
+                                         : er;
+                comb = __fadd_rn(comb, __fmul_rn(__half2float(p.d16[src * p.N + n0 + rr]), w16));
             }
             const float routed = __half2float(__float2half_rn(comb));
             const float gate = sigmoid_f32(p.gate_logit[row]);

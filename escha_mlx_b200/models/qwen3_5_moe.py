@@ -119,16 +119,17 @@ class EschaSparseMoeBlock(torch.nn.Module):
         return (self._e_hi - self._e_lo) != self.num_experts
 
     def _expert_rows(self, xf: torch.Tensor, ids: torch.Tensor,
-                     jobs: torch.Tensor | None = None) -> torch.Tensor:
+                     jobs: torch.Tensor | None = None, local_only: bool = False) -> torch.Tensor:
         """Expert outputs d16 [T*top_k, H] f16 for the (token, slot) rows, complete on
         every rank (under expert parallelism the owners' rows are all-gathered).
         ``jobs`` are the row jobs of this rank's experts when the router launch has
-        already built them."""
+        already built them.  ``local_only`` (needs ``jobs``): return this rank's buffer
+        as it is -- rows of other ranks' experts are left unwritten."""
         row_expert = ids.reshape(xf.shape[0] * self.top_k).to(torch.int32)
         m = row_expert.shape[0]
         owned = None
         job_expert = row_expert
-        if self._sharded():
+        if self._sharded() and not local_only:
             # rows of experts another rank owns get no job here (expert -1 matches no
             # local expert); their output rows stay zero and are replaced by the
             # owner's rows in the ownership-selecting all-gather below
@@ -200,11 +201,21 @@ class EschaSparseMoeBlock(torch.nn.Module):
                 self.num_experts, ids=ids, expert_range=(self._e_lo, self._e_hi))
             if ids is None:
                 scores = scores_r
-            d16 = self._expert_rows(xf, ids_r, jobs)
-            gu_sh = quant.w8a16(xf, self._sh_gu_w8, self._sh_gu_scale)
-            out = msl.moe_shared_finish(
-                gu_sh, self.sh_down._w8, self.sh_down._scale, d16,
-                scores.reshape(t * self.top_k).to(torch.float32).contiguous(), slog, self.top_k)
+            sc = scores.reshape(t * self.top_k).to(torch.float32).contiguous()
+            if self._sharded():
+                # one collective per block: every rank's buffer side by side; the tail
+                # picks each row from the rank that owns its expert
+                d16 = sharding.all_gather_rows(self._expert_rows(xf, ids_r, jobs, local_only=True))
+                gu_sh = quant.w8a16(xf, self._sh_gu_w8, self._sh_gu_scale)
+                out = msl.moe_shared_finish(
+                    gu_sh, self.sh_down._w8, self.sh_down._scale, d16, sc, slog, self.top_k,
+                    ids=ids_r.reshape(-1).to(torch.int32).contiguous(),
+                    experts_per_rank=self._e_hi - self._e_lo)
+            else:
+                d16 = self._expert_rows(xf, ids_r, jobs)
+                gu_sh = quant.w8a16(xf, self._sh_gu_w8, self._sh_gu_scale)
+                out = msl.moe_shared_finish(gu_sh, self.sh_down._w8, self.sh_down._scale, d16, sc,
+                                            slog, self.top_k)
             return out.to(x.dtype).reshape(shape)
         if ids is None:
             ids, scores = self.route(xf)

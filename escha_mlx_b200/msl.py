@@ -588,17 +588,24 @@ def moe_route(x: torch.Tensor, gate_w: torch.Tensor | None, shg_w: torch.Tensor 
 
 
 def moe_shared_finish(gu: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor, d16: torch.Tensor,
-                      scores: torch.Tensor, shared_gate_logit: torch.Tensor, top_k: int) -> torch.Tensor:
+                      scores: torch.Tensor, shared_gate_logit: torch.Tensor, top_k: int,
+                      ids: torch.Tensor | None = None, experts_per_rank: int = 0) -> torch.Tensor:
     """Shared expert's SwiGLU + down linear, routed-expert combine and the gated add
-    in one launch -> out f16 [T, H] (models/qwen3_5_moe.py:227-273)."""
+    in one launch -> out f16 [T, H] (models/qwen3_5_moe.py:227-273).  Expert
+    parallel: ``d16`` is the all-gathered [ranks * T * top_k, H] buffer and ``ids``
+    [T, top_k] selects each row from the copy of the rank that owns its expert."""
     T, two_i = gu.shape
     H, inter = w8.shape
-    if two_i != 2 * inter or d16.shape != (T * top_k, H):
+    m = T * top_k
+    ranks = d16.shape[0] // m if ids is not None else 1
+    if two_i != 2 * inter or d16.shape != (ranks * m, H):
         raise ValueError(f"shapes do not form a shared-expert tail: gu {tuple(gu.shape)}, "
                          f"w8 {tuple(w8.shape)}, d16 {tuple(d16.shape)}, top_k {top_k}")
     out = torch.empty((T, H), dtype=torch.float16, device=gu.device)
     check(lib.escha_moe_shared_finish(ptr(gu, torch.float16), ptr(w8, torch.int8),
                                       ptr(scale, torch.float16), ptr(d16, torch.float16),
-                                      ptr(scores, torch.float32), ptr(shared_gate_logit, torch.float32),
+                                      ptr(ids, torch.int32) if ids is not None else None,
+                                      int(experts_per_rank), ptr(scores, torch.float32),
+                                      ptr(shared_gate_logit, torch.float32),
                                       T, top_k, H, inter, ptr(out), stream()))
     return out

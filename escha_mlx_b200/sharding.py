@@ -75,6 +75,17 @@ def all_gather_columns(y_local: torch.Tensor, group=None) -> torch.Tensor:
     return flat.view(size, m, oc_local).permute(1, 0, 2).reshape(m, size * oc_local)
 
 
+def all_gather_rows(rows_local: torch.Tensor, group=None) -> torch.Tensor:
+    """Every rank's [m, H] buffer side by side -> [size * m, H] (rank-major)."""
+    rank, size = world()
+    if size == 1:
+        return rows_local
+    m, h = rows_local.shape
+    flat = torch.empty((size * m, h), dtype=rows_local.dtype, device=rows_local.device)
+    dist.all_gather_into_tensor(flat, rows_local.contiguous(), group=group)
+    return flat
+
+
 def all_gather_rows_by_owner(rows_local: torch.Tensor, owned: torch.Tensor, group=None) -> torch.Tensor:
     """Expert-parallel join: every rank computed the rows whose expert it owns
     (``owned`` [m] bool marks them; other rows of ``rows_local`` are ignored).

@@ -269,10 +269,15 @@ int escha_moe_route(const void *x, const void *gate_w, const void *shg_w, const 
  *   out[t,:] = f16( f32(routed) + f32(sh) * sigmoid(shared_gate_logit[t]) )
  * gu [T,2I] binary16 (the shared expert's gate and up outputs side by side),
  * w8 [H,I] int8, scale [H] binary16, d16 [T*top_k,H] binary16, out [T,H] binary16.
+ * Expert parallel (no reference counterpart): with ids [T*top_k] given, d16 is the
+ * all-gathered [ranks, T*top_k, H] buffer and row r is read from the copy of rank
+ * ids[r] / experts_per_rank, the one that computed it; rows a rank does not own are
+ * never read, so they need not be initialised.  ids NULL: a single [T*top_k,H] buffer.
  * H a multiple of 16, I a multiple of 64. */
 int escha_moe_shared_finish(const void *gu, const void *w8, const void *scale, const void *d16,
-                            const float *scores, const float *shared_gate_logit, int T, int top_k,
-                            int H, int I, void *out, void *stream);
+                            const int32_t *ids, int experts_per_rank, const float *scores,
+                            const float *shared_gate_logit, int T, int top_k, int H, int I,
+                            void *out, void *stream);
 
 #ifdef __cplusplus
 }
