@@ -555,4 +555,53 @@ int escha_moe_shared_finish(const void* gu, const void* w8, const void* scale, c
     return cuda_result(escha::launch_w8a16_mma(q, as_stream(stream)), "escha_moe_shared_finish");
 }
 
+int escha_coded_gemm_tc_splits(int IC, int OC, int sm_count) {
+    if (IC < 128 || OC < 128) return 1;
+    if (sm_count <= 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            sm_count = 148;
+    }
+    // one CTA per SM (a CTA holds most of an SM's shared memory): as many splits as keep
+    // the grid within one wave, at least four 64-channel chunks per split
+    long s = sm_count / (OC / 128);
+    const long smax = IC / 256;
+    if (s > smax) s = smax;
+    if (s < 1) s = 1;
+    return static_cast<int>(s);
+}
+
+int escha_coded_gemm_tc(const void* xh, const void* code, int M, int IC, int OC, int K, int splits,
+                        float* planes, float* mid, void* stream) {
+    if (int rc = check_shape(__func__, K, IC, OC, 128)) return rc;
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE_PTR(xh);
+    REQUIRE_PTR(code);
+    REQUIRE_PTR(mid);
+    if (splits <= 0) splits = escha_coded_gemm_tc_splits(IC, OC, 0);
+    REQUIRE(splits <= IC / 64 && splits <= 65535, "%s: splits=%d exceeds the %d 64-channel chunks",
+            __func__, splits, IC / 64);
+    REQUIRE((M + 255) / 256 <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
+    if (splits > 1) REQUIRE_PTR(planes);
+    escha::GemmTcParams p{};
+    p.code = static_cast<const uint32_t*>(code);
+    p.xh = static_cast<const __half*>(xh);
+    p.out = splits > 1 ? planes : mid;
+    p.M = M; p.IC = IC; p.OC = OC; p.K = K; p.splits = splits;
+    p.hash_mask = 0x8FFF8FFFu;
+    p.hash_xor = 0x3B603B60u;
+    p.mul2 = 2u; p.mul4 = 4u; p.mul16 = 16u; p.mul32 = 32u; p.mul64 = 64u; p.mul128 = 128u;
+    cudaError_t e = escha::launch_gemm_tc(p, as_stream(stream));
+    if (e == cudaSuccess && splits > 1)
+        e = escha::launch_sum_planes(planes, mid, static_cast<size_t>(M) * OC, splits, as_stream(stream));
+    return cuda_result(e, "escha_coded_gemm_tc");
+}
+
+int escha_coded_gemm_tc_status(void) {
+    int st = 0;
+    if (escha::gemm_tc_status(&st) != cudaSuccess) return -1;
+    return st;
+}
+
 }  // extern "C"

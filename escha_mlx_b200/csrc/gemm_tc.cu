@@ -1,0 +1,341 @@
+// Prefill row-blocked coded GEMM on the 5th-generation tensor cores:
+//     mid[r, :] = f32(xh[r, :]) @ f32(decode(code))        for M = tens to hundreds of rows
+// -- the product behind dense_gemm_mat / dense_gemm_rows at prefill sizes
+// (escha_mlx/msl.py:1608-1782, :1785-1841 of the reference, which runs it on 8x8
+// simdgroup-matrix fragments with R = 16 rows per decode).
+//
+// At these row counts the decoded tile is a real dense contraction, so the trellis
+// decode and the matrix product are split between the two machines an SM has:
+//
+//   8 decode warps   read the code stream (each warp one 16-channel column of tiles),
+//                    walk the trellis windows in registers, and write binary16
+//                    weights into a shared-memory ring in the K-major, 128-byte
+//                    swizzled layout tcgen05 consumes: each weight is decoded ONCE
+//                    for up to 256 rows.
+//   2 loader warps   copy the matching slice of the activations (cp.async, 16 bytes
+//                    per lane, 128 contiguous bytes per row) into the same ring.
+//   1 issuing thread feeds tcgen05.mma (M = 128 rows x N = 128 channels x K = 16 per
+//                    instruction, both operands from shared memory) with fp32
+//                    accumulators in tensor memory; tcgen05.commit hands each ring
+//                    slot back to the producers when the tensor core is done with it.
+//   4 warps          read the accumulators back with tcgen05.ld and store fp32.
+//
+// One CTA owns a 128-channel output block (one Hadamard block) for up to 256 rows
+// and a range of the input dimension; with splits > 1 each split writes its own
+// partial [M, OC] plane, summed afterwards in split order (deterministic).  The
+// output transform runs as its own kernel on the summed mid.
+//
+// Every wait on an mbarrier is bounded; a wait that gives up raises the status word,
+// the CTA drains, frees its tensor memory and leaves.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace escha {
+
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kChunkK = 64;                       // input channels per ring slot
+constexpr int kTileN = 128;                       // output channels per CTA
+constexpr int kBBytes = kTileN * kChunkK * 2;     // 16 KiB of decoded weights per slot
+constexpr int kABytesPerMt = 128 * kChunkK * 2;   // 16 KiB of activations per 128 rows
+constexpr int kDecodeWarps = 8, kLoaderWarps = 2;
+constexpr int kThreadsTc = (kDecodeWarps + kLoaderWarps + 1) * 32;
+
+__device__ int g_gemm_status = 0;
+
+// ---- tcgen05 / tensor-memory primitives (one CTA per group)
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                 "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// writes made through the generic proxy (st.shared, cp.async) become visible to the
+// tensor core's reads of shared memory
+__device__ __forceinline__ void fence_async_proxy() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, f16 inputs, f32 accumulate
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                         uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrive on an mbarrier of this CTA once all tcgen05.mma issued so far have completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns of tensor memory -> 16 registers per thread
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15])
+        : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64
+// halves) with the 128-byte swizzle: 8-row groups 1024 bytes apart, descriptor
+// version 1, layout type 2.  `addr` is the shared address of the first row (1024-byte
+// aligned tile) plus 32 bytes per 16 channels already consumed.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (uint64_t(1) << 16) |
+           (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// Instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128, N = 128.
+constexpr uint32_t kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+// byte offset of (row, 16-byte chunk) inside a swizzled [rows][128 B] tile
+__device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) {
+    return row * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+
+template <int K, int MT>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
+    constexpr int WPT = 8 * K;
+    constexpr uint32_t kSlotBytes = kBBytes + MT * kABytesPerMt;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kStages], s_empty[kStages], s_done;
+    __shared__ uint32_t s_tmem;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t ocb = blockIdx.x, split = blockIdx.y, r0 = blockIdx.z * (128u * MT);
+    // dynamic shared memory is only guaranteed 16-byte alignment: round up to the
+    // 1024 bytes the swizzle pattern is anchored to
+    const uint32_t ring0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t full0 = smem_u32(s_full), empty0 = smem_u32(s_empty), done = smem_u32(&s_done);
+
+    const uint32_t nchunk_all = static_cast<uint32_t>(p.IC) / kChunkK;
+    const uint32_t S = p.splits, cbase = nchunk_all / S, crem = nchunk_all % S;
+    const uint32_t c_first = split * cbase + min(split, crem);
+    const uint32_t nchunk = cbase + (split < crem ? 1u : 0u);
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full0 + 8u * s, kDecodeWarps + kLoaderWarps);
+            mbar_init(empty0 + 8u * s, 1u);
+        }
+        mbar_init(done, 1u);
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&s_tmem), 128u * MT);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+
+    bool ok = true;
+    if (warp < kDecodeWarps) {
+        // ---- decode warps: warp w owns output channels 16w .. 16w+15 of the block
+        const LaneConsts<K> lc(lane);
+        const uint32_t g = lane >> 2, t = lane & 3u;
+        const uint32_t hmask = p.hash_mask, hxor = p.hash_xor;
+        const ShiftMuls muls{p.mul2, p.mul4, p.mul16, p.mul32, p.mul64, p.mul128};
+        const uint32_t TN = static_cast<uint32_t>(p.OC) >> 4;
+        const size_t kt_words = static_cast<size_t>(TN) * WPT;   // words from tile row kt to kt+1
+        const uint32_t* tile0 = p.code + (static_cast<size_t>(c_first) * 4u) * kt_words +
+                                (static_cast<size_t>(ocb) * 8u + warp) * WPT;
+        uint32_t wa[4], wb[4];
+        auto fetch = [&](uint32_t c) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t* tp = tile0 + (static_cast<size_t>(c) * 4u + q) * kt_words;
+                wa[q] = __ldg(tp + lc.ia());
+                wb[q] = __ldg(tp + lc.ib());
+            }
+        };
+        if (nchunk > 0) fetch(0);
+        const uint32_t row_lo = 16u * warp + g, row_hi = row_lo + 8u;
+        for (uint32_t c = 0; c < nchunk; ++c) {
+            const uint32_t slot = c % kStages;
+            uint32_t a[4][8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t s[8];
+                lc.states(wa[q], wb[q], muls, s);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a[q][j] = cba_decode_dup(s[j], hmask, hxor);
+            }
+            if (c + 1 < nchunk) fetch(c + 1);   // next chunk's words fly while this one is stored
+            if (c >= kStages && !mbar_wait(empty0 + 8u * slot, ((c / kStages) - 1u) & 1u)) {
+                ok = false;
+                break;
+            }
+            const uint32_t bslot = ring0 + slot * kSlotBytes;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                // value j sits at (channel g + 8*(j>=4), input 2t + (j&1) + 8*((j>>1)&1)) of
+                // tile row q: pairs (0,1), (2,3), (4,5), (6,7) are two consecutive inputs
+                const uint32_t c_lo = 2u * q, c_hi = 2u * q + 1u;   // 16-byte chunks of the row
+                const uint32_t p01 = prmt(a[q][0], a[q][1], 0x5410u), p23 = prmt(a[q][2], a[q][3], 0x5410u);
+                const uint32_t p45 = prmt(a[q][4], a[q][5], 0x5410u), p67 = prmt(a[q][6], a[q][7], 0x5410u);
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_lo) + 4u * t), "r"(p01) : "memory");
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_hi) + 4u * t), "r"(p23) : "memory");
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_lo) + 4u * t), "r"(p45) : "memory");
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_hi) + 4u * t), "r"(p67) : "memory");
+            }
+            fence_async_proxy();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8u * slot);
+        }
+    } else if (warp < kDecodeWarps + kLoaderWarps) {
+        // ---- loader warps: rows of xh for this chunk, 8 lanes x 16 bytes per row
+        const uint32_t lw = warp - kDecodeWarps;
+        const uint32_t sub = lane >> 3, chunk = lane & 7u;          // 4 rows per instruction
+        for (uint32_t c = 0; c < nchunk; ++c) {
+            const uint32_t slot = c % kStages;
+            if (c >= kStages && !mbar_wait(empty0 + 8u * slot, ((c / kStages) - 1u) & 1u)) {
+                ok = false;
+                break;
+            }
+            const uint32_t aslot = ring0 + slot * kSlotBytes + kBBytes;
+            const size_t k0 = static_cast<size_t>(c_first + c) * kChunkK + chunk * 8u;
+            for (uint32_t rr = lw * 4u + sub; rr < 128u * MT; rr += 4u * kLoaderWarps) {
+                const uint32_t row = min(r0 + rr, static_cast<uint32_t>(p.M) - 1u);
+                cp_async16_shared(aslot + sw128(rr, chunk), p.xh + static_cast<size_t>(row) * p.IC + k0);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            fence_async_proxy();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8u * slot);
+        }
+    } else if (lane == 0) {
+        // ---- the issuing thread
+        for (uint32_t c = 0; c < nchunk; ++c) {
+            const uint32_t slot = c % kStages;
+            if (!mbar_wait(full0 + 8u * slot, (c / kStages) & 1u)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t bslot = ring0 + slot * kSlotBytes, aslot = bslot + kBBytes;
+#pragma unroll
+            for (uint32_t k16 = 0; k16 < kChunkK / 16; ++k16) {
+                const uint64_t db = smem_desc_sw128(bslot + 32u * k16);
+#pragma unroll
+                for (uint32_t mt = 0; mt < MT; ++mt) {
+                    const uint64_t da = smem_desc_sw128(aslot + mt * kABytesPerMt + 32u * k16);
+                    umma_f16(tmem + mt * 128u, da, db, kIdesc, (c | k16) != 0u);
+                }
+            }
+            umma_commit(empty0 + 8u * slot);   // the slot is free once these MMAs have read it
+        }
+        if (ok) umma_commit(done);
+    }
+    if (!ok && lane == 0) atomicExch(&g_gemm_status, 1);
+
+    // ---- epilogue: warps 0..3 own accumulator lanes 32w .. 32w+31 (= rows of the tile)
+    if (warp < 4) {
+        bool ready = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0 && nchunk > 0;
+        if (ready && !mbar_wait(done, 0u)) {
+            ready = false;
+            if (lane == 0) atomicExch(&g_gemm_status, 2);
+        }
+        tc_fence_after_sync();
+        if (ready) {
+            float* plane = p.out + static_cast<size_t>(split) * p.M * p.OC;
+#pragma unroll
+            for (uint32_t mt = 0; mt < MT; ++mt) {
+                const uint32_t row = r0 + mt * 128u + 32u * warp + lane;
+#pragma unroll
+                for (uint32_t col = 0; col < 128u; col += 16u) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem + ((32u * warp) << 16) + mt * 128u + col, v);
+                    tmem_ld_wait();
+                    if (row < static_cast<uint32_t>(p.M)) {
+                        float4* dst = reinterpret_cast<float4*>(
+                            plane + static_cast<size_t>(row) * p.OC + ocb * 128u + col);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 128u * MT);
+}
+
+template <int K, int MT>
+cudaError_t launch_tc(const GemmTcParams& p, cudaStream_t st) {
+    const size_t smem = static_cast<size_t>(kStages) * (kBBytes + MT * kABytesPerMt) + 1024;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        e = cudaFuncSetAttribute(gemm_tc_kernel<K, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    const dim3 grid(p.OC / 128, p.splits, (p.M + 128 * MT - 1) / (128 * MT));
+    gemm_tc_kernel<K, MT><<<grid, kThreadsTc, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
+    const bool two = p.M > 128;
+    if (p.K == 2) return two ? launch_tc<2, 2>(p, st) : launch_tc<2, 1>(p, st);
+    return two ? launch_tc<3, 2>(p, st) : launch_tc<3, 1>(p, st);
+}
+
+namespace {
+// mid = ((plane0 + plane1) + plane2) + ... in split order
+__global__ void sum_planes_kernel(const float4* __restrict__ planes, float4* __restrict__ mid,
+                                  size_t n4, int splits) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    float4 a = planes[i];
+    for (int s = 1; s < splits; ++s) {
+        const float4 b = planes[static_cast<size_t>(s) * n4 + i];
+        a.x = __fadd_rn(a.x, b.x); a.y = __fadd_rn(a.y, b.y);
+        a.z = __fadd_rn(a.z, b.z); a.w = __fadd_rn(a.w, b.w);
+    }
+    mid[i] = a;
+}
+}  // namespace
+
+cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int splits, cudaStream_t st) {
+    const size_t n4 = n / 4;
+    sum_planes_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, st>>>(
+        reinterpret_cast<const float4*>(planes), reinterpret_cast<float4*>(mid), n4, splits);
+    return cudaGetLastError();
+}
+
+cudaError_t gemm_tc_status(int* host_status) {
+    return cudaMemcpyFromSymbol(host_status, g_gemm_status, sizeof(int));
+}
+
+}  // namespace escha

@@ -146,6 +146,19 @@ int coded_gemv_with_scratch(const void* xh, const void* code, const float* rout,
                             int OC, int K, int splits, float rs, int32_t* counters, float* part,
                             void* out, void* stream);
 
+// Prefill coded GEMM on tcgen05 (gemm_tc.cu): out[split][M][OC] f32 partial products.
+struct GemmTcParams {
+    const uint32_t* code;   // [IC/16, OC/16, 8K]
+    const __half* xh;       // [M, IC] transformed activations
+    float* out;             // [splits, M, OC]
+    int M, IC, OC, K, splits;
+    uint32_t hash_mask, hash_xor;
+    uint32_t mul2, mul4, mul16, mul32, mul64, mul128;
+};
+cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);
+cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int splits, cudaStream_t st);
+cudaError_t gemm_tc_status(int* host_status);
+
 cudaError_t launch_moe_route(const RouteParams& p, cudaStream_t st);
 size_t route_shared_bytes(int T, int top_k, int e_lo, int e_hi);
 bool w8a16_mma_supports(int N, int Kd);

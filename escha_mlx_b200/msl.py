@@ -609,3 +609,19 @@ def moe_shared_finish(gu: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor, d
                                       ptr(shared_gate_logit, torch.float32),
                                       T, top_k, H, inter, ptr(out), stream()))
     return out
+
+
+def dense_gemm_tc(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int, OC: int,
+                  splits: int | None = None) -> torch.Tensor:
+    """Prefill coded GEMM on the tcgen05 tensor cores -> mid f32 [M, OC]
+    (the product of dense_gemm_mat, msl.py:1608-1782, decoded once per 256 rows)."""
+    _check_code(code_u32)
+    m = xh.shape[0]
+    if m < 1:
+        raise ValueError("dense_gemm_tc needs at least one row")
+    s = int(lib.escha_coded_gemm_tc_splits(IC, OC, 0)) if splits is None else int(splits)
+    mid = torch.empty((m, OC), dtype=torch.float32, device=xh.device)
+    planes = torch.empty((s, m, OC), dtype=torch.float32, device=xh.device) if s > 1 else None
+    check(lib.escha_coded_gemm_tc(ptr(xh, torch.float16), ptr(code_u32), m, IC, OC, K, s,
+                                  ptr(planes), ptr(mid), stream()))
+    return mid

@@ -279,6 +279,27 @@ int escha_moe_shared_finish(const void *gu, const void *w8, const void *scale, c
                             const float *shared_gate_logit, int T, int top_k, int H, int I,
                             void *out, void *stream);
 
+/* Prefill form of the coded product on the tcgen05 tensor cores, for tens to
+ * hundreds of rows:  mid[r,:] = f32(xh[r,:]) @ f32(decode(code)),  f32 [M,OC].
+ * Replaces msl.dense_gemm_mat and the row-blocked msl.dense_gemm_rows at prefill
+ * sizes (msl.py:1608-1782, :1785-1841): every weight is decoded once per 256 rows
+ * into shared memory as binary16 and contracted by tcgen05.mma with fp32
+ * accumulators in tensor memory.  Reassociated like dense_gemm_mat, deterministic:
+ * tolerance-equal to escha_gemv_ref, bit-reproducible for fixed (shape, splits).
+ *   xh [M,IC] binary16 (already input-transformed), code [IC/16, OC/16, 8K].
+ *   splits <= 0 selects escha_coded_gemm_tc_splits(); with splits > 1 `planes` must
+ *   hold splits*M*OC floats of scratch (summed into mid in split order).
+ * The output transform is escha_scaled_had_out on mid. */
+int escha_coded_gemm_tc(const void *xh, const void *code, int M, int IC, int OC, int K, int splits,
+                        float *planes, float *mid, void *stream);
+
+/* Split policy of escha_coded_gemm_tc (shape only; sm_count <= 0 queries the device). */
+int escha_coded_gemm_tc_splits(int IC, int OC, int sm_count);
+
+/* 0 if no tensor-core GEMM launch on the current device has given up a bounded wait
+ * since the library was loaded; synchronises the device.  For tests and diagnostics. */
+int escha_coded_gemm_tc_status(void);
+
 #ifdef __cplusplus
 }
 #endif
