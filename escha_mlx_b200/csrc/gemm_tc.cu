@@ -7,11 +7,14 @@
 // At these row counts the decoded tile is a real dense contraction, so the trellis
 // decode and the matrix product are split between the two machines an SM has:
 //
-//   8 decode warps   read the code stream (each warp one 16-channel column of tiles),
+//   16 decode warps  read the code stream (each warp half of a 16-channel column of tiles),
 //                    walk the trellis windows in registers, and write binary16
 //                    weights into a shared-memory ring in the K-major, 128-byte
 //                    swizzled layout tcgen05 consumes: each weight is decoded ONCE
 //                    for up to 256 rows.
+//   1 code warp      streams the CTA's slice of the code into a shared-memory ring with
+//                    bulk copies (cp.async.bulk, no multicast), so the decode warps
+//                    never wait on a global load.
 //   2 loader warps   copy the matching slice of the activations (cp.async, 16 bytes
 //                    per lane, 128 contiguous bytes per row) into the same ring.
 //   1 issuing thread feeds tcgen05.mma (M = 128 rows x N = 128 channels x K = 16 per
@@ -39,10 +42,22 @@ constexpr int kChunkK = 64;                       // input channels per ring slo
 constexpr int kTileN = 128;                       // output channels per CTA
 constexpr int kBBytes = kTileN * kChunkK * 2;     // 16 KiB of decoded weights per slot
 constexpr int kABytesPerMt = 128 * kChunkK * 2;   // 16 KiB of activations per 128 rows
-constexpr int kDecodeWarps = 8, kLoaderWarps = 2;
-constexpr int kThreadsTc = (kDecodeWarps + kLoaderWarps + 1) * 32;
+constexpr int kDecodeWarps = 16, kLoaderWarps = 2;
+constexpr int kLoadDepth = 3;                     // activation chunks a loader warp keeps in flight
+constexpr int kCodeStages = 6;                    // code-stream ring depth (chunks)
+constexpr int kThreadsTc = (kDecodeWarps + kLoaderWarps + 2) * 32;   // + issuing warp + code warp
 
 __device__ int g_gemm_status = 0;
+
+// Bounded wait that sleeps between polls: a waiting warp must not take issue slots
+// from the decode warps, which are what limits this kernel.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < kMbarWaitLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(it < 64 ? 32 : 256);
+    }
+    return false;
+}
 
 // ---- tcgen05 / tensor-memory primitives (one CTA per group)
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
@@ -117,6 +132,7 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
     constexpr uint32_t kSlotBytes = kBBytes + MT * kABytesPerMt;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[kStages], s_empty[kStages], s_done;
+    __shared__ __align__(8) uint64_t s_cfull[kCodeStages], s_cempty[kCodeStages];
     __shared__ uint32_t s_tmem;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -125,17 +141,27 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
     // 1024 bytes the swizzle pattern is anchored to
     const uint32_t ring0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t full0 = smem_u32(s_full), empty0 = smem_u32(s_empty), done = smem_u32(&s_done);
+    const uint32_t cfull0 = smem_u32(s_cfull), cempty0 = smem_u32(s_cempty);
+    constexpr uint32_t kRowBytes = 8u * WPT * 4u;          // one tile row of the CTA's 8 tile columns
+    constexpr uint32_t kCodeChunkBytes = 4u * kRowBytes;   // four tile rows = 64 input channels
+    const uint32_t code0 = ring0 + kStages * kSlotBytes;   // code ring follows the operand ring
 
     const uint32_t nchunk_all = static_cast<uint32_t>(p.IC) / kChunkK;
     const uint32_t S = p.splits, cbase = nchunk_all / S, crem = nchunk_all % S;
     const uint32_t c_first = split * cbase + min(split, crem);
     const uint32_t nchunk = cbase + (split < crem ? 1u : 0u);
+    auto chunk_at = [&](uint32_t c) { return c_first + c; };
 
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full0 + 8u * s, kDecodeWarps + kLoaderWarps);
             mbar_init(empty0 + 8u * s, 1u);
+        }
+#pragma unroll
+        for (int s = 0; s < kCodeStages; ++s) {
+            mbar_init(cfull0 + 8u * s, 1u);             // the code warp's arrive.expect_tx
+            mbar_init(cempty0 + 8u * s, kDecodeWarps);  // one arrival per decode warp
         }
         mbar_init(done, 1u);
         mbar_fence_init();
@@ -151,85 +177,116 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
 
     bool ok = true;
     if (warp < kDecodeWarps) {
-        // ---- decode warps: warp w owns output channels 16w .. 16w+15 of the block
+        // ---- decode warps: warp w owns output channels 16(w&7) .. +15 of the block and
+        // tile rows 2(w>>3), 2(w>>3)+1 of every 64-channel chunk
         const LaneConsts<K> lc(lane);
         const uint32_t g = lane >> 2, t = lane & 3u;
+        const uint32_t wn = warp & 7u, q0 = 2u * (warp >> 3);
         const uint32_t hmask = p.hash_mask, hxor = p.hash_xor;
         const ShiftMuls muls{p.mul2, p.mul4, p.mul16, p.mul32, p.mul64, p.mul128};
-        const uint32_t TN = static_cast<uint32_t>(p.OC) >> 4;
-        const size_t kt_words = static_cast<size_t>(TN) * WPT;   // words from tile row kt to kt+1
-        const uint32_t* tile0 = p.code + (static_cast<size_t>(c_first) * 4u) * kt_words +
-                                (static_cast<size_t>(ocb) * 8u + warp) * WPT;
-        uint32_t wa[4], wb[4];
-        auto fetch = [&](uint32_t c) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const uint32_t* tp = tile0 + (static_cast<size_t>(c) * 4u + q) * kt_words;
-                wa[q] = __ldg(tp + lc.ia());
-                wb[q] = __ldg(tp + lc.ib());
-            }
-        };
-        if (nchunk > 0) fetch(0);
-        const uint32_t row_lo = 16u * warp + g, row_hi = row_lo + 8u;
+        const uint32_t my_words = code0 + q0 * kRowBytes + wn * (WPT * 4u);
+        const uint32_t row_lo = 16u * wn + g, row_hi = row_lo + 8u;
         for (uint32_t c = 0; c < nchunk; ++c) {
-            const uint32_t slot = c % kStages;
-            uint32_t a[4][8];
+            {
+                // this warp's two tiles of the chunk: two words per lane and tile from the code ring
+                const uint32_t cslot = c % kCodeStages;
+                if (!mbar_wait_relaxed(cfull0 + 8u * cslot, (c / kCodeStages) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                uint32_t wa[2], wb[2];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint32_t s[8];
-                lc.states(wa[q], wb[q], muls, s);
+                for (int q = 0; q < 2; ++q) {
+                    const uint32_t tp = my_words + cslot * kCodeChunkBytes + q * kRowBytes;
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(wa[q]) : "r"(tp + 4u * lc.ia()));
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(wb[q]) : "r"(tp + 4u * lc.ib()));
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(cempty0 + 8u * cslot);
+                const uint32_t slot = c % kStages;
+                uint32_t a[2][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) a[q][j] = cba_decode_dup(s[j], hmask, hxor);
-            }
-            if (c + 1 < nchunk) fetch(c + 1);   // next chunk's words fly while this one is stored
-            if (c >= kStages && !mbar_wait(empty0 + 8u * slot, ((c / kStages) - 1u) & 1u)) {
-                ok = false;
-                break;
-            }
-            const uint32_t bslot = ring0 + slot * kSlotBytes;
+                for (int q = 0; q < 2; ++q) {
+                    uint32_t s[8];
+                    lc.states(wa[q], wb[q], muls, s);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                // value j sits at (channel g + 8*(j>=4), input 2t + (j&1) + 8*((j>>1)&1)) of
-                // tile row q: pairs (0,1), (2,3), (4,5), (6,7) are two consecutive inputs
-                const uint32_t c_lo = 2u * q, c_hi = 2u * q + 1u;   // 16-byte chunks of the row
-                const uint32_t p01 = prmt(a[q][0], a[q][1], 0x5410u), p23 = prmt(a[q][2], a[q][3], 0x5410u);
-                const uint32_t p45 = prmt(a[q][4], a[q][5], 0x5410u), p67 = prmt(a[q][6], a[q][7], 0x5410u);
-                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_lo) + 4u * t), "r"(p01) : "memory");
-                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_hi) + 4u * t), "r"(p23) : "memory");
-                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_lo) + 4u * t), "r"(p45) : "memory");
-                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_hi) + 4u * t), "r"(p67) : "memory");
+                    for (int j = 0; j < 8; ++j) a[q][j] = cba_decode_dup(s[j], hmask, hxor);
+                }
+                if (c >= kStages && !mbar_wait_relaxed(empty0 + 8u * slot, ((c / kStages) - 1u) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t bslot = ring0 + slot * kSlotBytes;
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    // value j sits at (channel g + 8*(j>=4), input 2t + (j&1) + 8*((j>>1)&1)) of
+                    // its tile row: pairs (0,1), (2,3), (4,5), (6,7) are two consecutive inputs
+                    const uint32_t c_lo = 2u * (q0 + q), c_hi = c_lo + 1u;   // 16-byte chunks of the row
+                    const uint32_t p01 = prmt(a[q][0], a[q][1], 0x5410u), p23 = prmt(a[q][2], a[q][3], 0x5410u);
+                    const uint32_t p45 = prmt(a[q][4], a[q][5], 0x5410u), p67 = prmt(a[q][6], a[q][7], 0x5410u);
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_lo) + 4u * t), "r"(p01) : "memory");
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_hi) + 4u * t), "r"(p23) : "memory");
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_lo) + 4u * t), "r"(p45) : "memory");
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_hi) + 4u * t), "r"(p67) : "memory");
+                }
+                fence_async_proxy();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8u * slot);
             }
-            fence_async_proxy();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full0 + 8u * slot);
         }
     } else if (warp < kDecodeWarps + kLoaderWarps) {
-        // ---- loader warps: rows of xh for this chunk, 8 lanes x 16 bytes per row
+        // ---- loader warps: rows of xh for each chunk, 8 lanes x 16 bytes per row; up to
+        // kLoadDepth chunks' copies are in flight before the oldest is published
         const uint32_t lw = warp - kDecodeWarps;
         const uint32_t sub = lane >> 3, chunk = lane & 7u;          // 4 rows per instruction
+        for (uint32_t c = 0; c < nchunk + kLoadDepth - 1u; ++c) {
+            if (c < nchunk) {
+                const uint32_t slot = c % kStages;
+                if (c >= kStages && !mbar_wait_relaxed(empty0 + 8u * slot, ((c / kStages) - 1u) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t aslot = ring0 + slot * kSlotBytes + kBBytes;
+                const size_t k0 = static_cast<size_t>(chunk_at(c)) * kChunkK + chunk * 8u;
+                for (uint32_t rr = lw * 4u + sub; rr < 128u * MT; rr += 4u * kLoaderWarps) {
+                    const uint32_t row = min(r0 + rr, static_cast<uint32_t>(p.M) - 1u);
+                    cp_async16_shared(aslot + sw128(rr, chunk), p.xh + static_cast<size_t>(row) * p.IC + k0);
+                }
+            }
+            cp_async_commit();   // an empty group past the last chunk keeps the count uniform
+            if (c + 1u >= kLoadDepth) {
+                cp_async_wait<kLoadDepth - 1>();
+                fence_async_proxy();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8u * ((c + 1u - kLoadDepth) % kStages));
+            }
+        }
+    } else if (warp == kDecodeWarps + kLoaderWarps + 1) {
+        // ---- code warp: bulk copies (TMA, untiled, no multicast) of the CTA's slice of the
+        // code stream, one copy per tile row (8 tiles side by side), four rows per chunk
+        const uint32_t TN = static_cast<uint32_t>(p.OC) >> 4;
+        const size_t kt_words = static_cast<size_t>(TN) * WPT;   // words from tile row kt to kt+1
+        const uint32_t* grow0 = p.code + static_cast<size_t>(lane) * kt_words +
+                                static_cast<size_t>(ocb) * 8u * WPT;
         for (uint32_t c = 0; c < nchunk; ++c) {
-            const uint32_t slot = c % kStages;
-            if (c >= kStages && !mbar_wait(empty0 + 8u * slot, ((c / kStages) - 1u) & 1u)) {
+            const uint32_t cslot = c % kCodeStages;
+            if (c >= kCodeStages &&
+                !mbar_wait_relaxed(cempty0 + 8u * cslot, ((c / kCodeStages) - 1u) & 1u)) {
                 ok = false;
                 break;
             }
-            const uint32_t aslot = ring0 + slot * kSlotBytes + kBBytes;
-            const size_t k0 = static_cast<size_t>(c_first + c) * kChunkK + chunk * 8u;
-            for (uint32_t rr = lw * 4u + sub; rr < 128u * MT; rr += 4u * kLoaderWarps) {
-                const uint32_t row = min(r0 + rr, static_cast<uint32_t>(p.M) - 1u);
-                cp_async16_shared(aslot + sw128(rr, chunk), p.xh + static_cast<size_t>(row) * p.IC + k0);
-            }
-            cp_async_commit();
-            cp_async_wait<0>();
-            fence_async_proxy();
+            if (lane == 0) mbar_arrive_expect_tx(cfull0 + 8u * cslot, kCodeChunkBytes);
             __syncwarp();
-            if (lane == 0) mbar_arrive(full0 + 8u * slot);
+            if (lane < 4)
+                bulk_copy_g2s(code0 + cslot * kCodeChunkBytes + lane * kRowBytes,
+                              grow0 + static_cast<size_t>(chunk_at(c)) * 4u * kt_words, kRowBytes,
+                              cfull0 + 8u * cslot);
         }
     } else if (lane == 0) {
         // ---- the issuing thread
         for (uint32_t c = 0; c < nchunk; ++c) {
             const uint32_t slot = c % kStages;
-            if (!mbar_wait(full0 + 8u * slot, (c / kStages) & 1u)) {
+            if (!mbar_wait_relaxed(full0 + 8u * slot, (c / kStages) & 1u)) {
                 ok = false;
                 break;
             }
@@ -253,7 +310,7 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
     // ---- epilogue: warps 0..3 own accumulator lanes 32w .. 32w+31 (= rows of the tile)
     if (warp < 4) {
         bool ready = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0 && nchunk > 0;
-        if (ready && !mbar_wait(done, 0u)) {
+        if (ready && !mbar_wait_relaxed(done, 0u)) {
             ready = false;
             if (lane == 0) atomicExch(&g_gemm_status, 2);
         }
@@ -287,7 +344,8 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
 
 template <int K, int MT>
 cudaError_t launch_tc(const GemmTcParams& p, cudaStream_t st) {
-    const size_t smem = static_cast<size_t>(kStages) * (kBBytes + MT * kABytesPerMt) + 1024;
+    const size_t smem = static_cast<size_t>(kStages) * (kBBytes + MT * kABytesPerMt) +
+                        static_cast<size_t>(kCodeStages) * 4u * (8u * 8u * K * 4u) + 1024;
     static bool configured[64] = {false};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

@@ -209,7 +209,11 @@ class EschaLinear(torch.nn.Module):
                                       input_mode=msl.INPUT_RAW, rs=RS)[0]
             return self._finish(y, shape, x.dtype)
         xh = self._input_rows(rows)
-        if self._fused_had:
+        if msl.use_prefill_kernel(rows.shape[0]):
+            # prefill: decode once per 256 rows into shared memory, contract on tcgen05
+            w = self._w
+            y = self._output_rows(msl.dense_gemm_tc(xh, w.code, w.K, w.IC, w.OC))
+        elif self._fused_had:
             y = msl.dense_gemm_rows_direct_out(
                 xh, self._w.code, self._w.rout, self.K, self._w.IC, self._w.OC,
                 msl.dense_block_r(rows.shape[0], self._block_r_pin), RS)
@@ -246,7 +250,7 @@ def project_many(linears, x: torch.Tensor):
         and all(lin._w.IC == rows.shape[-1] and lin.K == first.K for lin in linears)
         and rows.dtype == torch.float16
     )
-    if not joint:
+    if not joint or msl.use_prefill_kernel(rows.shape[0]):
         return [lin(x) for lin in linears]
     rows = rows.contiguous()
     ws = [lin._w for lin in linears]

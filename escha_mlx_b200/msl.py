@@ -438,10 +438,23 @@ def dense_gemm_rows_direct(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC:
     return dense_gemv(xh, code_u32, K, IC, OC)
 
 
+#: From this many rows on the dense modules run the product on tcgen05 (decode once
+#: per 256 rows into shared memory) instead of the register-fragment kernel, which
+#: decodes once per 16 rows.  Measured crossover on the 27B-class shapes: ~40 rows.
+PREFILL_MIN_ROWS = 48
+
+
+def use_prefill_kernel(m: int) -> bool:
+    return gemv_family() == "mma" and m >= PREFILL_MIN_ROWS
+
+
 def dense_gemm_mat(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int,
                    OC: int) -> torch.Tensor:
-    """Matrix-unit dense GEMM (:1762-1782): always the tensor-core kernel here."""
+    """Matrix-unit dense GEMM (:1762-1782): the tcgen05 kernel at prefill row counts,
+    the register-fragment tensor-core kernel below them."""
     _check_code(code_u32)
+    if use_prefill_kernel(xh.shape[0]):
+        return dense_gemm_tc(xh, code_u32, K, IC, OC)
     return _gemv_mma_dense(xh, code_u32, None, K, IC, OC, None)
 
 

@@ -1,0 +1,79 @@
+"""GPU parity of the prefill coded GEMM (decode into shared memory, tcgen05.mma with
+fp32 accumulators in tensor memory) against the CPU oracle's float64 product of
+reference-decoded weights, against the register-fragment tensor-core kernel, and
+through the dense module.  Mirrors the reference's tests/test_gemm_mat.py bar:
+tolerance-equal to the per-row kernel, deterministic run to run."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from cases import rel_err
+from escha_mlx_b200 import dense, msl, synth
+from escha_mlx_b200._lib import lib
+
+pytestmark = pytest.mark.gpu
+
+GEMV_TOL = 1e-3      # max rel error vs f64 product of reference-decoded weights
+
+
+def dev(a, device):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.mark.parametrize("K,IC,OC,M,splits", [
+    (2, 128, 128, 1, 1),        # one chunk pair, one row
+    (2, 256, 128, 48, 1),
+    (3, 512, 256, 128, 1),      # exactly one row tile
+    (3, 512, 256, 129, 2),      # ragged second row tile, two planes
+    (2, 1024, 384, 256, None),  # policy split
+    (3, 768, 128, 300, 3),      # more than 256 rows: second pass over the weights
+    (2, 4096, 256, 64, 4),
+])
+def test_prefill_gemm_vs_oracle(cuda, oracle, K, IC, OC, M, splits):
+    rng = np.random.default_rng(K * 1000 + IC + M)
+    code, _, _ = synth.coded_projection(rng, IC, OC, K)
+    xh = (rng.standard_normal((M, IC)) * 0.25).astype(np.float16)
+    c, xd = msl.code_tensor(code, cuda), dev(xh, cuda)
+    mid = msl.dense_gemm_tc(xd, c, K, IC, OC, splits=splits)
+    torch.cuda.synchronize()
+    assert lib.escha_coded_gemm_tc_status() == 0
+    want = oracle.gemv_f64(xh, code, None, K, IC, OC)
+    assert rel_err(host(mid), want) < GEMV_TOL
+    # bit-reproducible, and tolerance-equal to the register-fragment kernel
+    assert torch.equal(msl.dense_gemm_tc(xd, c, K, IC, OC, splits=splits), mid)
+    assert rel_err(host(mid), host(msl.dense_gemv(xd, c, K, IC, OC))) < 2e-5
+
+
+def test_prefill_rejects_bad_arguments(cuda):
+    xh = torch.zeros((4, 256), dtype=torch.float16, device=cuda)
+    code = torch.zeros((16, 8, 16), dtype=torch.int32, device=cuda)
+    with pytest.raises(ValueError, match="splits=9 exceeds"):
+        msl.dense_gemm_tc(xh, code, 2, 256, 128, splits=9)
+    with pytest.raises(ValueError, match="at least one row"):
+        msl.dense_gemm_tc(xh[:0], code, 2, 256, 128)
+
+
+@pytest.mark.parametrize("M", [48, 200])
+def test_dense_linear_prefill_path(cuda, oracle, monkeypatch, M):
+    """EschaLinear at prefill row counts (input transform, tcgen05 product, output
+    transform) against the oracle's full linear."""
+    monkeypatch.delenv("ESCHA_MLX_GEMV", raising=False)
+    rng = np.random.default_rng(M)
+    K, IC, OC = 3, 512, 384
+    code, rin, rout = synth.coded_projection(rng, IC, OC, K)
+    x = synth.activations(rng, M, IC)
+    lin = dense.EschaLinear(dense.EschaWeight(code, rin, rout, device=cuda))
+    assert msl.use_prefill_kernel(M)
+    y = lin(dev(x, cuda))
+    ri, ro = oracle.fold_scales(rin, rout)
+    want = oracle.dense_linear(x, code, ri, ro, K)
+    assert rel_err(host(y), want) < 2e-3
+    assert torch.equal(lin(dev(x, cuda)), y)
+    a, b = dense.project_pair(lin, lin, dev(x, cuda))
+    assert torch.equal(a, y) and torch.equal(b, y)
