@@ -56,6 +56,15 @@ L2_BYTES = 126 * 1024 * 1024
 METRIC = "coded GEMV compressed-weight GB/s"
 
 
+def measured_peak_tflops() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 def measured_peak_gbs() -> tuple[float, str]:
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -194,7 +203,8 @@ def run_reference(args, rank: int) -> None:
 
 
 def workload_config(args, n_sets: int) -> dict:
-    return {"workload": f"dense27b_layer_decode_b{args.batch}",
+    return {"workload": (f"dense27b_layer_prefill_m{args.batch}" if args.workload == "prefill"
+                         else f"dense27b_layer_decode_b{args.batch}"),
             "projections": "q/k/v/o 2-bit 5120x{6144,1024,1024,5120}; gate/up 3-bit 5120x17408; "
                            "down 3-bit 17408x5120",
             "batch": args.batch, "code_bytes_per_step": LAYER_BYTES,
@@ -362,9 +372,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "step"],
-                    help="dense: 27B-class layer (default, the headline); moe: one 35B-A3B-class "
-                         "MoE layer at --tokens; step: 40-layer MoE decode step at batch 32")
+    ap.add_argument("--workload", default="dense", choices=["dense", "prefill", "moe", "step"],
+                    help="dense: 27B-class layer at decode batch --batch (default, the headline); "
+                         "prefill: the same layer at 256 rows on the tcgen05 GEMM, reported in "
+                         "TFLOP/s; moe: one 35B-A3B-class MoE layer at --tokens; step: 40-layer "
+                         "MoE decode step at batch 32")
     ap.add_argument("--tokens", type=int, default=8, help="tokens per step for --workload moe")
     ap.add_argument("--cpu-seconds", type=float, default=10.0,
                     help="bounded CPU-baseline sample (rank 0, N=1)")
@@ -378,9 +390,12 @@ def main() -> None:
     if args.impl == "reference":
         run_reference(args, rank)
         return
-    if args.workload != "dense":
+    if args.workload in ("moe", "step"):
         run_moe(args, rank, world, local_rank)
         return
+    prefill = args.workload == "prefill"
+    if prefill and args.batch == 1:
+        args.batch = 256
 
     import torch
     import torch.distributed as dist
@@ -504,12 +519,17 @@ def main() -> None:
     ms_e2e = ee0.elapsed_time(ee1)
 
     # ---- roofline leg: the coded GEMV kernel alone --------------------------------------------
+    tensor_leg = msl.use_prefill_kernel(M)
+
     def gemv_only(layer, xs):
         outs = []
         for name, _, _, _ in LAYER:
             w = layer[name]._w
-            outs.append(msl.dense_gemm_rows_direct_out(xs[w.IC], w.code, w.rout, w.K, w.IC, w.OC,
-                                                       8, msl.RS))
+            if tensor_leg:   # the tcgen05 GEMM alone (f32 mid out)
+                outs.append(msl.dense_gemm_tc(xs[w.IC], w.code, w.K, w.IC, w.OC))
+            else:
+                outs.append(msl.dense_gemm_rows_direct_out(xs[w.IC], w.code, w.rout, w.K, w.IC,
+                                                           w.OC, 8, msl.RS))
         return outs
 
     xs = {ic: msl.dense_scaled_had(torch.randn((M, ic), device=device, generator=gen).half(),
@@ -550,6 +570,7 @@ def main() -> None:
         # factor; this is the average over the seven launches timed above, per GPU.
         traffic = (sum(ic * oc * k // 8 * (1.013 if k == 2 else 1.004) for _, ic, oc, k in LAYER)
                    / 7 / world) if M == 1 else None
+        flops_step = 2.0 * M * sum(ic * oc for _, ic, oc, _ in LAYER)
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
@@ -570,12 +591,39 @@ def main() -> None:
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
             "clocks": clocks.summary(),
         }
+        if tensor_leg:
+            tpeak, tkind = measured_peak_tflops()
+            tf = flops_step / world * reps / (ms_gemv * 1e-3) / 1e12      # per GPU
+            line["tflops"] = flops_step * args.steps / (ms_total * 1e-3) / 1e12
+            line["roofline"] = {
+                "bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s",
+                "frac": tf / tpeak, "traffic": None,
+                "kernel": "gemm_tc_kernel (trellis decode into shared memory + tcgen05.mma)",
+                "launches_timed": launches, "avg_launch_us": ms_gemv * 1e3 / launches,
+                "algorithmic_flops_per_launch_avg": flops_step / world / 7,
+                "peak_source": f"MEASURED_PEAKS.json bf16_tflops burst ({tkind}); f16 and bf16 "
+                               "share the tensor rate"}
+        if prefill:
+            line.update({"metric": "prefill coded GEMM TFLOP/s", "value": line["tflops"],
+                         "unit": "TFLOP/s",
+                         "e2e": {"value": flops_step * args.steps / (ms_e2e * 1e-3) / 1e12,
+                                 "unit": "TFLOP/s", "h2d_bytes_per_step": M * HIDDEN * 2,
+                                 "d2h_bytes_per_step": M * HIDDEN * 2}})
         if world == 1:
-            cpu_gbs, passes, dt, cores = time_cpu(M, args.cpu_seconds, 200)
+            cpu_rows = min(M, 16)
+            cpu_gbs, passes, dt, cores = time_cpu(cpu_rows, args.cpu_seconds, 200)
+            if prefill:
+                cpu_gbs = cpu_gbs / LAYER_BYTES * (flops_step * cpu_rows / M) / 1e3   # GB/s -> TFLOP/s
+                line["cpu_baseline"] = {
+                    "value": cpu_gbs, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                    "sample": f"{passes} passes ({dt:.1f} s) of the same layer at {cpu_rows} rows on "
+                              "the CPU oracle (C port of escha_mlx/ref.py)"}
+                print(json.dumps(line), flush=True)
+                return
             line["cpu_baseline"] = {
                 "value": cpu_gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                 "sample": f"{passes} full layer passes ({dt:.1f} s) of the same 7-projection "
-                          f"layer at batch {M} on the CPU oracle (C port of escha_mlx/ref.py)"}
+                          f"layer at batch {cpu_rows} on the CPU oracle (C port of escha_mlx/ref.py)"}
         print(json.dumps(line), flush=True)
     if world > 1:
         # graphs that captured NCCL collectives pin the communicator: NCCL's teardown
