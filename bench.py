@@ -466,16 +466,19 @@ def main() -> None:
     x0 = torch.randn((M, HIDDEN), device=device, generator=gen).half()
 
     if args.only:
-        # profiling aid: K launches of one projection's fused GEMV, rotating weight sets
+        # profiling aid: K launches of one projection's product kernel, rotating weight sets
         lin = [s[args.only] for s in sets]
         ic = lin[0]._w.IC
         xh = msl.dense_scaled_had(torch.randn((M, ic), device=device, generator=gen).half(),
                                   lin[0]._w.rin, msl.RS)
         for i in range(args.warmup + args.steps):
             w = lin[i % n_sets]._w
-            msl.dense_gemm_rows_direct_out(xh, w.code, w.rout, w.K, w.IC, w.OC, 8, msl.RS)
+            if msl.use_prefill_kernel(M):
+                msl.dense_gemm_tc(xh, w.code, w.K, w.IC, w.OC)
+            else:
+                msl.dense_gemm_rows_direct_out(xh, w.code, w.rout, w.K, w.IC, w.OC, 8, msl.RS)
         torch.cuda.synchronize()
-        print(json.dumps({"only": args.only, "launches": args.steps}))
+        print(json.dumps({"only": args.only, "rows": M, "launches": args.steps}))
         return
 
     step_graphs = [graphs.GraphedCall(lambda x, L=L: layer_step(L, x), [x0]) for L in sets]
