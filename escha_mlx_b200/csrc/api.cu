@@ -297,33 +297,40 @@ int escha_coded_gemv_splits(int IC, int OC, int njobs, int sm_count) {
     return static_cast<int>(s);
 }
 
-int escha_coded_projections(const void* x, const void* const* x_proj, const void* x_up,
-                            long x_stride, int x_row_div, int input_mode,
-                            int nproj, const void* const* code, const float* const* rin,
-                            const float* const* rout, void* const* out, const int* OC,
-                            const void* jobs, int njobs, int rows_per_job, int M, int E, int IC,
-                            int K, const int* splits, float rs, void* workspace,
-                            size_t workspace_bytes, void* stream) {
-    REQUIRE(nproj >= 1 && nproj <= escha::kMaxProblems, "%s: nproj=%d outside [1, %d]", __func__,
+}  // extern "C"
+
+namespace {
+int coded_projections_impl(const char* fn, const void* x, const void* const* x_proj, const void* x_up,
+                           long x_stride, int x_row_div, int input_mode,
+                           int nproj, const void* const* code, const float* const* rin,
+                           const float* const* rout, void* const* out, const int* OC,
+                           const void* jobs, int njobs, int rows_per_job, int M, int E, int IC,
+                           int K, const int* splits, float rs, void* workspace,
+                           size_t workspace_bytes, void* stream,
+                           void* const* peer_out, int npeers, const int* out_ld, const int* out_col0) {
+    REQUIRE(npeers >= 0 && npeers <= escha::kMaxPeers, "%s: npeers=%d outside [0, %d]", fn,
+            npeers, escha::kMaxPeers);
+    if (npeers > 0) REQUIRE(peer_out != nullptr, "%s: peer_out is NULL", fn);
+    REQUIRE(nproj >= 1 && nproj <= escha::kMaxProblems, "%s: nproj=%d outside [1, %d]", fn,
             nproj, escha::kMaxProblems);
-    REQUIRE(code && rout && out && OC, "%s: NULL projection table", __func__);
-    REQUIRE(input_mode >= 0 && input_mode <= 2, "%s: unknown input mode %d", __func__, input_mode);
-    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
-    REQUIRE(E >= 1, "%s: needs at least one expert stream, got E=%d", __func__, E);
+    REQUIRE(code && rout && out && OC, "%s: NULL projection table", fn);
+    REQUIRE(input_mode >= 0 && input_mode <= 2, "%s: unknown input mode %d", fn, input_mode);
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", fn, M);
+    REQUIRE(E >= 1, "%s: needs at least one expert stream, got E=%d", fn, E);
     REQUIRE_PTR(x);
     if (input_mode == escha::kInputSwiglu) REQUIRE_PTR(x_up);
     if (x_stride <= 0) x_stride = IC;
     REQUIRE(x_stride >= IC && x_stride % 8 == 0, "%s: row stride %ld must be >= IC=%d and a multiple of 8",
-            __func__, x_stride, IC);
+            fn, x_stride, IC);
     escha::GemvMmaParams p{};
     int total_ocb = 0;
     for (int i = 0; i < nproj; ++i) {
-        if (int rc = check_shape(__func__, K, IC, OC[i], 128)) return rc;
+        if (int rc = check_shape(fn, K, IC, OC[i], 128)) return rc;
         REQUIRE_PTR(code[i]);
         REQUIRE_PTR(out[i]);
         OPTIONAL_PTR(rout[i]);
         if (input_mode != escha::kInputTransformed) {
-            REQUIRE(rin != nullptr, "%s: a fused input transform needs rin", __func__);
+            REQUIRE(rin != nullptr, "%s: a fused input transform needs rin", fn);
             REQUIRE_PTR(rin[i]);
         }
         p.prob[i].code = static_cast<const uint32_t*>(code[i]);
@@ -337,27 +344,43 @@ int escha_coded_projections(const void* x, const void* const* x_proj, const void
         p.prob[i].OC = OC[i];
         p.prob[i].ocb0 = total_ocb;
         total_ocb += OC[i] / 128;
+        p.prob[i].out_ld = out_ld ? out_ld[i] : 0;
+        p.prob[i].out_col0 = out_col0 ? out_col0[i] : 0;
+        if (p.prob[i].out_ld) {
+            REQUIRE(p.prob[i].out_ld >= p.prob[i].out_col0 + OC[i] && p.prob[i].out_ld % 8 == 0 &&
+                        p.prob[i].out_col0 % 8 == 0 && p.prob[i].out_col0 >= 0,
+                    "%s: output row of %d elements cannot hold %d columns at offset %d", fn,
+                    p.prob[i].out_ld, OC[i], p.prob[i].out_col0);
+        } else {
+            REQUIRE(p.prob[i].out_col0 == 0, "%s: out_col0 needs out_ld", fn);
+        }
+        p.prob[i].npeer = npeers;
+        for (int g = 0; g < npeers; ++g) {
+            void* pp = peer_out[static_cast<size_t>(i) * npeers + g];
+            REQUIRE_PTR(pp);
+            p.prob[i].peer[g] = pp;
+        }
     }
     p.nprob = nproj;
     p.total_ocb = total_ocb;
     if (jobs) {
         REQUIRE_PTR(jobs);
         REQUIRE(rows_per_job == 8 || rows_per_job == 16, "%s: rows per job must be 8 or 16, got %d",
-                __func__, rows_per_job);
-        REQUIRE(njobs >= 1, "%s: njobs=%d", __func__, njobs);
+                fn, rows_per_job);
+        REQUIRE(njobs >= 1, "%s: njobs=%d", fn, njobs);
     } else {
         rows_per_job = M <= 8 ? 8 : 16;
         njobs = (M + rows_per_job - 1) / rows_per_job;
     }
-    REQUIRE(njobs <= 65535, "%s: %d row jobs exceed the launch grid", __func__, njobs);
+    REQUIRE(njobs <= 65535, "%s: %d row jobs exceed the launch grid", fn, njobs);
     int smax = 1;
     for (int i = 0; i < nproj; ++i) {
         int si = splits ? splits[i] : 0;
         if (si <= 0) {
-            REQUIRE(jobs == nullptr, "%s: with row jobs pass the split factor explicitly", __func__);
+            REQUIRE(jobs == nullptr, "%s: with row jobs pass the split factor explicitly", fn);
             si = escha_coded_gemv_splits(IC, OC[i], 1, 0);
         }
-        REQUIRE(si <= IC / 128 && si <= 65535, "%s: splits=%d exceeds the %d input blocks", __func__,
+        REQUIRE(si <= IC / 128 && si <= 65535, "%s: splits=%d exceeds the %d input blocks", fn,
                 si, IC / 128);
         p.prob[i].splits = si;
         if (si > smax) smax = si;
@@ -381,15 +404,63 @@ int escha_coded_projections(const void* x, const void* const* x_proj, const void
             escha_coded_gemv_workspace_bytes(njobs, total_ocb * 128, smax, rows_per_job);
         REQUIRE_PTR(workspace);
         REQUIRE(workspace_bytes >= need, "%s: workspace of %zu bytes is smaller than the %zu needed",
-                __func__, workspace_bytes, need);
+                fn, workspace_bytes, need);
         // the tail of the counter region belongs to escha_moe_route
         REQUIRE(static_cast<size_t>(njobs) * total_ocb <= kMaxCounters - kRouteCounters,
-                "%s: %d jobs x %d output blocks exceed the %zu split-K counters", __func__, njobs,
+                "%s: %d jobs x %d output blocks exceed the %zu split-K counters", fn, njobs,
                 total_ocb, kMaxCounters);
         p.counters = static_cast<int32_t*>(workspace);
         p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + kCounterBytes);
     }
-    return cuda_result(escha::launch_gemv_mma(p, as_stream(stream)), __func__);
+    return cuda_result(escha::launch_gemv_mma(p, as_stream(stream)), fn);
+}
+}  // namespace
+
+extern "C" {
+
+int escha_coded_projections(const void* x, const void* const* x_proj, const void* x_up,
+                            long x_stride, int x_row_div, int input_mode,
+                            int nproj, const void* const* code, const float* const* rin,
+                            const float* const* rout, void* const* out, const int* OC,
+                            const void* jobs, int njobs, int rows_per_job, int M, int E, int IC,
+                            int K, const int* splits, float rs, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+    return coded_projections_impl(__func__, x, x_proj, x_up, x_stride, x_row_div, input_mode, nproj,
+                                  code, rin, rout, out, OC, jobs, njobs, rows_per_job, M, E, IC, K,
+                                  splits, rs, workspace, workspace_bytes, stream, nullptr, 0, nullptr,
+                                  nullptr);
+}
+
+int escha_coded_projections_gather(const void* x, const void* const* x_proj, const void* x_up,
+                                   long x_stride, int x_row_div, int input_mode,
+                                   int nproj, const void* const* code, const float* const* rin,
+                                   const float* const* rout, void* const* out, const int* OC,
+                                   int M, int IC, int K, const int* splits, float rs,
+                                   void* workspace, size_t workspace_bytes,
+                                   void* const* peer_out, int npeers, const int* out_ld,
+                                   const int* out_col0, void* stream) {
+    REQUIRE(out_ld != nullptr && out_col0 != nullptr, "%s: out_ld and out_col0 are required", __func__);
+    return coded_projections_impl(__func__, x, x_proj, x_up, x_stride, x_row_div, input_mode, nproj,
+                                  code, rin, rout, out, OC, nullptr, 0, 0, M, 1, IC, K, splits, rs,
+                                  workspace, workspace_bytes, stream, peer_out, npeers, out_ld,
+                                  out_col0);
+}
+
+int escha_peer_barrier(int32_t* local_flags, int32_t* const* peer_flags, int rank, int nranks,
+                       void* stream) {
+    REQUIRE(nranks >= 2 && nranks <= escha::kMaxPeers + 1, "%s: nranks=%d outside [2, %d]", __func__,
+            nranks, escha::kMaxPeers + 1);
+    REQUIRE(rank >= 0 && rank < nranks, "%s: rank %d outside [0, %d)", __func__, rank, nranks);
+    REQUIRE(local_flags != nullptr && peer_flags != nullptr, "%s: NULL flags", __func__);
+    escha::PeerBarrierParams p{};
+    p.local = local_flags;
+    for (int g = 0; g < nranks; ++g) {
+        if (g != rank) REQUIRE(peer_flags[g] != nullptr, "%s: peer %d has no flags", __func__, g);
+        p.peer[g] = peer_flags[g];
+    }
+    p.rank = rank;
+    p.nranks = nranks;
+    return cuda_result(escha::launch_peer_barrier(p, as_stream(stream)), __func__);
 }
 
 int escha_coded_gemv(const void* xh, const void* code, const float* rout, int M, int IC, int OC,

@@ -58,7 +58,8 @@ inline int x_chunk_blocks(int xrows) {
 
 template <bool FUSED_OUT>
 __device__ __forceinline__ void finalize_row(float v[4], uint32_t lane, const float* rout_blk,
-                                             void* out, size_t off, float rs) {
+                                             const GemvProblem& pr, size_t off, float rs) {
+    void* const out = pr.out;
     if (FUSED_OUT) {
         const float4 sc = *reinterpret_cast<const float4*>(rout_blk + lane * 4u);
         wht128_warp(v, lane);
@@ -68,9 +69,14 @@ __device__ __forceinline__ void finalize_row(float v[4], uint32_t lane, const fl
         packed.y = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[2], rs), sc.z),
                                             __fmul_rn(__fmul_rn(v[3], rs), sc.w)));
         *reinterpret_cast<uint2*>(static_cast<__half*>(out) + off) = packed;
+        // the same block into the gathered row of every other GPU (plain stores over NVLink)
+        for (int g = 0; g < pr.npeer; ++g)
+            *reinterpret_cast<uint2*>(static_cast<__half*>(pr.peer[g]) + off) = packed;
     } else {
-        *reinterpret_cast<float4*>(static_cast<float*>(out) + off) =
-            make_float4(v[0], v[1], v[2], v[3]);
+        const float4 q = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(static_cast<float*>(out) + off) = q;
+        for (int g = 0; g < pr.npeer; ++g)
+            *reinterpret_cast<float4*>(static_cast<float*>(pr.peer[g]) + off) = q;
     }
 }
 
@@ -327,15 +333,17 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
 
     const float* rout_blk =
         pr.rout ? pr.rout + static_cast<size_t>(expert) * OC + ocb * 128u : nullptr;
+    const size_t out_ld = pr.out_ld ? static_cast<size_t>(pr.out_ld) : OC;
 
     if (S == 1) {
         for (uint32_t r = warp; r < static_cast<uint32_t>(nrows); r += 8u) {
             const float4 a4 = *reinterpret_cast<const float4*>(s_acc + r * 128u + lane * 4u);
             float v[4] = {a4.x, a4.y, a4.z, a4.w};
-            const size_t off = static_cast<size_t>(s_rows[r]) * OC + ocb * 128u + lane * 4u;
-            if (pr.rout) finalize_row<true>(v, lane, rout_blk, pr.out, off, p.rs);
-            else finalize_row<false>(v, lane, rout_blk, pr.out, off, p.rs);
+            const size_t off = static_cast<size_t>(s_rows[r]) * out_ld + pr.out_col0 + ocb * 128u + lane * 4u;
+            if (pr.rout) finalize_row<true>(v, lane, rout_blk, pr, off, p.rs);
+            else finalize_row<false>(v, lane, rout_blk, pr, off, p.rs);
         }
+        if (pr.npeer) __threadfence_system();
         return;
     }
 
@@ -372,10 +380,11 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
                 v[2] = __fadd_rn(v[2], q.z); v[3] = __fadd_rn(v[3], q.w);
             }
         }
-        const size_t off = static_cast<size_t>(s_rows[r]) * OC + ocb * 128u + lane * 4u;
-        if (pr.rout) finalize_row<true>(v, lane, rout_blk, pr.out, off, p.rs);
-        else finalize_row<false>(v, lane, rout_blk, pr.out, off, p.rs);
+        const size_t off = static_cast<size_t>(s_rows[r]) * out_ld + pr.out_col0 + ocb * 128u + lane * 4u;
+        if (pr.rout) finalize_row<true>(v, lane, rout_blk, pr, off, p.rs);
+        else finalize_row<false>(v, lane, rout_blk, pr, off, p.rs);
     }
+    if (pr.npeer) __threadfence_system();
 }
 
 template <int K, int MT>

@@ -17,6 +17,7 @@ struct RowJob {
 };
 
 constexpr int kMaxProblems = 4;
+constexpr int kMaxPeers = 7;   // other GPUs of an 8-GPU node
 
 // One projection inside a (possibly multi-projection) launch.  All projections
 // of a launch share the input rows, IC and K; each has its own stream, vectors
@@ -30,6 +31,12 @@ struct GemvProblem {
     int OC;
     int ocb0;               // index of this projection's first 128-channel block in the grid
     int splits;             // split-K factor of this projection (<= GemvMmaParams::splits)
+    // Output placement.  out_ld = elements between output rows (0: OC), out_col0 = this
+    // projection's first column inside a row.  peer[0..npeer) are the SAME buffer mapped
+    // from other GPUs: the epilogue stores its block there too, so that a split-N shard
+    // lands in every rank's gathered [M, OC_total] row without a separate all-gather.
+    int out_ld, out_col0, npeer;
+    void* peer[kMaxPeers];
 };
 
 enum GemvInput : int {
@@ -158,6 +165,14 @@ struct GemmTcParams {
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);
 cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int splits, cudaStream_t st);
 cudaError_t gemm_tc_status(int* host_status);
+
+// Cross-GPU barrier over peer-mapped flag words (peer.cu).
+struct PeerBarrierParams {
+    int32_t* local;              // this GPU's flags: [nranks] arrivals, [nranks] epoch, [nranks+1] status
+    int32_t* peer[kMaxPeers + 1];  // every rank's flags (index = rank; own entry unused)
+    int rank, nranks;
+};
+cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t st);
 
 cudaError_t launch_moe_route(const RouteParams& p, cudaStream_t st);
 size_t route_shared_bytes(int T, int top_k, int e_lo, int e_hi);

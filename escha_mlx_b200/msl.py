@@ -295,7 +295,7 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
                       jobs: torch.Tensor | None = None, E: int = 1, splits: int | None = None,
                       rs: float = RS, rows_per_job: int = 8, outs=None,
                       policy_rows: int | None = None, xs=None, rows: int | None = None,
-                      x_stride: int | None = None, x_row_div: int = 1):
+                      x_stride: int | None = None, x_row_div: int = 1, gather=None):
     """One launch of the tensor-core kernel for 1..4 projections of the same rows.
 
     ``codes``/``rins``/``routs``/``OCs`` are equal-length sequences (rins may be
@@ -309,6 +309,12 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
     r reads input row ``r // x_row_div`` at ``x_stride`` elements per row, which
     lets the first expert leg read token rows directly and the second read the
     gate/up halves of one merged tensor.
+
+    ``gather`` (dense streams, split-N tensor parallelism): a sequence with one
+    ``(peer_tensor, col0)`` per projection, ``peer_tensor`` a ``peer.PeerTensor`` of
+    shape [rows, OC_total].  The kernel stores this rank's columns at ``col0`` of the
+    local copy and of every other GPU's copy; the caller runs ``PeerGroup.barrier()``
+    before reading.  Returns the local gathered tensors.
     """
     n = len(codes)
     m = x.shape[0] if rows is None else rows
@@ -330,7 +336,7 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
         njobs = (m + rows_per_job - 1) // rows_per_job
     else:
         njobs = jobs.shape[0]
-    if outs is None:
+    if outs is None and gather is None:
         outs = [torch.empty((m, oc), dtype=torch.float32 if ro is None else torch.float16,
                             device=x.device) for oc, ro in zip(OCs, routs)]
     ws, nbytes = None, 0
@@ -354,6 +360,21 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
         x_stride = IC if x.shape[0] == 1 else x.stride(0)
     if x.stride(-1) != 1 or (x_up is not None and x_up.stride(-1) != 1):
         raise ValueError("activation rows must be contiguous along the channel axis")
+    if gather is not None:
+        if not dense:
+            raise ValueError("the fused all-gather is for dense streams, not row jobs")
+        locs = [g[0].local for g in gather]
+        npeers = len(gather[0][0].peer_ptrs())
+        flat = [p for g in gather for p in g[0].peer_ptrs()]
+        check(lib.escha_coded_projections_gather(
+            x_ptr, None if xs is None else table(xs, torch.float16), up_ptr,
+            x_stride, x_row_div, input_mode, n, table(codes), table(rins, torch.float32),
+            table(routs, torch.float32), table(locs), (ctypes.c_int * n)(*OCs), m, IC, K,
+            (ctypes.c_int * n)(*per), float(rs), ptr(ws), ctypes.c_size_t(nbytes),
+            (ctypes.c_void_p * len(flat))(*flat), npeers,
+            (ctypes.c_int * n)(*[t.shape[-1] for t in locs]),
+            (ctypes.c_int * n)(*[int(g[1]) for g in gather]), stream()))
+        return locs
     check(lib.escha_coded_projections(
         x_ptr, None if xs is None else table(xs, torch.float16), up_ptr,
         x_stride, x_row_div, input_mode, n, table(codes), table(rins, torch.float32),

@@ -1,0 +1,96 @@
+"""Peer-mapped buffers for the fused GEMV + all-gather (one process per GPU of a node).
+
+The reference is single-device; this module has no counterpart there.  Split-N
+tensor parallelism needs every rank's output columns on every rank.  Instead of a
+library all-gather after the kernel, the GEMV epilogue stores its 128-channel blocks
+straight into the gathered row of every GPU (``msl.coded_projections(gather=...)``),
+and the ranks meet in ``PeerGroup.barrier()`` -- a one-warp kernel over peer-mapped
+flag words -- before anyone reads.
+
+Buffers are ordinary CUDA allocations shared between the processes with CUDA IPC
+(the same mechanism ``torch.multiprocessing`` uses for CUDA tensors); handles travel
+through ``torch.distributed`` once, at set-up.  Nothing here is on the per-step path
+except the barrier launch.
+
+Rules for users:
+
+* a gathered buffer may be overwritten only after a later barrier has passed on every
+  rank (keep two buffers per tensor and alternate, or use one set per CUDA graph and
+  at least two graphs);
+* every rank must launch the same sequence of gathers and barriers;
+* ranks must sit on different GPUs (the barrier kernels wait for one another).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ._lib import check, lib, stream
+
+
+class PeerTensor:
+    """A tensor of identical shape on every rank, each mapped into every process."""
+
+    def __init__(self, local: torch.Tensor, views: list[torch.Tensor | None], rank: int) -> None:
+        self.local = local
+        self._views = views                 # keeps the IPC mappings alive
+        self.rank = rank
+        self.ptrs = [local.data_ptr() if r == rank else v.data_ptr() for r, v in enumerate(views)]
+
+    def peer_ptrs(self) -> list[int]:
+        """Device addresses of the other ranks' copies, in rank order."""
+        return [p for r, p in enumerate(self.ptrs) if r != self.rank]
+
+
+class PeerGroup:
+    """The GPUs of one node, as seen from this rank."""
+
+    def __init__(self, group=None) -> None:
+        if not dist.is_initialized():
+            raise RuntimeError("PeerGroup needs an initialised torch.distributed process group")
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        if not 2 <= self.size <= 8:
+            raise ValueError(f"peer groups span 2 to 8 GPUs of one node, got {self.size}")
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._flags = self.empty((self.size + 2,), torch.int32, zero=True)
+        self._flag_table = (ctypes.c_void_p * self.size)(*self._flags.ptrs)
+        dist.barrier(group)     # every rank's flag words are zero before any kernel signals
+
+    def empty(self, shape, dtype, zero: bool = False) -> PeerTensor:
+        """Allocate ``shape`` on every rank and map all copies into this process."""
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        make = torch.zeros if zero else torch.empty
+        # a dedicated allocation: an IPC handle exports the whole underlying block
+        local = make((max(numel, 1),), dtype=dtype, device=self.device)
+        torch.cuda.synchronize()
+        handle = local.untyped_storage()._share_cuda_()
+        gathered: list = [None] * self.size
+        dist.all_gather_object(gathered, handle, group=self.group)
+        views: list[torch.Tensor | None] = []
+        for r, h in enumerate(gathered):
+            if r == self.rank:
+                views.append(None)
+                continue
+            # the exporter's device index is not ours: open the handle on this device
+            storage = torch.UntypedStorage._new_shared_cuda(self.device.index, *h[1:])
+            views.append(torch.empty(0, dtype=dtype, device=self.device).set_(
+                storage, 0, (max(numel, 1),)))
+        dist.barrier(self.group)    # nobody frees or reuses before everyone has mapped
+        t = PeerTensor(local.view(*shape) if numel else local, views, self.rank)
+        return t
+
+    def barrier(self) -> None:
+        """Enqueue the cross-GPU barrier on the current stream (graph-capturable)."""
+        check(lib.escha_peer_barrier(ctypes.c_void_p(self._flags.local.data_ptr()), self._flag_table,
+                                     self.rank, self.size, stream()))
+
+    def status(self) -> int:
+        """1 if a barrier on this rank ever gave up waiting (synchronises the stream)."""
+        torch.cuda.synchronize()
+        return int(self._flags.local[self.size + 1].item())

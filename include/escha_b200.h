@@ -279,6 +279,37 @@ int escha_moe_shared_finish(const void *gu, const void *w8, const void *scale, c
                             const float *shared_gate_logit, int T, int top_k, int H, int I,
                             void *out, void *stream);
 
+/* escha_coded_projections for split-N tensor parallelism with the all-gather fused
+ * into the kernel's epilogue (no counterpart in the reference, which is
+ * single-device).  Each output out[i] is a gathered buffer [M, out_ld[i]] in which
+ * this rank's OC[i] columns start at out_col0[i]; peer_out (host table of
+ * nproj*npeers device pointers, peer g of projection i at [i*npeers+g]) holds the
+ * same buffer of every other GPU, mapped into this process (CUDA IPC / symmetric
+ * memory).  The epilogue stores each 128-channel block into out[i] and into every
+ * peer with plain stores over NVLink, then fences system-wide; follow the launch
+ * with escha_peer_barrier on every rank before anyone reads its buffer, and do not
+ * overwrite a buffer until a later barrier has passed (double-buffer across steps).
+ * Dense streams only (no row jobs).  npeers <= 7; out_ld, out_col0 multiples of 8. */
+int escha_coded_projections_gather(const void *x, const void *const *x_proj, const void *x_up,
+                                   long x_stride, int x_row_div, int input_mode, int nproj,
+                                   const void *const *code, const float *const *rin,
+                                   const float *const *rout, void *const *out, const int *OC, int M,
+                                   int IC, int K, const int *splits, float rs, void *workspace,
+                                   size_t workspace_bytes, void *const *peer_out, int npeers,
+                                   const int *out_ld, const int *out_col0, void *stream);
+
+/* Barrier between the GPUs of a node over peer-mapped flag words (no reference
+ * counterpart).  local_flags: this rank's nranks+2 int32 words, zero-initialised
+ * once, in memory the other ranks can write; peer_flags: host array of nranks
+ * device pointers, entry r = rank r's flag words mapped here (own entry ignored).
+ * One small kernel per rank: it announces a new epoch to every peer (release,
+ * system scope, after a system-wide fence) and polls until every peer has
+ * announced it.  The poll is bounded (about two seconds); if a peer never arrives
+ * word nranks+1 of local_flags is set to 1 and the kernel returns.  Ranks must run
+ * on different GPUs.  Identical launch every time: CUDA-graph replayable. */
+int escha_peer_barrier(int32_t *local_flags, int32_t *const *peer_flags, int rank, int nranks,
+                       void *stream);
+
 /* Prefill form of the coded product on the tcgen05 tensor cores, for tens to
  * hundreds of rows:  mid[r,:] = f32(xh[r,:]) @ f32(decode(code)),  f32 [M,OC].
  * Replaces msl.dense_gemm_mat and the row-blocked msl.dense_gemm_rows at prefill

@@ -25,7 +25,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from escha_mlx_b200 import dense, graphs, moe, sharding, synth  # noqa: E402
+from escha_mlx_b200 import dense, graphs, moe, msl, peer, sharding, synth  # noqa: E402
 from escha_mlx_b200.models.qwen3_5_moe import EschaSparseMoeBlock  # noqa: E402
 
 
@@ -48,6 +48,44 @@ def split_n(device, rank, size) -> None:
             for _ in range(2):
                 same(g(x), want, f"graphed split-N K={K} M={M}")
             g.close()   # NCCL's teardown waits for graphs that captured its collectives
+
+
+def fused_gather(device, rank, size) -> None:
+    """Split-N shards whose GEMV epilogue stores straight into every GPU's gathered row,
+    followed by the peer barrier: equal to the unsharded linear bit for bit."""
+    pg = peer.PeerGroup()
+    K, IC, OCs = 2, 1024, [128 * 2 * size, 128 * size]
+    rng = np.random.default_rng(5 + size)
+    ws = [dense.EschaWeight(*synth.coded_projection(rng, IC, oc, K), device=device) for oc in OCs]
+    fulls = [dense.EschaLinear(w) for w in ws]
+    shards = [w.shard_out(rank, size) for w in ws]
+    for M in (1, 3, 12):
+        x = torch.from_numpy(synth.activations(rng, M, IC)).to(device)
+        want = [f(x) for f in fulls]
+        # two buffer sets, alternated: a buffer is rewritten only after a later barrier
+        bufs = [[pg.empty((M, oc), torch.float16) for oc in OCs] for _ in range(2)]
+
+        def step(t, which):
+            gather = [(b, rank * s.OC) for b, s in zip(bufs[which], shards)]
+            outs = msl.coded_projections(t, [s.code for s in shards], [s.rin for s in shards],
+                                         [s.rout for s in shards], K, IC, [s.OC for s in shards],
+                                         input_mode=msl.INPUT_RAW, gather=gather)
+            pg.barrier()
+            return [o.clone() for o in outs]
+
+        for it in range(4):
+            got = step(x, it % 2)
+            for g, w in zip(got, want):
+                same(g, w, f"fused gather M={M} it={it}")
+        graphed = [graphs.GraphedCall(lambda t, wch=wch: step(t, wch), [x]) for wch in range(2)]
+        for it in range(4):
+            got = graphed[it % 2](x)
+            for g, w in zip(got, want):
+                same(g, w, f"graphed fused gather M={M} it={it}")
+        for g in graphed:
+            g.close()
+    if pg.status() != 0:
+        raise AssertionError(f"rank {rank}: a peer barrier gave up waiting")
 
 
 def expert_parallel(device, rank, size) -> None:
@@ -81,6 +119,7 @@ def main() -> None:
     dist.init_process_group("nccl", device_id=device)
     rank, size = dist.get_rank(), dist.get_world_size()
     split_n(device, rank, size)
+    fused_gather(device, rank, size)
     expert_parallel(device, rank, size)
     torch.cuda.synchronize()
     dist.barrier()
