@@ -22,8 +22,10 @@ Metric: compressed-weight GB/s = code bytes per step / time per step, whole job.
             host cores, bounded sample of the same layer.
 
 At N > 1 GPUs the projections are split-N tensor parallel (whole 128-channel
-output blocks per rank) with an NCCL all-gather of each projection's f16 output;
-total work is fixed, so scaling is "strong".
+output blocks per rank); the GEMV epilogue stores each rank's columns into every
+GPU's gathered row through peer-mapped memory and a bounded barrier kernel closes
+each launch (NCCL only carries set-up and the timing reduction); total work is
+fixed, so scaling is "strong".
 
 `--impl reference` times the reference's CPU implementation of the path: its
 NumPy module cannot be installed on the GPU machine (it needs mlx), so this arm
@@ -208,7 +210,8 @@ def workload_config(args, n_sets: int) -> dict:
             "projections": "q/k/v/o 2-bit 5120x{6144,1024,1024,5120}; gate/up 3-bit 5120x17408; "
                            "down 3-bit 17408x5120",
             "batch": args.batch, "code_bytes_per_step": LAYER_BYTES,
-            "parallelism": f"tp{args.gpus} split-N" if args.gpus > 1 else "single GPU",
+            "parallelism": (f"tp{args.gpus} split-N, epilogue all-gather over peer memory"
+                            if args.gpus > 1 else "single GPU"),
             "l2_policy": f"{n_sets} distinct weight sets rotated per step "
                          f"({n_sets * LAYER_BYTES // args.gpus} B per GPU > L2)"}
 
@@ -439,29 +442,58 @@ def main() -> None:
     sets = [{name: dense.EschaLinear(make_weight(ic, oc, k)) for name, ic, oc, k in LAYER}
             for _ in range(n_sets)]
 
-    def gather(y):
-        if world == 1:
-            return y
-        from escha_mlx_b200 import sharding
-        return sharding.all_gather_columns(y)
+    ROW = sum(oc for _, _, oc, _ in LAYER)     # gathered halves per activation row and layer
+    if world > 1:
+        # split-N tensor parallel: the GEMV epilogue stores each rank's columns into every
+        # GPU's gathered row (peer-mapped memory), one bounded cross-GPU barrier per launch.
+        # One buffer set per weight set: a buffer is rewritten n_sets barriers later.
+        from escha_mlx_b200 import peer
+        pg = peer.PeerGroup()
+        arena = pg.empty((n_sets * M * ROW,), torch.float16)
+        gathered = []
+        for i in range(n_sets):
+            off, bufs = i * M * ROW, {}
+            for name, _, oc, _ in LAYER:
+                bufs[name] = arena.carve(off, (M, oc))
+                off += M * oc
+            gathered.append(bufs)
 
-    def layer_step(layer, x):
+    def tp_launch(layer, bufs, names, x, x_up=None):
+        """One fused launch of the named projections' shards into their gathered buffers."""
+        ws = [layer[n]._w for n in names]
+        fuse_in = M <= msl.FUSE_INPUT_MAX_ROWS
+        if x_up is not None and not fuse_in:
+            x, x_up = msl.swiglu_pair(x.contiguous(), x_up.contiguous()), None
+        mode = (msl.INPUT_SWIGLU if x_up is not None else msl.INPUT_RAW) if fuse_in \
+            else msl.INPUT_TRANSFORMED
+        xs = None if fuse_in else [msl.dense_scaled_had(x, w.rin, msl.RS) for w in ws]
+        outs = msl.coded_projections(
+            x if fuse_in else xs[0], [w.code for w in ws], [w.rin for w in ws] if fuse_in else None,
+            [w.rout for w in ws], ws[0].K, ws[0].IC, [w.OC for w in ws], input_mode=mode,
+            x_up=x_up, rs=msl.RS, xs=xs, gather=[(bufs[n], rank * w.OC) for n, w in zip(names, ws)])
+        pg.barrier()
+        return outs
+
+    def layer_step(layer, x, bufs=None):
+        if world > 1:
+            q, k, v = tp_launch(layer, bufs, ("q_proj", "k_proj", "v_proj"), x)
+            (o,) = tp_launch(layer, bufs, ("o_proj",), x)
+            g, u = tp_launch(layer, bufs, ("gate_proj", "up_proj"), x)
+            (d,) = tp_launch(layer, bufs, ("down_proj",), g, u)   # full-width SwiGLU input
+            return q, k, v, o, d
         q, k, v = dense.project_many([layer["q_proj"], layer["k_proj"], layer["v_proj"]], x)
-        q, k, v = gather(q), gather(k), gather(v)
-        o = gather(layer["o_proj"](x))
+        o = layer["o_proj"](x)
         g, u = dense.project_pair(layer["gate_proj"], layer["up_proj"], x)
-        if world == 1:
-            d = dense.swiglu_project(layer["down_proj"], g, u)
-        else:   # down needs the full SwiGLU output: gather the shards first
-            d = gather(layer["down_proj"](gather(msl.swiglu_pair(g, u))))
+        d = dense.swiglu_project(layer["down_proj"], g, u)
         return q, k, v, o, d
 
     # launches of this library's kernels per step: fused small-batch path = q/k/v, o,
     # gate/up, swiglu+down (4); larger batches add the separate input transforms
     if M <= msl.FUSE_INPUT_MAX_ROWS:
-        launches_per_step = 4 if world == 1 else 6
+        launches_per_step = 4 if world == 1 else 8      # 4 fused GEMV + 4 peer barriers
     else:
-        launches_per_step = 11   # q/k/v 3+1, o 1+1, gate/up 1+1, swiglu 1, down 1+1
+        # q/k/v 3+1, o 1+1, gate/up 1+1 (pair transform), swiglu 1, down 1+1 (+ 4 barriers)
+        launches_per_step = 11 if world == 1 else 15
 
     x0 = torch.randn((M, HIDDEN), device=device, generator=gen).half()
 
@@ -481,7 +513,9 @@ def main() -> None:
         print(json.dumps({"only": args.only, "rows": M, "launches": args.steps}))
         return
 
-    step_graphs = [graphs.GraphedCall(lambda x, L=L: layer_step(L, x), [x0]) for L in sets]
+    step_graphs = [graphs.GraphedCall(
+        lambda x, L=L, i=i: layer_step(L, x, gathered[i] if world > 1 else None), [x0])
+        for i, L in enumerate(sets)]
 
     def sync_all():
         torch.cuda.synchronize()
@@ -559,6 +593,7 @@ def main() -> None:
         return float(t.item())
 
     ms_total, ms_e2e, ms_gemv = (max_over_ranks(v) for v in (ms_total, ms_e2e, ms_gemv))
+    barrier_gave_up = max_over_ranks(float(pg.status())) if world > 1 else 0.0
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
@@ -594,6 +629,8 @@ def main() -> None:
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
             "clocks": clocks.summary(),
         }
+        if world > 1:
+            line["peer_barrier_gave_up"] = bool(barrier_gave_up)   # must be false for a valid run
         if tensor_leg:
             tpeak, tkind = measured_peak_tflops()
             tf = flops_step / world * reps / (ms_gemv * 1e-3) / 1e12      # per GPU
@@ -634,9 +671,18 @@ def main() -> None:
         torch.cuda.synchronize()
         for g in step_graphs + gemv_graphs:
             g.close()
+        del out, gathered, arena
+        pg.close()      # unmap the other ranks' buffers while their owners are still alive
         torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
+        # Everything is released and reported.  Leave without running interpreter and
+        # library finalisers: with CUDA IPC mappings having existed in the process, their
+        # order against the CUDA runtime's own teardown is not defined (seen as a crash
+        # after the last line of main on this software stack).
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -43,6 +43,22 @@ class PeerTensor:
         """Device addresses of the other ranks' copies, in rank order."""
         return [p for r, p in enumerate(self.ptrs) if r != self.rank]
 
+    def carve(self, offset: int, shape) -> "PeerTensor":
+        """A sub-tensor of ``shape`` starting ``offset`` elements into this (flat) tensor,
+        at the same place in every rank's copy.  Offsets must keep 16-byte alignment."""
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        flat = self.local.reshape(-1)
+        if offset < 0 or offset + numel > flat.numel() or (offset * flat.element_size()) % 16:
+            raise ValueError(f"cannot carve {numel} elements at offset {offset} of {flat.numel()}")
+        sub = object.__new__(PeerTensor)
+        sub.local = flat[offset:offset + numel].view(*shape)
+        sub._views = self._views
+        sub.rank = self.rank
+        sub.ptrs = [p + offset * flat.element_size() for p in self.ptrs]
+        return sub
+
 
 class PeerGroup:
     """The GPUs of one node, as seen from this rank."""
@@ -56,6 +72,7 @@ class PeerGroup:
         if not 2 <= self.size <= 8:
             raise ValueError(f"peer groups span 2 to 8 GPUs of one node, got {self.size}")
         self.device = torch.device("cuda", torch.cuda.current_device())
+        self._made: list[PeerTensor] = []
         self._flags = self.empty((self.size + 2,), torch.int32, zero=True)
         self._flag_table = (ctypes.c_void_p * self.size)(*self._flags.ptrs)
         dist.barrier(group)     # every rank's flag words are zero before any kernel signals
@@ -83,7 +100,24 @@ class PeerGroup:
                 storage, 0, (max(numel, 1),)))
         dist.barrier(self.group)    # nobody frees or reuses before everyone has mapped
         t = PeerTensor(local.view(*shape) if numel else local, views, self.rank)
+        self._made.append(t)
         return t
+
+    def close(self) -> None:
+        """Drop every mapping of other ranks' memory made through this group.  Call on all
+        ranks, with no kernel of this group in flight, before the process group is
+        destroyed: the exporting rank must outlive its importers' mappings."""
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        for t in self._made:
+            t._views = []
+            t.local = None
+        self._made = []
+        self._flags = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
 
     def barrier(self) -> None:
         """Enqueue the cross-GPU barrier on the current stream (graph-capturable)."""

@@ -86,6 +86,8 @@ def fused_gather(device, rank, size) -> None:
             g.close()
     if pg.status() != 0:
         raise AssertionError(f"rank {rank}: a peer barrier gave up waiting")
+    del bufs, graphed
+    pg.close()
 
 
 def expert_parallel(device, rank, size) -> None:
