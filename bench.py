@@ -242,7 +242,13 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
     T = 32 if full_step else args.tokens
     cfg = workloads.MOE_35B
     er = sharding.expert_range(cfg["experts"], rank, world) if world > 1 else None
-    layers = workloads.moe_stack(MOE_LAYERS, device, attention=full_step, expert_range=er, rank=rank)
+    pg = None
+    if world > 1:
+        # expert rows travel through peer-mapped memory straight from the kernel epilogue
+        from escha_mlx_b200 import peer
+        pg = peer.PeerGroup()
+    layers = workloads.moe_stack(MOE_LAYERS, device, attention=full_step, expert_range=er, rank=rank,
+                                 peer_group=pg)
     gen = torch.Generator(device=device)
     gen.manual_seed(99)
     x0 = torch.randn((T, cfg["hidden"]), device=device, generator=gen).half()
@@ -316,9 +322,10 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
     ms_e2e = ee0.elapsed_time(ee1)
 
     if world > 1:
-        t = torch.tensor([ms_total, ms_e2e, float(code_bytes)], device=device, dtype=torch.float64)
+        t = torch.tensor([ms_total, ms_e2e, float(code_bytes), float(pg.status())], device=device,
+                         dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, ms_e2e, max_code = (float(v) for v in t.tolist())
+        ms_total, ms_e2e, max_code, gave_up = (float(v) for v in t.tolist())
         tot = torch.tensor([float(code_bytes)], device=device, dtype=torch.float64)
         dist.all_reduce(tot)
         sum_code = float(tot.item())
@@ -341,7 +348,8 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
                 "experts": "256 routed 2-bit (2048->1024, 512->2048), top-8, int8 shared expert"
                            + ("; int8 q/k/v/o 2048->{4096,512,512}, 4096->2048" if full_step else ""),
                 "tokens": T, "layers_resident": MOE_LAYERS,
-                "parallelism": f"ep{world}" if world > 1 else "single GPU",
+                "parallelism": (f"ep{world}, expert rows stored to every GPU from the kernel "
+                                "epilogue (peer memory)") if world > 1 else "single GPU",
                 "routed_experts_per_layer_avg": routed / MOE_LAYERS,
                 "max_over_mean_code_bytes_per_gpu": (max_code * world / sum_code) if sum_code else None,
                 "l2_policy": f"{MOE_LAYERS} layers of distinct weights "
@@ -358,12 +366,21 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
             "clocks": clocks.summary(),
         }
+        if world > 1:
+            line["peer_barrier_gave_up"] = bool(gave_up)   # must be false for a valid run
         print(json.dumps(line), flush=True)
     if world > 1:
         torch.cuda.synchronize()
         g.close()
+        for layer in layers:
+            layer.block._peer_bufs = {}
+        del layers
+        pg.close()
         dist.barrier()
         dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)     # see the note at the end of main()
 
 
 # --------------------------------------------------------------------------- GPU side

@@ -40,8 +40,8 @@ SIGNATURES = {
     "escha_coded_projections": (_i, [_vp, _vp, _vp, ctypes.c_long, _i, _i, _i, _vp, _vp, _vp, _vp, _vp,
                                      _vp, _i, _i, _i, _i, _i, _i, _vp, _f, _vp, _sz, _vp]),
     "escha_coded_projections_gather": (_i, [_vp, _vp, _vp, ctypes.c_long, _i, _i, _i, _vp, _vp, _vp,
-                                           _vp, _vp, _i, _i, _i, _vp, _f, _vp, _sz, _vp, _i, _vp,
-                                           _vp, _vp]),
+                                           _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _f, _vp,
+                                           _sz, _vp, _i, _vp, _vp, _vp]),
     "escha_peer_barrier": (_i, [_vp, _vp, _i, _i, _vp]),
     "escha_moe_jobs_bound": (_i, [_i, _i, _i]),
     "escha_moe_group_rows": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _vp]),

@@ -435,15 +435,16 @@ int escha_coded_projections_gather(const void* x, const void* const* x_proj, con
                                    long x_stride, int x_row_div, int input_mode,
                                    int nproj, const void* const* code, const float* const* rin,
                                    const float* const* rout, void* const* out, const int* OC,
-                                   int M, int IC, int K, const int* splits, float rs,
+                                   const void* jobs, int njobs, int rows_per_job, int M, int E,
+                                   int IC, int K, const int* splits, float rs,
                                    void* workspace, size_t workspace_bytes,
                                    void* const* peer_out, int npeers, const int* out_ld,
                                    const int* out_col0, void* stream) {
     REQUIRE(out_ld != nullptr && out_col0 != nullptr, "%s: out_ld and out_col0 are required", __func__);
     return coded_projections_impl(__func__, x, x_proj, x_up, x_stride, x_row_div, input_mode, nproj,
-                                  code, rin, rout, out, OC, nullptr, 0, 0, M, 1, IC, K, splits, rs,
-                                  workspace, workspace_bytes, stream, peer_out, npeers, out_ld,
-                                  out_col0);
+                                  code, rin, rout, out, OC, jobs, njobs, rows_per_job, M, E, IC, K,
+                                  splits, rs, workspace, workspace_bytes, stream, peer_out, npeers,
+                                  out_ld, out_col0);
 }
 
 int escha_peer_barrier(int32_t* local_flags, int32_t* const* peer_flags, int rank, int nranks,

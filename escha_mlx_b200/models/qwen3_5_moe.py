@@ -44,7 +44,7 @@ class EschaSparseMoeBlock(torch.nn.Module):
                  gu: moe.EschaExperts, dn: moe.EschaExperts,
                  gate_w: np.ndarray, shg_w: np.ndarray, shared: dict,
                  group_size: int = quant.DEFAULT_GROUP,
-                 expert_range: tuple[int, int] | None = None) -> None:
+                 expert_range: tuple[int, int] | None = None, peer_group=None) -> None:
         super().__init__()
         self.top_k = top_k
         self.num_experts = num_experts
@@ -70,6 +70,12 @@ class EschaSparseMoeBlock(torch.nn.Module):
         # gate and up of the shared expert as one [2I, H] matrix: one launch, merged output
         self._sh_gu_w8 = torch.cat([self.sh_gate._w8, self.sh_up._w8]).contiguous()
         self._sh_gu_scale = torch.cat([self.sh_gate._scale, self.sh_up._scale]).contiguous()
+        # expert parallel over peer-mapped memory (peer.PeerGroup): the second expert leg
+        # stores its rows into every GPU's buffer and one barrier kernel replaces the
+        # all-gather.  Two buffers per row count, alternated call by call.
+        self._peers = peer_group
+        self._peer_bufs: dict[int, list] = {}
+        self._peer_calls = 0
         self._mode = "fused"
         self._fused_had = msl.use_fused_had()
         self._block_env = envs.ESCHA_MLX_BLOCK_R.get()
@@ -165,6 +171,33 @@ class EschaSparseMoeBlock(torch.nn.Module):
             d16 = sharding.all_gather_rows_by_owner(d16, owned)
         return d16
 
+    def _expert_rows_to_peers(self, xf: torch.Tensor, jobs: torch.Tensor) -> torch.Tensor:
+        """Both expert legs for this rank's jobs; the second leg's epilogue stores each
+        output row into every GPU's [T*top_k, H] buffer, then the ranks meet in the peer
+        barrier.  Returns the local buffer, complete.
+
+        A buffer is rewritten two calls later; between the two, every rank must have
+        passed a later barrier (the next call's, or another layer's in the same graph).
+        A CUDA graph that holds a single call of a single block and is replayed back to
+        back does not satisfy this: capture at least two calls or two layers."""
+        gu, dn, inter = self._gu, self._dn, self._inter
+        m = xf.shape[0] * self.top_k
+        bufs = self._peer_bufs.get(m)
+        if bufs is None:
+            bufs = [self._peers.empty((m, dn.OC), torch.float16) for _ in range(2)]
+            self._peer_bufs[m] = bufs
+        buf = bufs[self._peer_calls % 2]
+        self._peer_calls += 1
+        gu16 = msl.coded_projections(xf, [gu.code], [gu.rin], [gu.rout], gu.K, gu.IC, [gu.OC],
+                                     input_mode=msl.INPUT_RAW, jobs=jobs, E=gu.E, rows=m,
+                                     x_stride=gu.IC, x_row_div=self.top_k)[0]
+        d16 = msl.coded_projections(gu16[:, :inter], [dn.code], [dn.rin], [dn.rout], dn.K, dn.IC,
+                                    [dn.OC], input_mode=msl.INPUT_SWIGLU, x_up=gu16[:, inter:],
+                                    jobs=jobs, E=dn.E, rows=m, x_stride=2 * inter,
+                                    gather=[(buf, 0)])[0]
+        self._peers.barrier()
+        return d16
+
     def _expert_path(self, xf: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
         t = xf.shape[0]
         d16 = self._expert_rows(xf, ids)
@@ -202,7 +235,13 @@ class EschaSparseMoeBlock(torch.nn.Module):
             if ids is None:
                 scores = scores_r
             sc = scores.reshape(t * self.top_k).to(torch.float32).contiguous()
-            if self._sharded():
+            if self._sharded() and self._peers is not None:
+                # expert rows land in every GPU's buffer straight from the kernel epilogue
+                d16 = self._expert_rows_to_peers(xf, jobs)
+                gu_sh = quant.w8a16(xf, self._sh_gu_w8, self._sh_gu_scale)
+                out = msl.moe_shared_finish(gu_sh, self.sh_down._w8, self.sh_down._scale, d16, sc,
+                                            slog, self.top_k)
+            elif self._sharded():
                 # one collective per block: every rank's buffer side by side; the tail
                 # picks each row from the rank that owns its expert
                 d16 = sharding.all_gather_rows(self._expert_rows(xf, ids_r, jobs, local_only=True))

@@ -310,11 +310,12 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
     lets the first expert leg read token rows directly and the second read the
     gate/up halves of one merged tensor.
 
-    ``gather`` (dense streams, split-N tensor parallelism): a sequence with one
-    ``(peer_tensor, col0)`` per projection, ``peer_tensor`` a ``peer.PeerTensor`` of
-    shape [rows, OC_total].  The kernel stores this rank's columns at ``col0`` of the
-    local copy and of every other GPU's copy; the caller runs ``PeerGroup.barrier()``
-    before reading.  Returns the local gathered tensors.
+    ``gather``: a sequence with one ``(peer_tensor, col0)`` per projection,
+    ``peer_tensor`` a ``peer.PeerTensor`` of shape [rows, row_width].  The kernel stores
+    this rank's columns at ``col0`` of the local copy and of every other GPU's copy
+    (split-N tensor parallelism: row_width = OC_total; expert parallelism with row
+    jobs: row_width = OC, col0 = 0, rows disjoint across ranks); the caller runs
+    ``PeerGroup.barrier()`` before reading.  Returns the local gathered tensors.
     """
     n = len(codes)
     m = x.shape[0] if rows is None else rows
@@ -361,15 +362,14 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
     if x.stride(-1) != 1 or (x_up is not None and x_up.stride(-1) != 1):
         raise ValueError("activation rows must be contiguous along the channel axis")
     if gather is not None:
-        if not dense:
-            raise ValueError("the fused all-gather is for dense streams, not row jobs")
         locs = [g[0].local for g in gather]
         npeers = len(gather[0][0].peer_ptrs())
         flat = [p for g in gather for p in g[0].peer_ptrs()]
         check(lib.escha_coded_projections_gather(
             x_ptr, None if xs is None else table(xs, torch.float16), up_ptr,
             x_stride, x_row_div, input_mode, n, table(codes), table(rins, torch.float32),
-            table(routs, torch.float32), table(locs), (ctypes.c_int * n)(*OCs), m, IC, K,
+            table(routs, torch.float32), table(locs), (ctypes.c_int * n)(*OCs),
+            None if dense else ptr(jobs, torch.int32), njobs, rows_per_job, m, E, IC, K,
             (ctypes.c_int * n)(*per), float(rs), ptr(ws), ctypes.c_size_t(nbytes),
             (ctypes.c_void_p * len(flat))(*flat), npeers,
             (ctypes.c_int * n)(*[t.shape[-1] for t in locs]),

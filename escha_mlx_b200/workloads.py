@@ -52,7 +52,8 @@ class MoeLayer(torch.nn.Module):
     """
 
     def __init__(self, device, gen, cfg=MOE_35B, attention: bool = False,
-                 expert_range: tuple[int, int] | None = None, gen_experts=None) -> None:
+                 expert_range: tuple[int, int] | None = None, gen_experts=None,
+                 peer_group=None) -> None:
         """``gen`` draws everything every rank replicates (router, shared expert, int8
         projections) and must be seeded alike on all ranks; ``gen_experts`` draws this
         rank's expert shard."""
@@ -72,7 +73,7 @@ class MoeLayer(torch.nn.Module):
             lin = _q8(n, kd, device, gen)
             shared[f"{name}_w8"], shared[f"{name}_scale"] = lin._w8, lin._scale
         self.block = EschaSparseMoeBlock(H, E, cfg["top_k"], gu, dn, gate_w, shg_w, shared,
-                                         expert_range=expert_range)
+                                         expert_range=expert_range, peer_group=peer_group)
         self.attention = attention
         if attention:
             qd, kvd = cfg["q_heads"] * cfg["head_dim"], cfg["kv_heads"] * cfg["head_dim"]
@@ -105,10 +106,10 @@ class MoeLayer(torch.nn.Module):
 
 def moe_stack(n_layers: int, device, seed: int = 1234, attention: bool = False,
               expert_range: tuple[int, int] | None = None, rank: int = 0,
-              cfg=MOE_35B) -> list[MoeLayer]:
+              cfg=MOE_35B, peer_group=None) -> list[MoeLayer]:
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     gen_experts = torch.Generator(device=device)
     gen_experts.manual_seed(seed + 1 + rank)
-    return [MoeLayer(device, gen, cfg, attention, expert_range, gen_experts)
+    return [MoeLayer(device, gen, cfg, attention, expert_range, gen_experts, peer_group)
             for _ in range(n_layers)]

@@ -279,21 +279,28 @@ int escha_moe_shared_finish(const void *gu, const void *w8, const void *scale, c
                             const float *shared_gate_logit, int T, int top_k, int H, int I,
                             void *out, void *stream);
 
-/* escha_coded_projections for split-N tensor parallelism with the all-gather fused
- * into the kernel's epilogue (no counterpart in the reference, which is
- * single-device).  Each output out[i] is a gathered buffer [M, out_ld[i]] in which
- * this rank's OC[i] columns start at out_col0[i]; peer_out (host table of
- * nproj*npeers device pointers, peer g of projection i at [i*npeers+g]) holds the
- * same buffer of every other GPU, mapped into this process (CUDA IPC / symmetric
- * memory).  The epilogue stores each 128-channel block into out[i] and into every
- * peer with plain stores over NVLink, then fences system-wide; follow the launch
- * with escha_peer_barrier on every rank before anyone reads its buffer, and do not
- * overwrite a buffer until a later barrier has passed (double-buffer across steps).
- * Dense streams only (no row jobs).  npeers <= 7; out_ld, out_col0 multiples of 8. */
+/* escha_coded_projections with the all-gather that follows it under multi-GPU
+ * sharding fused into the kernel's epilogue (no counterpart in the reference, which
+ * is single-device).  Arguments as escha_coded_projections, plus: each output out[i]
+ * is a gathered buffer of rows of out_ld[i] elements in which this rank's OC[i]
+ * columns start at out_col0[i]; peer_out (host table of nproj*npeers device
+ * pointers, peer g of projection i at [i*npeers+g]) holds the same buffer of every
+ * other GPU, mapped into this process (CUDA IPC / symmetric memory).  The epilogue
+ * stores each 128-channel block of each output row into out[i] and into every peer
+ * with plain stores over NVLink, then fences system-wide.
+ *   split-N tensor parallelism (dense streams): out_ld = OC_total, out_col0 = rank's
+ *     first column -- every rank ends up with the whole row;
+ *   expert parallelism (row jobs): out_ld = OC, out_col0 = 0 -- a rank's jobs cover
+ *     only the rows of its experts, rows are disjoint across ranks, and every rank
+ *     ends up with all rows.
+ * Follow the launch with escha_peer_barrier on every rank before anyone reads its
+ * buffer, and do not overwrite a buffer until a later barrier has passed
+ * (double-buffer across steps).  npeers <= 7; out_ld, out_col0 multiples of 8. */
 int escha_coded_projections_gather(const void *x, const void *const *x_proj, const void *x_up,
                                    long x_stride, int x_row_div, int input_mode, int nproj,
                                    const void *const *code, const float *const *rin,
-                                   const float *const *rout, void *const *out, const int *OC, int M,
+                                   const float *const *rout, void *const *out, const int *OC,
+                                   const void *jobs, int njobs, int rows_per_job, int M, int E,
                                    int IC, int K, const int *splits, float rs, void *workspace,
                                    size_t workspace_bytes, void *const *peer_out, int npeers,
                                    const int *out_ld, const int *out_col0, void *stream);

@@ -114,6 +114,42 @@ def expert_parallel(device, rank, size) -> None:
         g.close()
 
 
+def expert_parallel_over_peers(device, rank, size) -> None:
+    """Expert shards whose second leg stores its rows into every GPU's buffer, one peer
+    barrier per block: equal to the unsharded block bit for bit."""
+    pg = peer.PeerGroup()
+    E, H, I, top_k = 8 * size, 256, 128, 4
+    rng = np.random.default_rng(300 + size)
+    w = synth.moe_weights(rng, E, H, I, 2, 2)
+    shared = {k[3:]: v for k, v in w.items() if k.startswith("sh_")}
+
+    def block(lo, hi, pgroup):
+        gu = moe.EschaExperts(w["gu_code"][lo:hi], w["gu_rin"][lo:hi], w["gu_rout"][lo:hi], device=device)
+        dn = moe.EschaExperts(w["dn_code"][lo:hi], w["dn_rin"][lo:hi], w["dn_rout"][lo:hi], device=device)
+        return EschaSparseMoeBlock(H, E, top_k, gu, dn, w["gate_w"], w["shg_w"], shared,
+                                   expert_range=(lo, hi), peer_group=pgroup)
+
+    full = block(0, E, None)
+    part = block(*sharding.expert_range(E, rank, size), pg)
+    for T in (1, 8, 37):
+        x = torch.from_numpy(synth.activations(rng, T, H)).to(device)
+        want = full(x)
+        for it in range(3):
+            same(part(x), want, f"peer expert-parallel T={T} it={it}")
+        # two calls per graph: a buffer is reused only after the other call's barrier
+        g = graphs.GraphedCall(lambda t: torch.stack([part(t), part(t)]), [x])
+        for it in range(3):
+            both = g(x)
+            same(both[0], want, f"graphed peer expert-parallel T={T} it={it} call 0")
+            same(both[1], want, f"graphed peer expert-parallel T={T} it={it} call 1")
+        g.close()
+    if pg.status() != 0:
+        raise AssertionError(f"rank {rank}: a peer barrier gave up waiting")
+    part._peer_bufs = {}
+    del part
+    pg.close()
+
+
 def main() -> None:
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -123,6 +159,7 @@ def main() -> None:
     split_n(device, rank, size)
     fused_gather(device, rank, size)
     expert_parallel(device, rank, size)
+    expert_parallel_over_peers(device, rank, size)
     torch.cuda.synchronize()
     dist.barrier()
     print(f"MULTI_GPU_OK {rank}", flush=True)
