@@ -237,6 +237,20 @@ int escha_w8a16(const void* x, const void* w8, const void* scale, int M, int N, 
         "escha_w8a16");
 }
 
+int escha_q8_embed(const int64_t* ids, const void* w8, const void* scale, int rows, int N, int Kd,
+                   void* out, void* stream) {
+    REQUIRE(rows >= 1 && N >= 1, "%s: empty input (rows=%d N=%d)", __func__, rows, N);
+    REQUIRE(Kd >= 16 && Kd % 16 == 0, "%s: row width must be a positive multiple of 16, got %d",
+            __func__, Kd);
+    REQUIRE(ids != nullptr && scale != nullptr, "%s: NULL pointer", __func__);
+    REQUIRE_PTR(w8);
+    REQUIRE_PTR(out);
+    return cuda_result(
+        escha::launch_q8_embed(ids, static_cast<const int8_t*>(w8), static_cast<const __half*>(scale),
+                               static_cast<__half*>(out), rows, N, Kd, as_stream(stream)),
+        "escha_q8_embed");
+}
+
 int escha_gemv_ref(const void* xh, const void* code, const int32_t* row_expert,
                    const int32_t* row_map, int slots, const void* lut, int M, int IC, int OC,
                    int K, int splits, float* part, float* mid, void* stream) {

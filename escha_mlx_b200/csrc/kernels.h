@@ -143,6 +143,8 @@ cudaError_t launch_moe_combine(const __half* d16, const float* scores, int T, in
 cudaError_t launch_had128(const float* x, float* out, long nblocks, cudaStream_t st);
 cudaError_t launch_w8a16(const __half* x, const int8_t* w8, const __half* scale, __half* y, int M,
                          int N, int Kd, cudaStream_t st);
+cudaError_t launch_q8_embed(const int64_t* ids, const int8_t* w8, const __half* scale, __half* out,
+                            int rows, int N, int Kd, cudaStream_t st);
 size_t gemv_mma_part_floats(int njobs, int splits, int total_ocb, int rows_per_job);
 
 // Used by the entry point that carries its own scratch (noalloc.cu): record an

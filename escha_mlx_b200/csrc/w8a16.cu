@@ -70,7 +70,42 @@ w8a16_kernel(const __half* __restrict__ x, const int8_t* __restrict__ w8,
     }
 }
 
+// Embedding rows of an int8 table: out[r, :] = f16( f32(w8[ids[r], :]) * f32(scale[ids[r]]) ),
+// the per-weight rounding of the int8 linear (EschaQ8Embedding, escha_mlx/quant.py:249-262).
+// One warp per row, 16 weights per lane and step.
+__global__ void __launch_bounds__(256)
+q8_embed_kernel(const int64_t* __restrict__ ids, const int8_t* __restrict__ w8,
+                const __half* __restrict__ scale, __half* __restrict__ out, int rows, int N, int Kd) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    long id = ids[r];
+    if (id < 0 || id >= N) id = 0;   // callers validate; never read out of bounds
+    const __half2 sc2 = __half2half2(scale[id]);
+    const int8_t* wrow = w8 + static_cast<size_t>(id) * Kd;
+    __half* orow = out + static_cast<size_t>(r) * Kd;
+    for (uint32_t k = lane * 16u; k < static_cast<uint32_t>(Kd); k += 512u) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k);
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            o[2 * q] = as_u32(__hmul2(i8x2_to_half2(ww[q], 0x4140u), sc2));
+            o[2 * q + 1] = as_u32(__hmul2(i8x2_to_half2(ww[q], 0x4342u), sc2));
+        }
+        uint4* dst = reinterpret_cast<uint4*>(orow + k);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_q8_embed(const int64_t* ids, const int8_t* w8, const __half* scale, __half* out,
+                            int rows, int N, int Kd, cudaStream_t st) {
+    q8_embed_kernel<<<(rows + 7) / 8, 256, 0, st>>>(ids, w8, scale, out, rows, N, Kd);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_w8a16(const __half* x, const int8_t* w8, const __half* scale, __half* y, int M,
                          int N, int Kd, cudaStream_t st) {

@@ -73,6 +73,7 @@ class EschaSparseMoeBlock(torch.nn.Module):
         # expert parallel over peer-mapped memory (peer.PeerGroup): the second expert leg
         # stores its rows into every GPU's buffer and one barrier kernel replaces the
         # all-gather.  Two buffers per row count, alternated call by call.
+        self._side: torch.cuda.Stream | None = None
         self._peers = peer_group
         self._peer_bufs: dict[int, list] = {}
         self._peer_calls = 0
@@ -229,6 +230,16 @@ class EschaSparseMoeBlock(torch.nn.Module):
         xf = x.reshape(-1, hdim).to(torch.float16).contiguous()
         if self._single_pass():
             t = xf.shape[0]
+            # the shared expert's gate/up linear depends on nothing but x: it runs on a
+            # second stream beside the router and the expert legs (a fork/join that a
+            # CUDA-graph capture records as parallel branches)
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream()
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                gu_sh = quant.w8a16(xf, self._sh_gu_w8, self._sh_gu_scale)
+            gu_sh.record_stream(main)
             ids_r, scores_r, slog, jobs = msl.moe_route(
                 xf, self.gate_weight, self.shared_expert_gate_weight.reshape(-1), self.top_k,
                 self.num_experts, ids=ids, expert_range=(self._e_lo, self._e_hi))
@@ -238,21 +249,21 @@ class EschaSparseMoeBlock(torch.nn.Module):
             if self._sharded() and self._peers is not None:
                 # expert rows land in every GPU's buffer straight from the kernel epilogue
                 d16 = self._expert_rows_to_peers(xf, jobs)
-                gu_sh = quant.w8a16(xf, self._sh_gu_w8, self._sh_gu_scale)
+                main.wait_stream(self._side)
                 out = msl.moe_shared_finish(gu_sh, self.sh_down._w8, self.sh_down._scale, d16, sc,
                                             slog, self.top_k)
             elif self._sharded():
                 # one collective per block: every rank's buffer side by side; the tail
                 # picks each row from the rank that owns its expert
                 d16 = sharding.all_gather_rows(self._expert_rows(xf, ids_r, jobs, local_only=True))
-                gu_sh = quant.w8a16(xf, self._sh_gu_w8, self._sh_gu_scale)
+                main.wait_stream(self._side)
                 out = msl.moe_shared_finish(
                     gu_sh, self.sh_down._w8, self.sh_down._scale, d16, sc, slog, self.top_k,
                     ids=ids_r.reshape(-1).to(torch.int32).contiguous(),
                     experts_per_rank=self._e_hi - self._e_lo)
             else:
                 d16 = self._expert_rows(xf, ids_r, jobs)
-                gu_sh = quant.w8a16(xf, self._sh_gu_w8, self._sh_gu_scale)
+                main.wait_stream(self._side)
                 out = msl.moe_shared_finish(gu_sh, self.sh_down._w8, self.sh_down._scale, d16, sc,
                                             slog, self.top_k)
             return out.to(x.dtype).reshape(shape)

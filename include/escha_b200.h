@@ -90,6 +90,13 @@ int escha_had128(const float *x, long nblocks, float *out, void *stream);
 int escha_w8a16(const void *x, const void *w8, const void *scale, int M, int N, int Kd, void *y,
                 void *stream);
 
+/* Embedding lookup in an int8 table with one binary16 scale per row:
+ *   out[r,:] = f16( f32(w8[ids[r],:]) * f32(scale[ids[r]]) ),  ids int64 [rows],
+ * w8 [N,Kd] int8, out [rows,Kd] binary16, Kd a multiple of 16.  Replaces
+ * EschaQ8Embedding's mx.dequantize of gathered rows (escha_mlx/quant.py:249-262). */
+int escha_q8_embed(const int64_t *ids, const void *w8, const void *scale, int rows, int N, int Kd,
+                   void *out, void *stream);
+
 /* Per-row coded GEMV in the reference kernels' exact accumulation order
  * (bit-identical to them for a given input):
  *     mid[r,:] = f32(xh[r,:]) @ f32(decode(code[row_expert[r]]))      f32 [M,OC]

@@ -403,3 +403,24 @@ def test_single_pass_block_matches_op_by_op(cuda, monkeypatch):
     assert not staged_blk._single_pass()
     staged = staged_blk(x, ids, scores)
     assert rel_err(host(fused), host(staged)) < 2e-3
+
+
+# --------------------------------------------------------------------------- int8 head / embedding
+
+def test_q8_head_and_embedding(cuda, oracle):
+    rng = np.random.default_rng(8)
+    V, Kd = 1024, 256
+    w8, sc = synth.int8_linear(rng, V, Kd)
+    head = quant.make_head(w8, sc, device=cuda)
+    for rows in (1, 8):
+        x = synth.activations(rng, rows, Kd)
+        got = host(quant.q8_head(dev(x, cuda), head._w8, head._scale))
+        assert rel_err(got, oracle.w8a16(x, w8, sc)) < 2e-3
+        assert np.array_equal(bits(got), bits(host(head(dev(x, cuda)))))
+    with pytest.raises(ValueError, match="1..8 rows"):
+        quant.q8_head(dev(synth.activations(rng, 9, Kd), cuda), head._w8, head._scale)
+    emb = quant.make_embedding(w8, sc, device=cuda)
+    ids = rng.integers(0, V, size=(3, 5))
+    got = host(emb(torch.from_numpy(ids).to(cuda)))
+    want = (w8[ids].astype(np.float32) * sc.astype(np.float32)[ids][..., None]).astype(np.float16)
+    assert got.shape == (3, 5, Kd) and np.array_equal(bits(got), bits(want))
