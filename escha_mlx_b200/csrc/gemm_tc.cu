@@ -15,8 +15,9 @@
 //   1 code warp      streams the CTA's slice of the code into a shared-memory ring with
 //                    bulk copies (cp.async.bulk, no multicast), so the decode warps
 //                    never wait on a global load.
-//   2 loader warps   copy the matching slice of the activations (cp.async, 16 bytes
-//                    per lane, 128 contiguous bytes per row) into the same ring.
+//   1 loader thread  brings the matching slice of the activations with one tiled TMA load
+//                    per chunk (cp.async.bulk.tensor, 128-byte swizzle, no multicast;
+//                    rows past M are zero-filled) into a ring of its own.
 //   1 issuing thread feeds tcgen05.mma (M = 128 rows x N = 128 channels x K = 16 per
 //                    instruction, both operands from shared memory) with fp32
 //                    accumulators in tensor memory; tcgen05.commit hands each ring
@@ -30,6 +31,8 @@
 //
 // Every wait on an mbarrier is bounded; a wait that gives up raises the status word,
 // the CTA drains, frees its tensor memory and leaves.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -37,15 +40,15 @@ namespace escha {
 
 namespace {
 
-constexpr int kStages = 4;
+constexpr int kBStages = 6;                       // decoded-weight ring (16 KiB slots)
+constexpr int kAStages = 3;                       // activation ring (16 KiB per 128 rows per slot)
 constexpr int kChunkK = 64;                       // input channels per ring slot
 constexpr int kTileN = 128;                       // output channels per CTA
 constexpr int kBBytes = kTileN * kChunkK * 2;     // 16 KiB of decoded weights per slot
 constexpr int kABytesPerMt = 128 * kChunkK * 2;   // 16 KiB of activations per 128 rows
-constexpr int kDecodeWarps = 16, kLoaderWarps = 2;
-constexpr int kLoadDepth = 3;                     // activation chunks a loader warp keeps in flight
+constexpr int kDecodeWarps = 16;
 constexpr int kCodeStages = 6;                    // code-stream ring depth (chunks)
-constexpr int kThreadsTc = (kDecodeWarps + kLoaderWarps + 2) * 32;   // + issuing warp + code warp
+constexpr int kThreadsTc = (kDecodeWarps + 3) * 32;   // + activation loader, issuing and code warps
 
 __device__ int g_gemm_status = 0;
 
@@ -125,38 +128,56 @@ __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) {
     return row * 128u + ((chunk ^ (row & 7u)) << 4);
 }
 
+// 2-D tiled TMA load (no multicast): box at element coordinates (x, y) of the tensor the
+// map describes -> shared memory, completion counted in bytes on an mbarrier of this CTA.
+// x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int32_t x, int32_t y,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
 template <int K, int MT>
 __global__ void __launch_bounds__(kThreadsTc, 1)
-gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
+gemm_tc_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ CUtensorMap xmap) {
     constexpr int WPT = 8 * K;
-    constexpr uint32_t kSlotBytes = kBBytes + MT * kABytesPerMt;
+    constexpr uint32_t kABytes = MT * kABytesPerMt;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[kStages], s_empty[kStages], s_done;
-    __shared__ __align__(8) uint64_t s_cfull[kCodeStages], s_cempty[kCodeStages];
+    __shared__ __align__(8) uint64_t s_bfull[kBStages], s_bempty[kBStages];
+    __shared__ __align__(8) uint64_t s_afull[kAStages], s_aempty[kAStages];
+    __shared__ __align__(8) uint64_t s_cfull[kCodeStages], s_cempty[kCodeStages], s_done;
     __shared__ uint32_t s_tmem;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t ocb = blockIdx.x, split = blockIdx.y, r0 = blockIdx.z * (128u * MT);
     // dynamic shared memory is only guaranteed 16-byte alignment: round up to the
     // 1024 bytes the swizzle pattern is anchored to
-    const uint32_t ring0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t full0 = smem_u32(s_full), empty0 = smem_u32(s_empty), done = smem_u32(&s_done);
-    const uint32_t cfull0 = smem_u32(s_cfull), cempty0 = smem_u32(s_cempty);
+    const uint32_t aring = (smem_u32(smem_raw) + 1023u) & ~1023u;   // [kAStages][rows][128 B]
+    const uint32_t bring = aring + kAStages * kABytes;              // [kBStages][128][128 B]
+    const uint32_t bfull0 = smem_u32(s_bfull), bempty0 = smem_u32(s_bempty);
+    const uint32_t afull0 = smem_u32(s_afull), aempty0 = smem_u32(s_aempty);
+    const uint32_t cfull0 = smem_u32(s_cfull), cempty0 = smem_u32(s_cempty), done = smem_u32(&s_done);
     constexpr uint32_t kRowBytes = 8u * WPT * 4u;          // one tile row of the CTA's 8 tile columns
     constexpr uint32_t kCodeChunkBytes = 4u * kRowBytes;   // four tile rows = 64 input channels
-    const uint32_t code0 = ring0 + kStages * kSlotBytes;   // code ring follows the operand ring
+    const uint32_t code0 = bring + kBStages * kBBytes;     // code ring follows the operand rings
 
     const uint32_t nchunk_all = static_cast<uint32_t>(p.IC) / kChunkK;
     const uint32_t S = p.splits, cbase = nchunk_all / S, crem = nchunk_all % S;
     const uint32_t c_first = split * cbase + min(split, crem);
     const uint32_t nchunk = cbase + (split < crem ? 1u : 0u);
-    auto chunk_at = [&](uint32_t c) { return c_first + c; };
 
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(full0 + 8u * s, kDecodeWarps + kLoaderWarps);
-            mbar_init(empty0 + 8u * s, 1u);
+        for (int s = 0; s < kBStages; ++s) {
+            mbar_init(bfull0 + 8u * s, kDecodeWarps);
+            mbar_init(bempty0 + 8u * s, 1u);
+        }
+#pragma unroll
+        for (int s = 0; s < kAStages; ++s) {
+            mbar_init(afull0 + 8u * s, 1u);    // the loader's arrive.expect_tx
+            mbar_init(aempty0 + 8u * s, 1u);
         }
 #pragma unroll
         for (int s = 0; s < kCodeStages; ++s) {
@@ -187,87 +208,73 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
         const uint32_t my_words = code0 + q0 * kRowBytes + wn * (WPT * 4u);
         const uint32_t row_lo = 16u * wn + g, row_hi = row_lo + 8u;
         for (uint32_t c = 0; c < nchunk; ++c) {
-            {
-                // this warp's two tiles of the chunk: two words per lane and tile from the code ring
-                const uint32_t cslot = c % kCodeStages;
-                if (!mbar_wait_relaxed(cfull0 + 8u * cslot, (c / kCodeStages) & 1u)) {
+            // this warp's two tiles of the chunk: two words per lane and tile from the code ring
+            const uint32_t cslot = c % kCodeStages;
+            if (!mbar_wait_relaxed(cfull0 + 8u * cslot, (c / kCodeStages) & 1u)) {
+                ok = false;
+                break;
+            }
+            uint32_t wa[2], wb[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const uint32_t tp = my_words + cslot * kCodeChunkBytes + q * kRowBytes;
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(wa[q]) : "r"(tp + 4u * lc.ia()));
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(wb[q]) : "r"(tp + 4u * lc.ib()));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cempty0 + 8u * cslot);
+            uint32_t a[2][8];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint32_t s[8];
+                lc.states(wa[q], wb[q], muls, s);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a[q][j] = cba_decode_dup(s[j], hmask, hxor);
+            }
+            const uint32_t slot = c % kBStages;
+            if (c >= kBStages && !mbar_wait_relaxed(bempty0 + 8u * slot, ((c / kBStages) - 1u) & 1u)) {
+                ok = false;
+                break;
+            }
+            const uint32_t bslot = bring + slot * kBBytes;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                // value j sits at (channel g + 8*(j>=4), input 2t + (j&1) + 8*((j>>1)&1)) of
+                // its tile row: pairs (0,1), (2,3), (4,5), (6,7) are two consecutive inputs
+                const uint32_t c_lo = 2u * (q0 + q), c_hi = c_lo + 1u;   // 16-byte chunks of the row
+                const uint32_t p01 = prmt(a[q][0], a[q][1], 0x5410u), p23 = prmt(a[q][2], a[q][3], 0x5410u);
+                const uint32_t p45 = prmt(a[q][4], a[q][5], 0x5410u), p67 = prmt(a[q][6], a[q][7], 0x5410u);
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_lo) + 4u * t), "r"(p01) : "memory");
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_hi) + 4u * t), "r"(p23) : "memory");
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_lo) + 4u * t), "r"(p45) : "memory");
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_hi) + 4u * t), "r"(p67) : "memory");
+            }
+            fence_async_proxy();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bfull0 + 8u * slot);
+        }
+    } else if (warp == kDecodeWarps) {
+        // ---- activation loader: one tiled TMA load per chunk (rows r0.., 64 channels, written
+        // in the 128-byte swizzle; rows past M are filled with zeros by the copy engine)
+        if (lane == 0) {
+            for (uint32_t c = 0; c < nchunk; ++c) {
+                const uint32_t slot = c % kAStages;
+                if (c >= kAStages && !mbar_wait_relaxed(aempty0 + 8u * slot, ((c / kAStages) - 1u) & 1u)) {
                     ok = false;
                     break;
                 }
-                uint32_t wa[2], wb[2];
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const uint32_t tp = my_words + cslot * kCodeChunkBytes + q * kRowBytes;
-                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(wa[q]) : "r"(tp + 4u * lc.ia()));
-                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(wb[q]) : "r"(tp + 4u * lc.ib()));
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(cempty0 + 8u * cslot);
-                const uint32_t slot = c % kStages;
-                uint32_t a[2][8];
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    uint32_t s[8];
-                    lc.states(wa[q], wb[q], muls, s);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) a[q][j] = cba_decode_dup(s[j], hmask, hxor);
-                }
-                if (c >= kStages && !mbar_wait_relaxed(empty0 + 8u * slot, ((c / kStages) - 1u) & 1u)) {
-                    ok = false;
-                    break;
-                }
-                const uint32_t bslot = ring0 + slot * kSlotBytes;
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    // value j sits at (channel g + 8*(j>=4), input 2t + (j&1) + 8*((j>>1)&1)) of
-                    // its tile row: pairs (0,1), (2,3), (4,5), (6,7) are two consecutive inputs
-                    const uint32_t c_lo = 2u * (q0 + q), c_hi = c_lo + 1u;   // 16-byte chunks of the row
-                    const uint32_t p01 = prmt(a[q][0], a[q][1], 0x5410u), p23 = prmt(a[q][2], a[q][3], 0x5410u);
-                    const uint32_t p45 = prmt(a[q][4], a[q][5], 0x5410u), p67 = prmt(a[q][6], a[q][7], 0x5410u);
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_lo) + 4u * t), "r"(p01) : "memory");
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_lo, c_hi) + 4u * t), "r"(p23) : "memory");
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_lo) + 4u * t), "r"(p45) : "memory");
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(bslot + sw128(row_hi, c_hi) + 4u * t), "r"(p67) : "memory");
-                }
-                fence_async_proxy();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + 8u * slot);
+                mbar_arrive_expect_tx(afull0 + 8u * slot, kABytes);
+                tma_load_2d(aring + slot * kABytes, &xmap, static_cast<int32_t>((c_first + c) * kChunkK),
+                            static_cast<int32_t>(r0), afull0 + 8u * slot);
             }
         }
-    } else if (warp < kDecodeWarps + kLoaderWarps) {
-        // ---- loader warps: rows of xh for each chunk, 8 lanes x 16 bytes per row; up to
-        // kLoadDepth chunks' copies are in flight before the oldest is published
-        const uint32_t lw = warp - kDecodeWarps;
-        const uint32_t sub = lane >> 3, chunk = lane & 7u;          // 4 rows per instruction
-        for (uint32_t c = 0; c < nchunk + kLoadDepth - 1u; ++c) {
-            if (c < nchunk) {
-                const uint32_t slot = c % kStages;
-                if (c >= kStages && !mbar_wait_relaxed(empty0 + 8u * slot, ((c / kStages) - 1u) & 1u)) {
-                    ok = false;
-                    break;
-                }
-                const uint32_t aslot = ring0 + slot * kSlotBytes + kBBytes;
-                const size_t k0 = static_cast<size_t>(chunk_at(c)) * kChunkK + chunk * 8u;
-                for (uint32_t rr = lw * 4u + sub; rr < 128u * MT; rr += 4u * kLoaderWarps) {
-                    const uint32_t row = min(r0 + rr, static_cast<uint32_t>(p.M) - 1u);
-                    cp_async16_shared(aslot + sw128(rr, chunk), p.xh + static_cast<size_t>(row) * p.IC + k0);
-                }
-            }
-            cp_async_commit();   // an empty group past the last chunk keeps the count uniform
-            if (c + 1u >= kLoadDepth) {
-                cp_async_wait<kLoadDepth - 1>();
-                fence_async_proxy();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + 8u * ((c + 1u - kLoadDepth) % kStages));
-            }
-        }
-    } else if (warp == kDecodeWarps + kLoaderWarps + 1) {
+    } else if (warp == kDecodeWarps + 2) {
         // ---- code warp: bulk copies (TMA, untiled, no multicast) of the CTA's slice of the
         // code stream, one copy per tile row (8 tiles side by side), four rows per chunk
         const uint32_t TN = static_cast<uint32_t>(p.OC) >> 4;
         const size_t kt_words = static_cast<size_t>(TN) * WPT;   // words from tile row kt to kt+1
-        const uint32_t* grow0 = p.code + static_cast<size_t>(lane) * kt_words +
-                                static_cast<size_t>(ocb) * 8u * WPT;
+        const uint32_t* grow = p.code + (static_cast<size_t>(c_first) * 4u + lane) * kt_words +
+                               static_cast<size_t>(ocb) * 8u * WPT;
         for (uint32_t c = 0; c < nchunk; ++c) {
             const uint32_t cslot = c % kCodeStages;
             if (c >= kCodeStages &&
@@ -278,20 +285,21 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
             if (lane == 0) mbar_arrive_expect_tx(cfull0 + 8u * cslot, kCodeChunkBytes);
             __syncwarp();
             if (lane < 4)
-                bulk_copy_g2s(code0 + cslot * kCodeChunkBytes + lane * kRowBytes,
-                              grow0 + static_cast<size_t>(chunk_at(c)) * 4u * kt_words, kRowBytes,
+                bulk_copy_g2s(code0 + cslot * kCodeChunkBytes + lane * kRowBytes, grow, kRowBytes,
                               cfull0 + 8u * cslot);
+            grow += 4u * kt_words;
         }
     } else if (lane == 0) {
-        // ---- the issuing thread
+        // ---- the issuing thread (warp kDecodeWarps + 1)
         for (uint32_t c = 0; c < nchunk; ++c) {
-            const uint32_t slot = c % kStages;
-            if (!mbar_wait_relaxed(full0 + 8u * slot, (c / kStages) & 1u)) {
+            const uint32_t bs = c % kBStages, as = c % kAStages;
+            if (!mbar_wait_relaxed(bfull0 + 8u * bs, (c / kBStages) & 1u) ||
+                !mbar_wait_relaxed(afull0 + 8u * as, (c / kAStages) & 1u)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t bslot = ring0 + slot * kSlotBytes, aslot = bslot + kBBytes;
+            const uint32_t bslot = bring + bs * kBBytes, aslot = aring + as * kABytes;
 #pragma unroll
             for (uint32_t k16 = 0; k16 < kChunkK / 16; ++k16) {
                 const uint64_t db = smem_desc_sw128(bslot + 32u * k16);
@@ -301,7 +309,9 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
                     umma_f16(tmem + mt * 128u, da, db, kIdesc, (c | k16) != 0u);
                 }
             }
-            umma_commit(empty0 + 8u * slot);   // the slot is free once these MMAs have read it
+            // both slots are free once these MMAs have read them
+            umma_commit(bempty0 + 8u * bs);
+            umma_commit(aempty0 + 8u * as);
         }
         if (ok) umma_commit(done);
     }
@@ -342,9 +352,37 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
     if (warp == 0) tmem_dealloc(tmem, 128u * MT);
 }
 
+// cuTensorMapEncodeTiled, resolved through the runtime (the library does not link libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+cudaError_t encode_x_map(CUtensorMap* map, const __half* xh, int M, int IC, int rows_per_box) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+        if (e != cudaSuccess) return e;
+        if (q != cudaDriverEntryPointSuccess || !sym) return cudaErrorNotSupported;
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(IC), static_cast<cuuint64_t>(M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(IC) * 2u};   // bytes between rows
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kChunkK), static_cast<cuuint32_t>(rows_per_box)};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2u, const_cast<__half*>(xh), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 template <int K, int MT>
 cudaError_t launch_tc(const GemmTcParams& p, cudaStream_t st) {
-    const size_t smem = static_cast<size_t>(kStages) * (kBBytes + MT * kABytesPerMt) +
+    const size_t smem = static_cast<size_t>(kAStages) * MT * kABytesPerMt +
+                        static_cast<size_t>(kBStages) * kBBytes +
                         static_cast<size_t>(kCodeStages) * 4u * (8u * 8u * K * 4u) + 1024;
     static bool configured[64] = {false};
     int dev = 0;
@@ -356,8 +394,11 @@ cudaError_t launch_tc(const GemmTcParams& p, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
+    CUtensorMap xmap;
+    e = encode_x_map(&xmap, p.xh, p.M, p.IC, 128 * MT);
+    if (e != cudaSuccess) return e;
     const dim3 grid(p.OC / 128, p.splits, (p.M + 128 * MT - 1) / (128 * MT));
-    gemm_tc_kernel<K, MT><<<grid, kThreadsTc, smem, st>>>(p);
+    gemm_tc_kernel<K, MT><<<grid, kThreadsTc, smem, st>>>(p, xmap);
     return cudaGetLastError();
 }
 
