@@ -18,8 +18,8 @@
 //   1 loader thread  brings the matching slice of the activations with one tiled TMA load
 //                    per chunk (cp.async.bulk.tensor, 128-byte swizzle, no multicast;
 //                    rows past M are zero-filled) into a ring of its own.
-//   1 issuing thread feeds tcgen05.mma (M = 128 rows x N = 128 channels x K = 16 per
-//                    instruction, both operands from shared memory) with fp32
+//   1 issuing thread feeds tcgen05.mma (M = 128 channels x N = 128 or 256 rows x K = 16
+//                    per instruction, both operands from shared memory) with fp32
 //                    accumulators in tensor memory; tcgen05.commit hands each ring
 //                    slot back to the producers when the tensor core is done with it.
 //   4 warps          read the accumulators back with tcgen05.ld and store fp32.
@@ -120,8 +120,11 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (uint64_t(1) << 16) |
            (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
 }
-// Instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128, N = 128.
-constexpr uint32_t kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128 (output
+// channels: the decoded weights are the A operand), N = rows of activations (128 or 256).
+__host__ __device__ constexpr uint32_t idesc_for(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
 
 // byte offset of (row, 16-byte chunk) inside a swizzled [rows][128 B] tile
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) {
@@ -300,15 +303,12 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ C
             }
             tc_fence_after_sync();
             const uint32_t bslot = bring + bs * kBBytes, aslot = aring + as * kABytes;
+            // D[channel][row] += W[channel][k] * X[row][k]: one instruction per 16 channels of
+            // K covers all 128 x (128 MT) outputs, so each weight tile is fetched once
 #pragma unroll
-            for (uint32_t k16 = 0; k16 < kChunkK / 16; ++k16) {
-                const uint64_t db = smem_desc_sw128(bslot + 32u * k16);
-#pragma unroll
-                for (uint32_t mt = 0; mt < MT; ++mt) {
-                    const uint64_t da = smem_desc_sw128(aslot + mt * kABytesPerMt + 32u * k16);
-                    umma_f16(tmem + mt * 128u, da, db, kIdesc, (c | k16) != 0u);
-                }
-            }
+            for (uint32_t k16 = 0; k16 < kChunkK / 16; ++k16)
+                umma_f16(tmem, smem_desc_sw128(bslot + 32u * k16), smem_desc_sw128(aslot + 32u * k16),
+                         idesc_for(128u * MT), (c | k16) != 0u);
             // both slots are free once these MMAs have read them
             umma_commit(bempty0 + 8u * bs);
             umma_commit(aempty0 + 8u * as);
@@ -317,7 +317,8 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ C
     }
     if (!ok && lane == 0) atomicExch(&g_gemm_status, 1);
 
-    // ---- epilogue: warps 0..3 own accumulator lanes 32w .. 32w+31 (= rows of the tile)
+    // ---- epilogue: warps 0..3 own accumulator lanes 32w .. 32w+31 (= output channels of the
+    // block); columns are activation rows.  For one row a warp stores 32 consecutive floats.
     if (warp < 4) {
         bool ready = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0 && nchunk > 0;
         if (ready && !mbar_wait_relaxed(done, 0u)) {
@@ -326,23 +327,18 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ C
         }
         tc_fence_after_sync();
         if (ready) {
-            float* plane = p.out + static_cast<size_t>(split) * p.M * p.OC;
+            float* plane = p.out + static_cast<size_t>(split) * p.M * p.OC + ocb * 128u + 32u * warp + lane;
+#pragma unroll 1
+            for (uint32_t col = 0; col < 128u * MT; col += 16u) {
+                if (r0 + col >= static_cast<uint32_t>(p.M)) break;   // uniform: no rows left
+                uint32_t v[16];
+                tmem_ld16(tmem + ((32u * warp) << 16) + col, v);
+                tmem_ld_wait();
 #pragma unroll
-            for (uint32_t mt = 0; mt < MT; ++mt) {
-                const uint32_t row = r0 + mt * 128u + 32u * warp + lane;
-#pragma unroll
-                for (uint32_t col = 0; col < 128u; col += 16u) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem + ((32u * warp) << 16) + mt * 128u + col, v);
-                    tmem_ld_wait();
-                    if (row < static_cast<uint32_t>(p.M)) {
-                        float4* dst = reinterpret_cast<float4*>(
-                            plane + static_cast<size_t>(row) * p.OC + ocb * 128u + col);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-                    }
+                for (uint32_t i = 0; i < 16u; ++i) {
+                    const uint32_t row = r0 + col + i;
+                    if (row < static_cast<uint32_t>(p.M))
+                        plane[static_cast<size_t>(row) * p.OC] = __uint_as_float(v[i]);
                 }
             }
         }
