@@ -383,6 +383,39 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
         os._exit(0)     # see the note at the end of main()
 
 
+def moe_leg(device, tokens: int, replays: int = 10) -> dict:
+    """Second half of the headline metric inside the default run: one 35B-A3B-class MoE
+    decode layer at `tokens` tokens (the `--workload moe` measurement, shortened)."""
+    import torch
+    from escha_mlx_b200 import graphs, workloads
+    cfg = workloads.MOE_35B
+    layers = workloads.moe_stack(MOE_LAYERS, device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(99)
+    x0 = torch.randn((tokens, cfg["hidden"]), device=device, generator=gen).half()
+
+    def pass_(x):
+        out = None
+        for layer in layers:
+            out = layer(x)
+        return out
+    g = graphs.GraphedCall(pass_, [x0])
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (replays * MOE_LAYERS)
+    g.close()
+    return {"metric": "MoE decode-layer tokens/s", "tokens": tokens, "us_per_layer": us,
+            "tokens_per_s": tokens / (us * 1e-6), "layers_resident": MOE_LAYERS,
+            "workload": f"moe35b_layer_decode_t{tokens} (see --workload moe)"}
+
+
 # --------------------------------------------------------------------------- GPU side
 
 def main() -> None:
@@ -400,6 +433,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=8, help="tokens per step for --workload moe")
     ap.add_argument("--cpu-seconds", type=float, default=10.0,
                     help="bounded CPU-baseline sample (rank 0, N=1)")
+    ap.add_argument("--no-moe-leg", action="store_true",
+                    help="skip the short MoE-layer measurement appended to the default line")
     ap.add_argument("--only", default=None,
                     help="profiling aid: run just this projection's GEMV for --steps launches")
     args = ap.parse_args()
@@ -666,6 +701,8 @@ def main() -> None:
                          "e2e": {"value": flops_step * args.steps / (ms_e2e * 1e-3) / 1e12,
                                  "unit": "TFLOP/s", "h2d_bytes_per_step": M * HIDDEN * 2,
                                  "d2h_bytes_per_step": M * HIDDEN * 2}})
+        if world == 1 and not prefill and not args.no_moe_leg:
+            line["moe"] = moe_leg(device, 8)
         if world == 1:
             cpu_rows = min(M, 16)
             cpu_gbs, passes, dt, cores = time_cpu(cpu_rows, args.cpu_seconds, 200)
