@@ -51,7 +51,7 @@ SIGNATURES = {
                                    _sz, _vp, _vp]),
     "escha_swiglu": (_i, [_vp, _vp, _i, _i, ctypes.c_long, _vp, _vp]),
     "escha_moe_combine": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
-    "escha_coded_gemm_tc": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "escha_coded_gemm_tc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
     "escha_coded_gemm_tc_splits": (_i, [_i, _i, _i]),
     "escha_coded_gemm_tc_status": (_i, []),
     "escha_moe_route": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,

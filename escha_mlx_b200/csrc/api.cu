@@ -658,29 +658,35 @@ int escha_coded_gemm_tc_splits(int IC, int OC, int sm_count) {
     return static_cast<int>(s);
 }
 
-int escha_coded_gemm_tc(const void* xh, const void* code, int M, int IC, int OC, int K, int splits,
-                        float* planes, float* mid, void* stream) {
+int escha_coded_gemm_tc(const void* xh, const void* code, const float* rout, int M, int IC, int OC,
+                        int K, int splits, float rs, float* planes, void* out, void* stream) {
     if (int rc = check_shape(__func__, K, IC, OC, 128)) return rc;
     REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
     REQUIRE_PTR(xh);
     REQUIRE_PTR(code);
-    REQUIRE_PTR(mid);
+    REQUIRE_PTR(out);
+    OPTIONAL_PTR(rout);
     if (splits <= 0) splits = escha_coded_gemm_tc_splits(IC, OC, 0);
     REQUIRE(splits <= IC / 64 && splits <= 65535, "%s: splits=%d exceeds the %d 64-channel chunks",
             __func__, splits, IC / 64);
     REQUIRE((M + 255) / 256 <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
-    if (splits > 1) REQUIRE_PTR(planes);
+    const bool need_planes = splits > 1 || rout != nullptr;
+    if (need_planes) REQUIRE_PTR(planes);
     escha::GemmTcParams p{};
     p.code = static_cast<const uint32_t*>(code);
     p.xh = static_cast<const __half*>(xh);
-    p.out = splits > 1 ? planes : mid;
+    p.out = need_planes ? planes : static_cast<float*>(out);
     p.M = M; p.IC = IC; p.OC = OC; p.K = K; p.splits = splits;
     p.hash_mask = 0x8FFF8FFFu;
     p.hash_xor = 0x3B603B60u;
     p.mul2 = 2u; p.mul4 = 4u; p.mul16 = 16u; p.mul32 = 32u; p.mul64 = 64u; p.mul128 = 128u;
     cudaError_t e = escha::launch_gemm_tc(p, as_stream(stream));
-    if (e == cudaSuccess && splits > 1)
-        e = escha::launch_sum_planes(planes, mid, static_cast<size_t>(M) * OC, splits, as_stream(stream));
+    if (e == cudaSuccess && rout != nullptr)
+        e = escha::launch_planes_out(planes, rout, static_cast<__half*>(out), M, OC, splits, rs,
+                                     as_stream(stream));
+    else if (e == cudaSuccess && splits > 1)
+        e = escha::launch_sum_planes(planes, static_cast<float*>(out), static_cast<size_t>(M) * OC,
+                                     splits, as_stream(stream));
     return cuda_result(e, "escha_coded_gemm_tc");
 }
 

@@ -422,6 +422,46 @@ __global__ void sum_planes_kernel(const float4* __restrict__ planes, float4* __r
 }
 }  // namespace
 
+namespace {
+// y = f16( (H128(plane0 + plane1 + ...) * rs) * rout ): the split-order sum and the output
+// transform (escha_mlx/ref.py:226-228) in one pass; one warp per (row, 128-channel block).
+__global__ void __launch_bounds__(256)
+planes_out_kernel(const float* __restrict__ planes, const float* __restrict__ rout,
+                  __half* __restrict__ y, int M, int OC, int splits, float rs) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t per_row = static_cast<uint32_t>(OC) >> 7;
+    const uint32_t row = unit / per_row;
+    if (row >= static_cast<uint32_t>(M)) return;
+    const uint32_t blk = unit - row * per_row;
+    const size_t off = static_cast<size_t>(row) * OC + blk * 128u + lane * 4u;
+    const size_t plane = static_cast<size_t>(M) * OC;
+    const float4 a = *reinterpret_cast<const float4*>(planes + off);
+    float v[4] = {a.x, a.y, a.z, a.w};
+    for (int s = 1; s < splits; ++s) {
+        const float4 b = *reinterpret_cast<const float4*>(planes + s * plane + off);
+        v[0] = __fadd_rn(v[0], b.x); v[1] = __fadd_rn(v[1], b.y);
+        v[2] = __fadd_rn(v[2], b.z); v[3] = __fadd_rn(v[3], b.w);
+    }
+    wht128_warp(v, lane);
+    const float4 sc = *reinterpret_cast<const float4*>(rout + blk * 128u + lane * 4u);
+    uint2 packed;
+    packed.x = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[0], rs), sc.x),
+                                        __fmul_rn(__fmul_rn(v[1], rs), sc.y)));
+    packed.y = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[2], rs), sc.z),
+                                        __fmul_rn(__fmul_rn(v[3], rs), sc.w)));
+    *reinterpret_cast<uint2*>(y + off) = packed;
+}
+}  // namespace
+
+cudaError_t launch_planes_out(const float* planes, const float* rout, __half* y, int M, int OC,
+                              int splits, float rs, cudaStream_t st) {
+    const long units = static_cast<long>(M) * (OC / 128);
+    planes_out_kernel<<<static_cast<unsigned>((units + 7) / 8), 256, 0, st>>>(planes, rout, y, M, OC,
+                                                                            splits, rs);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int splits, cudaStream_t st) {
     const size_t n4 = n / 4;
     sum_planes_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, st>>>(

@@ -165,6 +165,8 @@ struct GemmTcParams {
     uint32_t mul2, mul4, mul16, mul32, mul64, mul128;
 };
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);
+cudaError_t launch_planes_out(const float* planes, const float* rout, __half* y, int M, int OC,
+                              int splits, float rs, cudaStream_t st);
 cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int splits, cudaStream_t st);
 cudaError_t gemm_tc_status(int* host_status);
 

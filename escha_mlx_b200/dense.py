@@ -212,7 +212,7 @@ class EschaLinear(torch.nn.Module):
         if msl.use_prefill_kernel(rows.shape[0]):
             # prefill: decode once per 256 rows into shared memory, contract on tcgen05
             w = self._w
-            y = self._output_rows(msl.dense_gemm_tc(xh, w.code, w.K, w.IC, w.OC))
+            y = msl.dense_gemm_tc(xh, w.code, w.K, w.IC, w.OC, rout=w.rout, rs=RS)
         elif self._fused_had:
             y = msl.dense_gemm_rows_direct_out(
                 xh, self._w.code, self._w.rout, self.K, self._w.IC, self._w.OC,

@@ -646,16 +646,22 @@ def moe_shared_finish(gu: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor, d
 
 
 def dense_gemm_tc(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int, OC: int,
-                  splits: int | None = None) -> torch.Tensor:
-    """Prefill coded GEMM on the tcgen05 tensor cores -> mid f32 [M, OC]
-    (the product of dense_gemm_mat, msl.py:1608-1782, decoded once per 256 rows)."""
+                  splits: int | None = None, rout: torch.Tensor | None = None,
+                  rs: float = RS) -> torch.Tensor:
+    """Prefill coded GEMM on the tcgen05 tensor cores (the product of dense_gemm_mat,
+    msl.py:1608-1782, decoded once per 256 rows).  Returns mid f32 [M, OC], or with
+    ``rout`` the transformed output f16 [M, OC] (split-order sum and output transform
+    as one second kernel)."""
     _check_code(code_u32)
     m = xh.shape[0]
     if m < 1:
         raise ValueError("dense_gemm_tc needs at least one row")
     s = int(lib.escha_coded_gemm_tc_splits(IC, OC, 0)) if splits is None else int(splits)
-    mid = torch.empty((m, OC), dtype=torch.float32, device=xh.device)
-    planes = torch.empty((s, m, OC), dtype=torch.float32, device=xh.device) if s > 1 else None
-    check(lib.escha_coded_gemm_tc(ptr(xh, torch.float16), ptr(code_u32), m, IC, OC, K, s,
-                                  ptr(planes), ptr(mid), stream()))
-    return mid
+    out = torch.empty((m, OC), dtype=torch.float32 if rout is None else torch.float16,
+                      device=xh.device)
+    planes = torch.empty((s, m, OC), dtype=torch.float32, device=xh.device) \
+        if (s > 1 or rout is not None) else None
+    check(lib.escha_coded_gemm_tc(ptr(xh, torch.float16), ptr(code_u32),
+                                  ptr(rout, torch.float32) if rout is not None else None,
+                                  m, IC, OC, K, s, float(rs), ptr(planes), ptr(out), stream()))
+    return out

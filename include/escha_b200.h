@@ -332,11 +332,13 @@ int escha_peer_barrier(int32_t *local_flags, int32_t *const *peer_flags, int ran
  * accumulators in tensor memory.  Reassociated like dense_gemm_mat, deterministic:
  * tolerance-equal to escha_gemv_ref, bit-reproducible for fixed (shape, splits).
  *   xh [M,IC] binary16 (already input-transformed), code [IC/16, OC/16, 8K].
- *   splits <= 0 selects escha_coded_gemm_tc_splits(); with splits > 1 `planes` must
- *   hold splits*M*OC floats of scratch (summed into mid in split order).
- * The output transform is escha_scaled_had_out on mid. */
-int escha_coded_gemm_tc(const void *xh, const void *code, int M, int IC, int OC, int K, int splits,
-                        float *planes, float *mid, void *stream);
+ *   rout == NULL: out is f32 mid [M,OC];  rout != NULL: out is binary16
+ *     y = f16((H128(mid)*rs)*rout), the split-order sum and the output transform
+ *     (msl.dense_scaled_had_out, ref.py:226-228) running as one second kernel.
+ *   splits <= 0 selects escha_coded_gemm_tc_splits().  `planes` is scratch of
+ *     splits*M*OC floats, needed when splits > 1 or rout != NULL. */
+int escha_coded_gemm_tc(const void *xh, const void *code, const float *rout, int M, int IC, int OC,
+                        int K, int splits, float rs, float *planes, void *out, void *stream);
 
 /* Split policy of escha_coded_gemm_tc (shape only; sm_count <= 0 queries the device). */
 int escha_coded_gemm_tc_splits(int IC, int OC, int sm_count);

@@ -77,3 +77,16 @@ def test_dense_linear_prefill_path(cuda, oracle, monkeypatch, M):
     assert torch.equal(lin(dev(x, cuda)), y)
     a, b = dense.project_pair(lin, lin, dev(x, cuda))
     assert torch.equal(a, y) and torch.equal(b, y)
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_prefill_fused_output_equals_separate_transform(cuda, splits):
+    rng = np.random.default_rng(splits)
+    K, IC, OC, M = 3, 768, 256, 100
+    code, _, rout = synth.coded_projection(rng, IC, OC, K)
+    xh = (rng.standard_normal((M, IC)) * 0.25).astype(np.float16)
+    c, xd = msl.code_tensor(code, cuda), dev(xh, cuda)
+    ro = dev(rout.astype(np.float32), cuda)
+    fused = msl.dense_gemm_tc(xd, c, K, IC, OC, splits=splits, rout=ro)
+    separate = msl.dense_scaled_had_out(msl.dense_gemm_tc(xd, c, K, IC, OC, splits=splits), ro, msl.RS)
+    assert torch.equal(fused, separate)
