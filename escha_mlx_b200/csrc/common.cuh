@@ -12,6 +12,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 namespace escha {
 
 constexpr float kRS = 0.088388347648f;  // 1/sqrt(128) as the format pins it (ref.py:30)
@@ -264,6 +266,25 @@ __device__ __forceinline__ void grid_launch_dependents() {
 }
 __device__ __forceinline__ void grid_dependency_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Host side of the same: launch `kernel` so that it may be scheduled while the previous
+// kernel of the stream drains.  The kernel must call grid_dependency_wait() before it
+// touches anything an earlier kernel may have written.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

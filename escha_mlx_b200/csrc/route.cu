@@ -56,6 +56,9 @@ moe_route_kernel(const RouteParams p) {
     const int n_rows = n_gate + (p.shg_w ? 1 : 0);
     const int r = blockIdx.x, tile = blockIdx.y, t0 = tile * 8;
     const int n_tiles = gridDim.y;
+    // scheduled early (programmatic dependent launch): wait for the producer of x
+    grid_launch_dependents();
+    grid_dependency_wait();
 
     // ---- phase 1: this CTA's row against the tile's tokens
     if (r < n_rows) {
@@ -224,8 +227,7 @@ cudaError_t launch_moe_route(const RouteParams& p, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    moe_route_kernel<<<grid, 256, smem, st>>>(p);
-    return cudaGetLastError();
+    return launch_dependent(moe_route_kernel, grid, dim3(256), smem, st, p);
 }
 
 }  // namespace escha

@@ -75,6 +75,9 @@ w8a16_mma_kernel(const Q8Params p) {
     const int r0 = blockIdx.y * (8 * NT);
     const int chunks = p.Kd >> 6;
     const int cbase = chunks / 8, crem = chunks % 8;
+    // scheduled early (programmatic dependent launch): wait for the producers of the inputs
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int c0 = warp * cbase + min(warp, crem), cn = cbase + (warp < crem ? 1 : 0);
 
     const int8_t* wa_row = p.w8 + static_cast<size_t>(n0 + g) * p.Kd + 16 * t;
@@ -165,12 +168,11 @@ cudaError_t launch_nt(const Q8Params& p, cudaStream_t st) {
     const int nt = (rows + 7) / 8;
     const dim3 grid(p.N / 16, (p.M + 8 * nt - 1) / (8 * nt));
     switch (nt) {
-        case 1: w8a16_mma_kernel<1, IN, EP><<<grid, 256, 0, st>>>(p); break;
-        case 2: w8a16_mma_kernel<2, IN, EP><<<grid, 256, 0, st>>>(p); break;
-        case 3: w8a16_mma_kernel<3, IN, EP><<<grid, 256, 0, st>>>(p); break;
-        default: w8a16_mma_kernel<4, IN, EP><<<grid, 256, 0, st>>>(p); break;
+        case 1: return launch_dependent(w8a16_mma_kernel<1, IN, EP>, grid, dim3(256), 0, st, p);
+        case 2: return launch_dependent(w8a16_mma_kernel<2, IN, EP>, grid, dim3(256), 0, st, p);
+        case 3: return launch_dependent(w8a16_mma_kernel<3, IN, EP>, grid, dim3(256), 0, st, p);
+        default: return launch_dependent(w8a16_mma_kernel<4, IN, EP>, grid, dim3(256), 0, st, p);
     }
-    return cudaGetLastError();
 }
 
 }  // namespace
