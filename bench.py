@@ -210,8 +210,7 @@ def workload_config(args, n_sets: int) -> dict:
             "projections": "q/k/v/o 2-bit 5120x{6144,1024,1024,5120}; gate/up 3-bit 5120x17408; "
                            "down 3-bit 17408x5120",
             "batch": args.batch, "code_bytes_per_step": LAYER_BYTES,
-            "parallelism": (f"tp{args.gpus} split-N, epilogue all-gather over peer memory"
-                            if args.gpus > 1 else "single GPU"),
+            "parallelism": (f"tp{args.gpus} split-N" if args.gpus > 1 else "single GPU"),
             "l2_policy": f"{n_sets} distinct weight sets rotated per step "
                          f"({n_sets * LAYER_BYTES // args.gpus} B per GPU > L2)"}
 
@@ -246,7 +245,12 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
     if world > 1:
         # expert rows travel through peer-mapped memory straight from the kernel epilogue
         from escha_mlx_b200 import peer
-        pg = peer.PeerGroup()
+        try:
+            pg = peer.PeerGroup()
+        except peer.PeerUnavailable as e:       # raised on every rank together
+            pg = None
+            if rank == 0:
+                print(f"bench.py: {e}; falling back to NCCL all-gathers", file=sys.stderr)
     layers = workloads.moe_stack(MOE_LAYERS, device, attention=full_step, expert_range=er, rank=rank,
                                  peer_group=pg)
     gen = torch.Generator(device=device)
@@ -322,7 +326,8 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
     ms_e2e = ee0.elapsed_time(ee1)
 
     if world > 1:
-        t = torch.tensor([ms_total, ms_e2e, float(code_bytes), float(pg.status())], device=device,
+        t = torch.tensor([ms_total, ms_e2e, float(code_bytes),
+                          float(pg.status()) if pg is not None else 0.0], device=device,
                          dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total, ms_e2e, max_code, gave_up = (float(v) for v in t.tolist())
@@ -348,8 +353,10 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
                 "experts": "256 routed 2-bit (2048->1024, 512->2048), top-8, int8 shared expert"
                            + ("; int8 q/k/v/o 2048->{4096,512,512}, 4096->2048" if full_step else ""),
                 "tokens": T, "layers_resident": MOE_LAYERS,
-                "parallelism": (f"ep{world}, expert rows stored to every GPU from the kernel "
-                                "epilogue (peer memory)") if world > 1 else "single GPU",
+                "parallelism": (f"ep{world}, " + ("expert rows stored to every GPU from the kernel "
+                                                  "epilogue (peer memory)" if pg is not None
+                                                  else "NCCL all-gather of expert rows"))
+                if world > 1 else "single GPU",
                 "routed_experts_per_layer_avg": routed / MOE_LAYERS,
                 "max_over_mean_code_bytes_per_gpu": (max_code * world / sum_code) if sum_code else None,
                 "l2_policy": f"{MOE_LAYERS} layers of distinct weights "
@@ -375,7 +382,8 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
         for layer in layers:
             layer.block._peer_bufs = {}
         del layers
-        pg.close()
+        if pg is not None:
+            pg.close()
         dist.barrier()
         dist.destroy_process_group()
         sys.stdout.flush()
@@ -495,15 +503,20 @@ def main() -> None:
             for _ in range(n_sets)]
 
     ROW = sum(oc for _, _, oc, _ in LAYER)     # gathered halves per activation row and layer
+    pg, arena, gathered = None, None, []
     if world > 1:
         # split-N tensor parallel: the GEMV epilogue stores each rank's columns into every
         # GPU's gathered row (peer-mapped memory), one bounded cross-GPU barrier per launch.
         # One buffer set per weight set: a buffer is rewritten n_sets barriers later.
-        from escha_mlx_b200 import peer
-        pg = peer.PeerGroup()
-        arena = pg.empty((n_sets * M * ROW,), torch.float16)
-        gathered = []
-        for i in range(n_sets):
+        from escha_mlx_b200 import peer, sharding
+        try:
+            pg = peer.PeerGroup()
+            arena = pg.empty((n_sets * M * ROW,), torch.float16)
+        except peer.PeerUnavailable as e:       # raised on every rank together
+            pg = arena = None
+            if rank == 0:
+                print(f"bench.py: {e}; falling back to NCCL all-gathers", file=sys.stderr)
+        for i in range(n_sets if pg is not None else 0):
             off, bufs = i * M * ROW, {}
             for name, _, oc, _ in LAYER:
                 bufs[name] = arena.carve(off, (M, oc))
@@ -527,6 +540,15 @@ def main() -> None:
         return outs
 
     def layer_step(layer, x, bufs=None):
+        if world > 1 and pg is None:
+            # NCCL form of the same exchange: an all-gather of every projection's f16 output
+            ag = sharding.all_gather_columns
+            q, k, v = (ag(t) for t in dense.project_many(
+                [layer["q_proj"], layer["k_proj"], layer["v_proj"]], x))
+            o = ag(layer["o_proj"](x))
+            g, u = (ag(t) for t in dense.project_pair(layer["gate_proj"], layer["up_proj"], x))
+            d = ag(dense.swiglu_project(layer["down_proj"], g, u))
+            return q, k, v, o, d
         if world > 1:
             q, k, v = tp_launch(layer, bufs, ("q_proj", "k_proj", "v_proj"), x)
             (o,) = tp_launch(layer, bufs, ("o_proj",), x)
@@ -566,7 +588,7 @@ def main() -> None:
         return
 
     step_graphs = [graphs.GraphedCall(
-        lambda x, L=L, i=i: layer_step(L, x, gathered[i] if world > 1 else None), [x0])
+        lambda x, L=L, i=i: layer_step(L, x, gathered[i] if gathered else None), [x0])
         for i, L in enumerate(sets)]
 
     def sync_all():
@@ -645,7 +667,7 @@ def main() -> None:
         return float(t.item())
 
     ms_total, ms_e2e, ms_gemv = (max_over_ranks(v) for v in (ms_total, ms_e2e, ms_gemv))
-    barrier_gave_up = max_over_ranks(float(pg.status())) if world > 1 else 0.0
+    barrier_gave_up = max_over_ranks(float(pg.status())) if (world > 1 and pg is not None) else 0.0
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
@@ -682,6 +704,9 @@ def main() -> None:
             "clocks": clocks.summary(),
         }
         if world > 1:
+            line["config"]["exchange"] = ("GEMV epilogue stores into every GPU's gathered row "
+                                          "(peer memory) + barrier kernel" if pg is not None
+                                          else "NCCL all-gather per projection")
             line["peer_barrier_gave_up"] = bool(barrier_gave_up)   # must be false for a valid run
         if tensor_leg:
             tpeak, tkind = measured_peak_tflops()
@@ -726,7 +751,8 @@ def main() -> None:
         for g in step_graphs + gemv_graphs:
             g.close()
         del out, gathered, arena
-        pg.close()      # unmap the other ranks' buffers while their owners are still alive
+        if pg is not None:
+            pg.close()  # unmap the other ranks' buffers while their owners are still alive
         torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()

@@ -94,7 +94,7 @@ __device__ __forceinline__ __half swiglu_half(__half g16, __half u16) {
 __device__ __forceinline__ void stage_activations(const GemvMmaParams& p, const __half* xsrc, const float* rin,
                                                   const int* s_rows, int nrows, uint32_t blk0,
                                                   uint32_t cnt, uint32_t* s_x, uint32_t XS,
-                                                  uint32_t tid) {
+                                                  uint32_t tid, uint32_t dup) {
     const uint32_t lane = tid & 31u, warp = tid >> 5;
     if (p.input == kInputTransformed) {
         const uint32_t grp_per_row = cnt * 8u;  // 16-channel groups per row
@@ -107,10 +107,11 @@ __device__ __forceinline__ void stage_activations(const GemvMmaParams& p, const 
             const uint4 lo = src[0], hi = src[1];  // channels 0..7 and 8..15 of the group
             uint4* dst = reinterpret_cast<uint4*>(s_x + r * XS + v * 16u);
             // staged order c0 c8 c1 c9 ... c7 c15, each as a (x, 0) word
-            dst[0] = make_uint4(lo.x & 0xFFFFu, hi.x & 0xFFFFu, lo.x >> 16, hi.x >> 16);
-            dst[1] = make_uint4(lo.y & 0xFFFFu, hi.y & 0xFFFFu, lo.y >> 16, hi.y >> 16);
-            dst[2] = make_uint4(lo.z & 0xFFFFu, hi.z & 0xFFFFu, lo.z >> 16, hi.z >> 16);
-            dst[3] = make_uint4(lo.w & 0xFFFFu, hi.w & 0xFFFFu, lo.w >> 16, hi.w >> 16);
+            // dup = 1: (x, 0) words; dup = 0x10001: (x, x) words (see kernel comment on SUM)
+            dst[0] = make_uint4((lo.x & 0xFFFFu) * dup, (hi.x & 0xFFFFu) * dup, (lo.x >> 16) * dup, (hi.x >> 16) * dup);
+            dst[1] = make_uint4((lo.y & 0xFFFFu) * dup, (hi.y & 0xFFFFu) * dup, (lo.y >> 16) * dup, (hi.y >> 16) * dup);
+            dst[2] = make_uint4((lo.z & 0xFFFFu) * dup, (hi.z & 0xFFFFu) * dup, (lo.z >> 16) * dup, (hi.z >> 16) * dup);
+            dst[3] = make_uint4((lo.w & 0xFFFFu) * dup, (hi.w & 0xFFFFu) * dup, (lo.w >> 16) * dup, (hi.w >> 16) * dup);
         }
         return;
     }
@@ -139,10 +140,10 @@ __device__ __forceinline__ void stage_activations(const GemvMmaParams& p, const 
         // c = 4*(lane%4)+i within it, staged at word 2*(c%8) + c/8
         uint32_t* dst = s_x + r * XS + b * 128u + (lane >> 2) * 16u + ((lane & 1u) * 8u) +
                         ((lane >> 1) & 1u);
-        dst[0] = __half_as_ushort(__float2half_rn(__fmul_rn(v[0], p.rs)));
-        dst[2] = __half_as_ushort(__float2half_rn(__fmul_rn(v[1], p.rs)));
-        dst[4] = __half_as_ushort(__float2half_rn(__fmul_rn(v[2], p.rs)));
-        dst[6] = __half_as_ushort(__float2half_rn(__fmul_rn(v[3], p.rs)));
+        dst[0] = __half_as_ushort(__float2half_rn(__fmul_rn(v[0], p.rs))) * dup;
+        dst[2] = __half_as_ushort(__float2half_rn(__fmul_rn(v[1], p.rs))) * dup;
+        dst[4] = __half_as_ushort(__float2half_rn(__fmul_rn(v[2], p.rs))) * dup;
+        dst[6] = __half_as_ushort(__float2half_rn(__fmul_rn(v[3], p.rs))) * dup;
     }
 }
 
@@ -152,7 +153,13 @@ __device__ int g_gemv_status = 0;
 constexpr int kConsumerThreads = 256;   // 8 decode warps
 constexpr int kThreads = kConsumerThreads + 32;  // + 1 producer warp
 
-template <int K, int MT>
+// SUM = false (the default): each weight is rounded to binary16 exactly as the format
+// defines it, w = f16(lo) + f16(hi), kept as (w, w) against (x, 0).  SUM = true (opt-in,
+// ESCHA_B200_WEIGHT_SUM=tensor): the two halves go to the tensor core un-added, (lo, hi)
+// against (x, x), so the product uses lo + hi without the binary16 rounding of the sum:
+// one instruction fewer per weight, outputs within 3e-4 (max-norm) of the exact-weight
+// product instead of 2e-7.
+template <int K, int MT, bool SUM>
 __global__ void __launch_bounds__(kThreads, 3)
 gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     constexpr int WPT = 8 * K;
@@ -282,7 +289,8 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     for (uint32_t c0 = 0; c0 < nb && ok; c0 += XCB) {
         const uint32_t cnt = min(XCB, nb - c0);
         named_barrier_sync(1, kConsumerThreads);
-        stage_activations(p, xsrc, rin, s_rows, nrows, b0 + c0, cnt, s_x, XS, tid);
+        stage_activations(p, xsrc, rin, s_rows, nrows, b0 + c0, cnt, s_x, XS, tid,
+                          SUM ? 0x10001u : 1u);
         named_barrier_sync(1, kConsumerThreads);
         for (uint32_t cb = 0; cb < cnt; ++cb) {
             if (!mbar_wait(full0 + 8u * slot, phase)) { ok = false; break; }
@@ -296,7 +304,8 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
                 uint32_t s[8], a[8];
                 lc.states(wa[kk * ROW_WORDS], wb[kk * ROW_WORDS], muls, s);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) a[j] = cba_decode_dup(s[j], hmask, hxor);
+                for (int j = 0; j < 8; ++j)
+                    a[j] = SUM ? cba_hash_halves(s[j], hmask, hxor) : cba_decode_dup(s[j], hmask, hxor);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     // (x[2t], x[2t+8], x[2t+1], x[2t+9]) as (x, 0) words
@@ -387,7 +396,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     if (pr.npeer) __threadfence_system();
 }
 
-template <int K, int MT>
+template <int K, int MT, bool SUM>
 cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
     constexpr int STAGE_WORDS = 8 * 8 * 8 * K;
     const size_t XS = static_cast<size_t>(p.xcb) * 128u + 16u;
@@ -398,7 +407,7 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64 || smem > configured[dev]) {
-        e = cudaFuncSetAttribute(gemv_mma_kernel<K, MT>,
+        e = cudaFuncSetAttribute(gemv_mma_kernel<K, MT, SUM>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem));
         if (e != cudaSuccess) return e;
@@ -414,7 +423,7 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.pdl != kPdlOff ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<K, MT>, p);
+    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<K, MT, SUM>, p);
 }
 
 }  // namespace
@@ -434,6 +443,16 @@ static int pdl_mode() {
     return mode;
 }
 
+// ESCHA_B200_WEIGHT_SUM=tensor selects the un-rounded lo + hi product (see the kernel);
+// read once per process.  Anything else, or unset: exact binary16 weights.
+static bool weight_sum_in_tensor_core() {
+    static const bool on = [] {
+        const char* v = std::getenv("ESCHA_B200_WEIGHT_SUM");
+        return v != nullptr && !std::strcmp(v, "tensor");
+    }();
+    return on;
+}
+
 size_t gemv_mma_part_floats(int njobs, int splits, int total_ocb, int rows_per_job) {
     if (splits <= 1) return 0;
     return static_cast<size_t>(njobs) * splits * total_ocb * rows_per_job * 128u;
@@ -445,8 +464,12 @@ cudaError_t launch_gemv_mma(const GemvMmaParams& params, cudaStream_t st) {
     const int xrows = p.jobs ? rows : (p.M < rows ? p.M : rows);
     p.xcb = x_chunk_blocks(xrows);
     p.pdl = pdl_mode();
-    if (p.K == 2) return rows == 8 ? launch_t<2, 1>(p, xrows, st) : launch_t<2, 2>(p, xrows, st);
-    return rows == 8 ? launch_t<3, 1>(p, xrows, st) : launch_t<3, 2>(p, xrows, st);
+    if (weight_sum_in_tensor_core()) {
+        if (p.K == 2) return rows == 8 ? launch_t<2, 1, true>(p, xrows, st) : launch_t<2, 2, true>(p, xrows, st);
+        return rows == 8 ? launch_t<3, 1, true>(p, xrows, st) : launch_t<3, 2, true>(p, xrows, st);
+    }
+    if (p.K == 2) return rows == 8 ? launch_t<2, 1, false>(p, xrows, st) : launch_t<2, 2, false>(p, xrows, st);
+    return rows == 8 ? launch_t<3, 1, false>(p, xrows, st) : launch_t<3, 2, false>(p, xrows, st);
 }
 
 }  // namespace escha

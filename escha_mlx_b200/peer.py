@@ -30,6 +30,11 @@ import torch.distributed as dist
 from ._lib import check, lib, stream
 
 
+class PeerUnavailable(RuntimeError):
+    """Raised on EVERY rank when any rank could not map its peers' memory (no CUDA IPC in
+    this environment, no peer access between two GPUs ...): callers fall back to NCCL."""
+
+
 class PeerTensor:
     """A tensor of identical shape on every rank, each mapped into every process."""
 
@@ -86,19 +91,33 @@ class PeerGroup:
         # a dedicated allocation: an IPC handle exports the whole underlying block
         local = make((max(numel, 1),), dtype=dtype, device=self.device)
         torch.cuda.synchronize()
-        handle = local.untyped_storage()._share_cuda_()
+        error, handle = None, None
+        try:
+            handle = local.untyped_storage()._share_cuda_()
+        except Exception as e:                      # noqa: BLE001 -- reported collectively below
+            error = e
         gathered: list = [None] * self.size
         dist.all_gather_object(gathered, handle, group=self.group)
         views: list[torch.Tensor | None] = []
         for r, h in enumerate(gathered):
-            if r == self.rank:
+            if r == self.rank or error is not None or h is None:
                 views.append(None)
                 continue
-            # the exporter's device index is not ours: open the handle on this device
-            storage = torch.UntypedStorage._new_shared_cuda(self.device.index, *h[1:])
-            views.append(torch.empty(0, dtype=dtype, device=self.device).set_(
-                storage, 0, (max(numel, 1),)))
-        dist.barrier(self.group)    # nobody frees or reuses before everyone has mapped
+            try:
+                # the exporter's device index is not ours: open the handle on this device
+                storage = torch.UntypedStorage._new_shared_cuda(self.device.index, *h[1:])
+                views.append(torch.empty(0, dtype=dtype, device=self.device).set_(
+                    storage, 0, (max(numel, 1),)))
+            except Exception as e:                  # noqa: BLE001
+                error = e
+                views.append(None)
+        # every rank learns whether every rank succeeded, so that all fall back together
+        ok = torch.tensor([0 if (error is not None or any(h is None for h in gathered)) else 1],
+                          device=self.device, dtype=torch.int32)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            raise PeerUnavailable(f"peer-mapped memory is not available on every rank "
+                                  f"(this rank: {error!r})")
         t = PeerTensor(local.view(*shape) if numel else local, views, self.rank)
         self._made.append(t)
         return t
