@@ -237,6 +237,9 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     args.warmup = max(args.warmup, 3)
+    global MOE_LAYERS
+    if args.layers > 0:
+        MOE_LAYERS = args.layers
     full_step = args.workload == "step"
     T = 32 if full_step else args.tokens
     cfg = workloads.MOE_35B
@@ -439,6 +442,9 @@ def main() -> None:
                          "TFLOP/s; moe: one 35B-A3B-class MoE layer at --tokens; step: 40-layer "
                          "MoE decode step at batch 32")
     ap.add_argument("--tokens", type=int, default=8, help="tokens per step for --workload moe")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="resident MoE layers for --workload moe/step (default 40; fewer only for "
+                         "profiler captures, where less device memory must be saved and restored)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0,
                     help="bounded CPU-baseline sample (rank 0, N=1)")
     ap.add_argument("--no-moe-leg", action="store_true",
