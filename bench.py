@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch M] [--impl b200|reference]
 
-Workload (BASELINE.json configs[1]): one layer of a 27B-class dense model at
+Workload (the reference's published dense configuration): one layer of a 27B-class dense model at
 decode batch M (default 1) -- seven trellis-coded projections, hidden 5120:
 q/k/v/o 2-bit 5120x{6144,1024,1024,5120}, gate/up 3-bit 5120x17408, down 3-bit
 17408x5120 = 117,309,440 bytes of code per layer.  A step is one pass of the
@@ -221,9 +221,9 @@ MOE_LAYERS = 40
 
 
 def run_moe(args, rank: int, world: int, local_rank: int) -> None:
-    """`--workload moe`: BASELINE.json configs[2], one 35B-A3B-class MoE decode layer
+    """`--workload moe`: the published MoE configuration, one 35B-A3B-class MoE decode layer
     (256 routed 2-bit experts, top-8, hidden 2048, expert width 512, int8 shared expert)
-    at `--tokens` tokens.  `--workload step`: configs[3], the 40-layer decode step at
+    at `--tokens` tokens.  `--workload step`: the published full-step configuration, the 40-layer decode step at
     batch 32 with the int8 attention projections in front of every MoE block.
     A step is one layer (moe) or one 40-layer pass (step); 40 layers of distinct
     weights are resident so no step finds its experts in L2.  N > 1: expert parallel,
@@ -261,13 +261,12 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
     x0 = torch.randn((T, cfg["hidden"]), device=device, generator=gen).half()
 
     def norm(h):
-        h = h.float()
-        return (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6)).half()
+        return torch.nn.functional.rms_norm(h, (h.shape[-1],), eps=1e-6)
 
     if full_step:
         def pass_(x):
             for layer in layers:
-                x = norm(x.float() + layer(x).float())
+                x = norm(x + layer(x))      # residual + RMS norm between layers (framework ops)
             return x
         steps_per_replay = 1
     else:
@@ -285,7 +284,7 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
             xs, routed = x0, 0
             for layer in layers:
                 routed += layer.routed_experts(xs)
-                xs = norm(xs.float() + layer(xs).float())
+                xs = norm(xs + layer(xs))
         else:
             routed = sum(layer.routed_experts(x0) for layer in layers)
     torch.cuda.synchronize()

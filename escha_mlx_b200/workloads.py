@@ -90,7 +90,7 @@ class MoeLayer(torch.nn.Module):
         q = self.q(x)
         self.k(x)
         self.v(x)
-        return (x.float() + self.o(q).float() * 0.01).half()   # residual keeps the scale bounded
+        return torch.add(x, self.o(q), alpha=0.01)   # residual keeps the scale bounded
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.block(self._attention_projections(x))

@@ -14,7 +14,7 @@ from escha_mlx_b200 import dense, msl, synth
 pytestmark = pytest.mark.gpu
 
 RS = msl.RS
-GEMV_TOL = 1e-3      # BASELINE bar: max rel error vs f64 product of reference-decoded weights
+GEMV_TOL = 1e-3      # the stated bar: max rel error vs f64 product of reference-decoded weights
 ORDER_TOL = 2e-5     # two f32 summation orders of the same products
 
 
@@ -279,7 +279,7 @@ def test_split_n_shards_reassemble_bit_exact(cuda, monkeypatch):
         assert torch.equal(torch.cat(parts, dim=-1), full)
 
 
-# --------------------------------------------------------------------------- BASELINE sizes
+# --------------------------------------------------------------------------- benchmark sizes
 
 @pytest.mark.parametrize("name,IC,OC,K", [("c1", 4096, 4096, 2)] + list(synth.DENSE_LAYER_27B))
 def test_full_size_projection_properties(cuda, monkeypatch, name, IC, OC, K):
