@@ -52,12 +52,18 @@ constexpr int kThreadsTc = (kDecodeWarps + 3) * 32;   // + activation loader, is
 
 __device__ int g_gemm_status = 0;
 
-// Bounded wait that sleeps between polls: a waiting warp must not take issue slots
-// from the decode warps, which are what limits this kernel.
+// Bounded wait that does not poll: a waiting warp must not take issue slots from the
+// decode warps, which are what limits this kernel.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
-    for (uint32_t it = 0; it < kMbarWaitLimit; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(it < 64 ? 32 : 256);
+    // try_wait with a suspend-time hint parks the thread in hardware until the phase
+    // completes or the hint (in nanoseconds) runs out: one instruction per microsecond of
+    // waiting instead of a polling loop
+    for (uint32_t it = 0; it < (1u << 21); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+            : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+        if (ok) return true;
     }
     return false;
 }
