@@ -286,7 +286,8 @@ INPUT_TRANSFORMED, INPUT_RAW, INPUT_SWIGLU = 0, 1, 2
 
 #: Up to this many rows the dense modules fuse the input transform into the GEMV
 #: launch (every output block's CTA redoes it for its slice of the input, which is
-#: noise at decode batch sizes and a real cost beyond them).
+#: noise at decode batch sizes and a real cost beyond them: measured on the 27B-class
+#: layer, fusing at 8 rows is 10% slower than separate transform launches, at 16 rows 20%).
 FUSE_INPUT_MAX_ROWS = 4
 
 

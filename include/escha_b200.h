@@ -11,7 +11,9 @@
  *
  * Conventions
  *  - All pointers are DEVICE pointers owned by the caller, 16-byte aligned,
- *    dense row-major.  The library allocates nothing and keeps no device state.
+ *    dense row-major.  The library allocates nothing.  Its only device state
+ *    are two status words (raised if a bounded wait inside a kernel ever gives
+ *    up) and the static scratch of escha_coded_gemv_static.
  *  - Half-precision buffers are IEEE binary16 (declared void*).
  *  - `stream` is a cudaStream_t passed as void* (NULL = default stream).  Calls
  *    only enqueue work; they never synchronise.
