@@ -670,18 +670,25 @@ int escha_coded_gemm_tc(const void* xh, const void* code, const float* rout, int
     REQUIRE(splits <= IC / 64 && splits <= 65535, "%s: splits=%d exceeds the %d 64-channel chunks",
             __func__, splits, IC / 64);
     REQUIRE((M + 255) / 256 <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
-    const bool need_planes = splits > 1 || rout != nullptr;
+    const bool fused_out = rout != nullptr && splits == 1;   // transform inside the GEMM's epilogue
+    const bool need_planes = splits > 1;
     if (need_planes) REQUIRE_PTR(planes);
     escha::GemmTcParams p{};
     p.code = static_cast<const uint32_t*>(code);
     p.xh = static_cast<const __half*>(xh);
     p.out = need_planes ? planes : static_cast<float*>(out);
+    if (fused_out) {
+        p.out = nullptr;
+        p.rout = rout;
+        p.y16 = static_cast<__half*>(out);
+        p.rs = rs;
+    }
     p.M = M; p.IC = IC; p.OC = OC; p.K = K; p.splits = splits;
     p.hash_mask = 0x8FFF8FFFu;
     p.hash_xor = 0x3B603B60u;
     p.mul2 = 2u; p.mul4 = 4u; p.mul16 = 16u; p.mul32 = 32u; p.mul64 = 64u; p.mul128 = 128u;
     cudaError_t e = escha::launch_gemm_tc(p, as_stream(stream));
-    if (e == cudaSuccess && rout != nullptr)
+    if (e == cudaSuccess && rout != nullptr && !fused_out)
         e = escha::launch_planes_out(planes, rout, static_cast<__half*>(out), M, OC, splits, rs,
                                      as_stream(stream));
     else if (e == cudaSuccess && splits > 1)

@@ -324,7 +324,9 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ C
     if (!ok && lane == 0) atomicExch(&g_gemm_status, 1);
 
     // ---- epilogue: warps 0..3 own accumulator lanes 32w .. 32w+31 (= output channels of the
-    // block); columns are activation rows.  For one row a warp stores 32 consecutive floats.
+    // block); columns are activation rows.
+    const bool fused_out = p.rout != nullptr;   // only with splits == 1 (checked by the host)
+    float* const stage = reinterpret_cast<float*>(smem_raw + (aring - smem_u32(smem_raw)));
     if (warp < 4) {
         bool ready = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0 && nchunk > 0;
         if (ready && !mbar_wait_relaxed(done, 0u)) {
@@ -340,13 +342,40 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ C
                 uint32_t v[16];
                 tmem_ld16(tmem + ((32u * warp) << 16) + col, v);
                 tmem_ld_wait();
+                if (fused_out) {
+                    // transpose through shared memory (the rings are idle now): [row][channel]
 #pragma unroll
-                for (uint32_t i = 0; i < 16u; ++i) {
-                    const uint32_t row = r0 + col + i;
-                    if (row < static_cast<uint32_t>(p.M))
-                        plane[static_cast<size_t>(row) * p.OC] = __uint_as_float(v[i]);
+                    for (uint32_t i = 0; i < 16u; ++i)
+                        stage[(col + i) * 128u + 32u * warp + lane] = __uint_as_float(v[i]);
+                } else {
+                    // for one row a warp stores 32 consecutive floats
+#pragma unroll
+                    for (uint32_t i = 0; i < 16u; ++i) {
+                        const uint32_t row = r0 + col + i;
+                        if (row < static_cast<uint32_t>(p.M))
+                            plane[static_cast<size_t>(row) * p.OC] = __uint_as_float(v[i]);
+                    }
                 }
             }
+        }
+    }
+    if (fused_out) {
+        // every warp of the CTA: one row per step, four consecutive channels per lane ->
+        // 128-point butterflies across the warp, scales, binary16 store
+        __syncthreads();
+        const uint32_t nwarps = kThreadsTc / 32u;
+        const uint32_t rows_here = min(128u * MT, static_cast<uint32_t>(p.M) - r0);
+        const float4 sc = *reinterpret_cast<const float4*>(p.rout + ocb * 128u + lane * 4u);
+        for (uint32_t r = warp; r < rows_here; r += nwarps) {
+            const float4 a = *reinterpret_cast<const float4*>(stage + r * 128u + lane * 4u);
+            float v[4] = {a.x, a.y, a.z, a.w};
+            wht128_warp(v, lane);
+            uint2 packed;
+            packed.x = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[0], p.rs), sc.x),
+                                                __fmul_rn(__fmul_rn(v[1], p.rs), sc.y)));
+            packed.y = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[2], p.rs), sc.z),
+                                                __fmul_rn(__fmul_rn(v[3], p.rs), sc.w)));
+            *reinterpret_cast<uint2*>(p.y16 + static_cast<size_t>(r0 + r) * p.OC + ocb * 128u + lane * 4u) = packed;
         }
     }
     tc_fence_before_sync();

@@ -160,6 +160,11 @@ struct GemmTcParams {
     const uint32_t* code;   // [IC/16, OC/16, 8K]
     const __half* xh;       // [M, IC] transformed activations
     float* out;             // [splits, M, OC]
+    // splits == 1 and rout given: the epilogue runs the output transform itself and writes
+    // y16 = f16((H128(mid) * rs) * rout) instead of the f32 plane
+    const float* rout;      // [OC] or nullptr
+    __half* y16;            // [M, OC]
+    float rs;
     int M, IC, OC, K, splits;
     uint32_t hash_mask, hash_xor;
     uint32_t mul2, mul4, mul16, mul32, mul64, mul128;

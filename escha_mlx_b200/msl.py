@@ -660,8 +660,7 @@ def dense_gemm_tc(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int, OC:
     s = int(lib.escha_coded_gemm_tc_splits(IC, OC, 0)) if splits is None else int(splits)
     out = torch.empty((m, OC), dtype=torch.float32 if rout is None else torch.float16,
                       device=xh.device)
-    planes = torch.empty((s, m, OC), dtype=torch.float32, device=xh.device) \
-        if (s > 1 or rout is not None) else None
+    planes = torch.empty((s, m, OC), dtype=torch.float32, device=xh.device) if s > 1 else None
     check(lib.escha_coded_gemm_tc(ptr(xh, torch.float16), ptr(code_u32),
                                   ptr(rout, torch.float32) if rout is not None else None,
                                   m, IC, OC, K, s, float(rs), ptr(planes), ptr(out), stream()))
