@@ -46,6 +46,48 @@ __device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc)
     return acc;
 }
 
+// k rounds of warp arg-max over one token's logits (NV per lane), ties to the lower expert
+// index; softmax over the k selected values; lane s writes the s-th selection.
+template <int NV>
+__device__ __forceinline__ void topk_softmax_token(const RouteParams& p, int tok, int lane) {
+    float v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = e < p.E ? __ldcg(p.logits + static_cast<size_t>(tok) * p.E + e) : -INFINITY;
+    }
+    float my_v = 0.0f, top_v = 0.0f;
+    int my_e = 0;
+    for (int s = 0; s < p.top_k; ++s) {
+        float bv = -INFINITY;
+        int be = 0x7FFFFFFF;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (v[i] > bv) { bv = v[i]; be = lane + 32 * i; }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, m);
+            const int oe = __shfl_xor_sync(0xFFFFFFFFu, be, m);
+            if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+        }
+        if (s == 0) top_v = bv;
+        if (lane == s) { my_v = bv; my_e = be; }
+        if ((be & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (i == (be >> 5)) v[i] = -INFINITY;
+        }
+    }
+    // softmax over the k selected values: exp(v - max), summed in selection order
+    const float ex = lane < p.top_k ? expf(__fsub_rn(my_v, top_v)) : 0.0f;
+    float sum = 0.0f;
+    for (int s = 0; s < p.top_k; ++s) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, ex, s));
+    if (lane < p.top_k) {
+        p.ids[static_cast<size_t>(tok) * p.top_k + lane] = my_e;
+        p.scores[static_cast<size_t>(tok) * p.top_k + lane] = __fdiv_rn(ex, sum);
+    }
+}
+
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const RouteParams p) {
     extern __shared__ int32_t s_dyn[];  // phase 3: [El + 1] job offsets, then [m] local experts
@@ -108,57 +150,23 @@ moe_route_kernel(const RouteParams p) {
     // ---- phase 2: top-k and softmax for the tile's tokens, one warp per token
     const int tok = t0 + warp;
     if (!p.ids_in && tok < p.T) {
-        const int per_lane = (p.E + 31) / 32;
-        float v[kMaxExpertsPerLane];
-#pragma unroll
-        for (int i = 0; i < kMaxExpertsPerLane; ++i) {
-            const int e = lane + 32 * i;
-            v[i] = (i < per_lane && e < p.E) ? __ldcg(p.logits + static_cast<size_t>(tok) * p.E + e)
-                                             : -INFINITY;
-        }
-        float my_v = 0.0f, top_v = 0.0f;  // lane s keeps the s-th selection
-        int my_e = 0;
-        for (int s = 0; s < p.top_k; ++s) {
-            float bv = -INFINITY;
-            int be = 0x7FFFFFFF;
-#pragma unroll
-            for (int i = 0; i < kMaxExpertsPerLane; ++i)
-                if (i < per_lane && v[i] > bv) { bv = v[i]; be = lane + 32 * i; }
-#pragma unroll
-            for (int m = 16; m > 0; m >>= 1) {
-                const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, m);
-                const int oe = __shfl_xor_sync(0xFFFFFFFFu, be, m);
-                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
-            }
-            if (s == 0) top_v = bv;
-            if (lane == s) { my_v = bv; my_e = be; }
-            if ((be & 31) == lane) {
-#pragma unroll
-                for (int i = 0; i < kMaxExpertsPerLane; ++i)
-                    if (i == (be >> 5)) v[i] = -INFINITY;
-            }
-        }
-        // softmax over the k selected values: exp(v - max), summed in selection order
-        const float ex = lane < p.top_k ? expf(__fsub_rn(my_v, top_v)) : 0.0f;
-        float sum = 0.0f;
-        for (int s = 0; s < p.top_k; ++s) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, ex, s));
-        if (lane < p.top_k) {
-            p.ids[static_cast<size_t>(tok) * p.top_k + lane] = my_e;
-            p.scores[static_cast<size_t>(tok) * p.top_k + lane] = __fdiv_rn(ex, sum);
-        }
+        if (p.E <= 256) topk_softmax_token<8>(p, tok, lane);     // the common expert counts
+        else topk_softmax_token<kMaxExpertsPerLane>(p, tok, lane);
     }
     if (!p.jobs) return;
-    __threadfence();
     __syncthreads();
-    if (tid == 0) {
-        const int prev = atomicAdd(p.counter, 1);
-        const int last = prev == n_tiles - 1;
-        if (last) *p.counter = 0;
-        s_flag = last;
+    if (n_tiles > 1) {   // with a single tile its last CTA is the launch's last CTA
+        __threadfence();
+        if (tid == 0) {
+            const int prev = atomicAdd(p.counter, 1);
+            const int last = prev == n_tiles - 1;
+            if (last) *p.counter = 0;
+            s_flag = last;
+        }
+        __syncthreads();
+        if (!s_flag) return;
+        __threadfence();
     }
-    __syncthreads();
-    if (!s_flag) return;
-    __threadfence();
 
     // ---- phase 3: rows -> jobs.  Rows are counted per expert with shared-memory
     // atomics; then thread e owns local expert e and emits its rows in ascending
@@ -177,26 +185,56 @@ moe_route_kernel(const RouteParams p) {
         if (loc >= 0) atomicAdd(&s_off[loc + 1], 1);
     }
     __syncthreads();
-    if (tid == 0) {
-        int run = 0;
-        for (int e = 0; e < El; ++e) {
-            run += (s_off[e + 1] + R - 1) / R;
-            s_off[e + 1] = run;
+    // counts -> job offsets: exclusive prefix sum of ceil(count / R) over the experts.
+    // Thread t owns a run of consecutive experts; runs are combined with a warp scan and
+    // a scan of the eight warp totals (R is 8 or 16: the division is a shift).
+    {
+        __shared__ int s_warp_total[8];
+        const int rshift = R == 8 ? 3 : 4;
+        const int per = (El + 255) / 256;                 // experts per thread (<= 4)
+        const int e_first = tid * per;
+        int local[4], sum = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int e = e_first + k;
+            local[k] = (k < per && e < El) ? (s_off[e + 1] + R - 1) >> rshift : 0;
+            sum += local[k];
+        }
+        int incl = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += up;
+        }
+        if (lane == 31) s_warp_total[warp] = incl;
+        __syncthreads();
+        int base = 0;
+        for (int w = 0; w < warp; ++w) base += s_warp_total[w];
+        int run = base + incl - sum;                      // exclusive prefix of this thread's run
+        __syncthreads();                                   // counts are read before they are overwritten
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int e = e_first + k;
+            if (k < per && e < El) {
+                run += local[k];
+                s_off[e + 1] = run;
+            }
         }
     }
     __syncthreads();
     const int total = s_off[El];
+    const int rshift = R == 8 ? 3 : 4, rmask = R - 1;
     for (int e = tid; e < El; e += blockDim.x) {
         const int base = s_off[e], njobs_e = s_off[e + 1] - base;
         if (njobs_e == 0) continue;
         int k = 0;
         for (int i = 0; i < m; ++i) {
             if (s_loc[i] != e) continue;
-            const int j = base + k / R;
+            const int j = base + (k >> rshift);
             if (j < p.njobs_cap) {
-                p.jobs[j].rows[k % R] = i;
-                if (k % R == 0) p.jobs[j].expert = e;
-                p.jobs[j].nrows = k % R + 1;  // ascending k: the last write is the count
+                p.jobs[j].rows[k & rmask] = i;
+                if ((k & rmask) == 0) p.jobs[j].expert = e;
+                p.jobs[j].nrows = (k & rmask) + 1;  // ascending k: the last write is the count
             }
             ++k;
         }
