@@ -766,7 +766,7 @@ def main() -> None:
             line["roofline"] = {
                 "bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s",
                 "frac": tf / tpeak, "traffic": None,
-                "kernel": "gemm_tc_kernel (trellis decode into shared memory + tcgen05.mma)",
+                "kernel": "gemm_tcm_kernel (trellis decode into tensor memory + tcgen05.mma)",
                 "launches_timed": launches, "avg_launch_us": ms_gemv * 1e3 / launches,
                 "algorithmic_flops_per_launch_avg": flops_step / world / 7,
                 "peak_source": f"MEASURED_PEAKS.json bf16_tflops burst ({tkind}); f16 and bf16 "

@@ -31,10 +31,11 @@
 //
 // Every wait on an mbarrier is bounded; a wait that gives up raises the status word,
 // the CTA drains, frees its tensor memory and leaves.
-#include <cuda.h>
+#include <cstdlib>
+#include <cstring>
 
-#include "common.cuh"
 #include "kernels.h"
+#include "tcgen05.cuh"
 
 namespace escha {
 
@@ -51,102 +52,6 @@ constexpr int kCodeStages = 6;                    // code-stream ring depth (chu
 constexpr int kThreadsTc = (kDecodeWarps + 3) * 32;   // + activation loader, issuing and code warps
 
 __device__ int g_gemm_status = 0;
-
-// Bounded wait that does not poll: a waiting warp must not take issue slots from the
-// decode warps, which are what limits this kernel.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
-    // try_wait with a suspend-time hint parks the thread in hardware until the phase
-    // completes or the hint (in nanoseconds) runs out: one instruction per microsecond of
-    // waiting instead of a polling loop
-    for (uint32_t it = 0; it < (1u << 21); ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
-            : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
-// ---- tcgen05 / tensor-memory primitives (one CTA per group)
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
-                 "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_fence_before_sync() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after_sync() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-// writes made through the generic proxy (st.shared, cp.async) become visible to the
-// tensor core's reads of shared memory
-__device__ __forceinline__ void fence_async_proxy() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]^T, f16 inputs, f32 accumulate
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                         uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// arrive on an mbarrier of this CTA once all tcgen05.mma issued so far have completed
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(bar) : "memory");
-}
-// 32 lanes x 16 consecutive 32-bit columns of tensor memory -> 16 registers per thread
-__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-          "=r"(v[14]), "=r"(v[15])
-        : "r"(addr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64
-// halves) with the 128-byte swizzle: 8-row groups 1024 bytes apart, descriptor
-// version 1, layout type 2.  `addr` is the shared address of the first row (1024-byte
-// aligned tile) plus 32 bytes per 16 channels already consumed.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (uint64_t(1) << 16) |
-           (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
-}
-// Instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128 (output
-// channels: the decoded weights are the A operand), N = rows of activations (128 or 256).
-__host__ __device__ constexpr uint32_t idesc_for(uint32_t n) {
-    return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-}
-
-// byte offset of (row, 16-byte chunk) inside a swizzled [rows][128 B] tile
-__device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) {
-    return row * 128u + ((chunk ^ (row & 7u)) << 4);
-}
-
-// 2-D tiled TMA load (no multicast): box at element coordinates (x, y) of the tensor the
-// map describes -> shared memory, completion counted in bytes on an mbarrier of this CTA.
-// x * element size must be a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int32_t x, int32_t y,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
-}
 
 template <int K, int MT>
 __global__ void __launch_bounds__(kThreadsTc, 1)
@@ -383,6 +288,8 @@ gemm_tc_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ C
     if (warp == 0) tmem_dealloc(tmem, 128u * MT);
 }
 
+}  // namespace
+
 // cuTensorMapEncodeTiled, resolved through the runtime (the library does not link libcuda).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -410,6 +317,8 @@ cudaError_t encode_x_map(CUtensorMap* map, const __half* xh, int M, int IC, int 
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+namespace {
+
 template <int K, int MT>
 cudaError_t launch_tc(const GemmTcParams& p, cudaStream_t st) {
     const size_t smem = static_cast<size_t>(kAStages) * MT * kABytesPerMt +
@@ -436,6 +345,12 @@ cudaError_t launch_tc(const GemmTcParams& p, cudaStream_t st) {
 }  // namespace
 
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
+    // ESCHA_B200_TC_WEIGHTS=tmem (default) | smem: which operand path the decoded weights take
+    static const bool through_tmem = [] {
+        const char* e = std::getenv("ESCHA_B200_TC_WEIGHTS");
+        return e == nullptr || std::strcmp(e, "smem") != 0;
+    }();
+    if (through_tmem && gemm_tcm_supports(p)) return launch_gemm_tcm(p, st);
     const bool two = p.M > 128;
     if (p.K == 2) return two ? launch_tc<2, 2>(p, st) : launch_tc<2, 1>(p, st);
     return two ? launch_tc<3, 2>(p, st) : launch_tc<3, 1>(p, st);
@@ -505,7 +420,11 @@ cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int spl
 }
 
 cudaError_t gemm_tc_status(int* host_status) {
-    return cudaMemcpyFromSymbol(host_status, g_gemm_status, sizeof(int));
+    int a = 0, b = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&a, g_gemm_status, sizeof(int));
+    if (e == cudaSuccess) e = gemm_tcm_status(&b);
+    *host_status = a != 0 ? a : b;
+    return e;
 }
 
 }  // namespace escha

@@ -174,6 +174,10 @@ cudaError_t launch_planes_out(const float* planes, const float* rout, __half* y,
                               int splits, float rs, cudaStream_t st);
 cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int splits, cudaStream_t st);
 cudaError_t gemm_tc_status(int* host_status);
+// the same product with the decoded weights handed over through tensor memory (gemm_tcm.cu)
+bool gemm_tcm_supports(const GemmTcParams& p);
+cudaError_t launch_gemm_tcm(const GemmTcParams& p, cudaStream_t st);
+cudaError_t gemm_tcm_status(int* host_status);
 
 // Cross-GPU barrier over peer-mapped flag words (peer.cu).
 struct PeerBarrierParams {

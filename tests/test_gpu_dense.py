@@ -363,3 +363,26 @@ def test_swiglu_project_equals_unfused_chain(cuda, oracle, monkeypatch, M):
     ri, ro = oracle.fold_scales(rin, rout)
     h = oracle.swiglu(np.concatenate([host(g), host(u)], axis=-1))
     assert rel_err(host(y), oracle.dense_linear(h, code, ri, ro, K)) < 2e-3
+
+
+@pytest.mark.parametrize("L", [4, 8])
+def test_tree_verify_shapes(cuda, oracle, monkeypatch, L):
+    """The path's other consumer: speculative-decoding tree verification calls the coded
+    projections on [B, L, H] inputs with L = 4 or 8 draft nodes (escha_mlx/mtp.py:539-541 K/V
+    pair, escha_mlx/gdn_cache.py:658-665 qkv/z pair).  Same kernels, small-row shapes."""
+    set_env(monkeypatch, ESCHA_MLX_GEMV="mma", ESCHA_MLX_FUSED_HAD=1)
+    rng = np.random.default_rng(40 + L)
+    IC, K = 512, 2
+    lins, raw = [], []
+    for OC in (256, 128):
+        code, rin, rout = synth.coded_projection(rng, IC, OC, K)
+        raw.append((code, rin, rout))
+        lins.append(dense.EschaLinear(dense.EschaWeight(code, rin, rout, device=cuda)))
+    x = synth.activations(rng, L, IC).reshape(1, L, IC)
+    ya, yb = dense.project_pair(lins[0], lins[1], dev(x, cuda))
+    assert ya.shape == (1, L, 256) and yb.shape == (1, L, 128)
+    for y, lin, (code, rin, rout) in zip((ya, yb), lins, raw):
+        assert torch.equal(y, lin(dev(x, cuda)))
+        ri, ro = oracle.fold_scales(rin, rout)
+        want = oracle.dense_linear(x.reshape(L, IC), code, ri, ro, K)
+        assert rel_err(host(y).reshape(L, -1), want) < 2e-3

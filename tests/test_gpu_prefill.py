@@ -1,9 +1,14 @@
-"""GPU parity of the prefill coded GEMM (decode into shared memory, tcgen05.mma with
-fp32 accumulators in tensor memory) against the CPU oracle's float64 product of
+"""GPU parity of the prefill coded GEMM (channel-major decode into tensor memory, or into
+shared memory with ESCHA_B200_TC_WEIGHTS=smem; tcgen05.mma with fp32 accumulators in
+tensor memory) against the CPU oracle's float64 product of
 reference-decoded weights, against the register-fragment tensor-core kernel, and
 through the dense module.  Mirrors the reference's tests/test_gemm_mat.py bar:
 tolerance-equal to the per-row kernel, deterministic run to run."""
 from __future__ import annotations
+
+import os
+import subprocess
+import sys
 
 import numpy as np
 import pytest
@@ -34,6 +39,8 @@ def host(t):
     (2, 1024, 384, 256, None),  # policy split
     (3, 768, 128, 300, 3),      # more than 256 rows: second pass over the weights
     (2, 4096, 256, 64, 4),
+    (3, 256, 128, 20, 3),       # more splits than 128-channel stages: shared-memory-operand kernel
+    (3, 1280, 256, 256, 1),     # ten stages: every ring wraps
 ])
 def test_prefill_gemm_vs_oracle(cuda, oracle, K, IC, OC, M, splits):
     rng = np.random.default_rng(K * 1000 + IC + M)
@@ -90,3 +97,38 @@ def test_prefill_fused_output_equals_separate_transform(cuda, splits):
     fused = msl.dense_gemm_tc(xd, c, K, IC, OC, splits=splits, rout=ro)
     separate = msl.dense_scaled_had_out(msl.dense_gemm_tc(xd, c, K, IC, OC, splits=splits), ro, msl.RS)
     assert torch.equal(fused, separate)
+
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+SMEM_CHILD = r"""
+import sys
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+import numpy as np, torch
+from escha_mlx_b200 import msl, synth
+from escha_mlx_b200._lib import lib
+from oracle import escha_oracle as oracle
+dev = torch.device("cuda", 0)
+worst = 0.0
+for K, IC, OC, M, S in ((2, 1024, 256, 200, 1), (3, 768, 128, 300, 3)):
+    rng = np.random.default_rng(K + M)
+    code, rin, rout = synth.coded_projection(rng, IC, OC, K)
+    xh = (rng.standard_normal((M, IC)) * 0.25).astype(np.float16)
+    mid = msl.dense_gemm_tc(torch.from_numpy(xh).to(dev), msl.code_tensor(code, dev), K, IC, OC, splits=S)
+    torch.cuda.synchronize()
+    assert lib.escha_coded_gemm_tc_status() == 0
+    want = oracle.gemv_f64(xh, code, None, K, IC, OC)
+    worst = max(worst, float(np.abs(mid.cpu().numpy() - want).max() / np.abs(want).max()))
+print("WORST", worst)
+"""
+
+
+@pytest.mark.timeout(300)
+def test_shared_memory_operand_kernel_still_matches(cuda):
+    """The earlier kernel (weights as a shared-memory operand) stays selectable and correct;
+    the switch is read once per process, hence the child process."""
+    env = dict(os.environ, ESCHA_B200_TC_WEIGHTS="smem")
+    run = subprocess.run([sys.executable, "-c", SMEM_CHILD, ROOT], env=env, capture_output=True,
+                         text=True, timeout=240)
+    assert run.returncode == 0, run.stderr[-2000:]
+    assert float(run.stdout.split("WORST")[1]) < GEMV_TOL
