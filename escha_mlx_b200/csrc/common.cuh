@@ -12,6 +12,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <utility>
 
 namespace escha {
@@ -286,6 +288,29 @@ inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+// The same, unless ESCHA_B200_PDL=off (read once per process): then a plain launch, and the
+// kernel's grid_dependency_wait() is a no-op.  For the small kernels between the products
+// (transforms, SwiGLU, plane sums): they call launch_dependents and wait first thing, so only
+// launch latency and set-up overlap the previous kernel's tail.
+inline bool pdl_allowed() {
+    static const bool on = [] {
+        const char* v = std::getenv("ESCHA_B200_PDL");
+        return v == nullptr || std::strcmp(v, "off") != 0;
+    }();
+    return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t st, Args&&... args) {
+    if (pdl_allowed()) return launch_dependent(kernel, grid, block, smem, st, std::forward<Args>(args)...);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 

@@ -378,6 +378,8 @@ namespace {
 __global__ void __launch_bounds__(256)
 planes_out_kernel(const float* __restrict__ planes, const float* __restrict__ rout,
                   __half* __restrict__ y, int M, int OC, int splits, float rs) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint32_t per_row = static_cast<uint32_t>(OC) >> 7;
@@ -407,9 +409,8 @@ planes_out_kernel(const float* __restrict__ planes, const float* __restrict__ ro
 cudaError_t launch_planes_out(const float* planes, const float* rout, __half* y, int M, int OC,
                               int splits, float rs, cudaStream_t st) {
     const long units = static_cast<long>(M) * (OC / 128);
-    planes_out_kernel<<<static_cast<unsigned>((units + 7) / 8), 256, 0, st>>>(planes, rout, y, M, OC,
-                                                                            splits, rs);
-    return cudaGetLastError();
+    return launch_chained(planes_out_kernel, dim3(static_cast<unsigned>((units + 7) / 8)), dim3(256), 0,
+                          st, planes, rout, y, M, OC, splits, rs);
 }
 
 cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int splits, cudaStream_t st) {

@@ -164,6 +164,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
     const uint32_t s_first = split * sbase + min(split, srem);
     const uint32_t nstage = sbase + (split < srem ? 1u : 0u);
 
+    grid_launch_dependents();
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < kWStages; ++s) {
@@ -191,6 +192,8 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = s_tmem;
+    // the set-up above overlapped the previous kernel's tail; its results are needed from here
+    grid_dependency_wait();
 
     bool ok = true;
     if (warp >= kServiceWarps) {
@@ -394,8 +397,7 @@ cudaError_t launch_tcm(const GemmTcParams& p, cudaStream_t st) {
     e = encode_x_map(&xmap, p.xh, p.M, p.IC, 128 * MT);
     if (e != cudaSuccess) return e;
     const dim3 grid(p.OC / 128, p.splits, (p.M + 128 * MT - 1) / (128 * MT));
-    gemm_tcm_kernel<K, MT><<<grid, kThreadsTcm, smem, st>>>(p, xmap);
-    return cudaGetLastError();
+    return launch_chained(gemm_tcm_kernel<K, MT>, grid, dim3(kThreadsTcm), smem, st, p, xmap);
 }
 
 }  // namespace

@@ -26,6 +26,8 @@ template <bool OUTPUT>
 __global__ void __launch_bounds__(256)
 scaled_had_kernel(HadShard s0, HadShard s1, const int32_t* __restrict__ row_expert, int M,
                   float rs) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint32_t nb0 = s0.dim >> 7, nb1 = s1.dim >> 7;
@@ -94,9 +96,8 @@ cudaError_t launch_scaled_had(bool output, const void* src0, const float* vec0, 
     const long units = static_cast<long>(M) * ((dim0 + dim1) / 128);
     const int warps = 8;
     dim3 grid(static_cast<unsigned>((units + warps - 1) / warps)), block(warps * 32);
-    if (output) scaled_had_kernel<true><<<grid, block, 0, st>>>(s0, s1, row_expert, M, rs);
-    else scaled_had_kernel<false><<<grid, block, 0, st>>>(s0, s1, row_expert, M, rs);
-    return cudaGetLastError();
+    if (output) return launch_chained(scaled_had_kernel<true>, grid, block, 0, st, s0, s1, row_expert, M, rs);
+    return launch_chained(scaled_had_kernel<false>, grid, block, 0, st, s0, s1, row_expert, M, rs);
 }
 
 }  // namespace escha

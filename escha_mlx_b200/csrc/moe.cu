@@ -82,6 +82,8 @@ __global__ void jobs_from_groups_kernel(const int32_t* __restrict__ rows_idx,
 // ---------------------------------------------------------------------------
 __global__ void swiglu_kernel(const __half* __restrict__ gate, const __half* __restrict__ up,
                               int M, int I, long stride, __half* __restrict__ h) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= static_cast<long>(M) * I) return;
     const long r = idx / I, i = idx - r * I;
@@ -131,8 +133,8 @@ cudaError_t launch_jobs_from_groups(const int32_t* rows_idx, const int32_t* grou
 cudaError_t launch_swiglu(const __half* gate, const __half* up, int M, int I, long stride,
                           __half* h, cudaStream_t st) {
     const long n = static_cast<long>(M) * I;
-    swiglu_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(gate, up, M, I, stride, h);
-    return cudaGetLastError();
+    return launch_chained(swiglu_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, st,
+                          gate, up, M, I, stride, h);
 }
 
 cudaError_t launch_moe_combine(const __half* d16, const float* scores, int T, int top_k, int H,
