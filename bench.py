@@ -533,11 +533,13 @@ def main() -> None:
         """One fused launch of the named projections' shards into their gathered buffers."""
         ws = [layer[n]._w for n in names]
         fuse_in = M <= msl.FUSE_INPUT_MAX_ROWS
-        if x_up is not None and not fuse_in:
-            x, x_up = msl.swiglu_pair(x.contiguous(), x_up.contiguous()), None
         mode = (msl.INPUT_SWIGLU if x_up is not None else msl.INPUT_RAW) if fuse_in \
             else msl.INPUT_TRANSFORMED
-        xs = None if fuse_in else [msl.dense_scaled_had(x, w.rin, msl.RS) for w in ws]
+        xs = None
+        if not fuse_in:   # one launch: SwiGLU (if any) and every projection's input transform
+            xs = msl.dense_scaled_had_many(x.contiguous(), [w.rin for w in ws], msl.RS,
+                                           up=None if x_up is None else x_up.contiguous())
+            x_up = None
         outs = msl.coded_projections(
             x if fuse_in else xs[0], [w.code for w in ws], [w.rin for w in ws] if fuse_in else None,
             [w.rout for w in ws], ws[0].K, ws[0].IC, [w.OC for w in ws], input_mode=mode,
@@ -571,9 +573,16 @@ def main() -> None:
     # gate/up, swiglu+down (4); larger batches add the separate input transforms
     if M <= msl.FUSE_INPUT_MAX_ROWS:
         launches_per_step = 4 if world == 1 else 8      # 4 fused GEMV + 4 peer barriers
+    elif msl.use_prefill_kernel(M) and world == 1:
+        # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), seven tcgen05 GEMMs,
+        # and a plane sum + output transform for every projection the policy splits along K
+        from escha_mlx_b200._lib import lib as _lib
+        n_split = sum(1 for _, ic, oc, _k in LAYER
+                      if _lib.escha_coded_gemm_tc_splits(ic, oc, 0) > 1)
+        launches_per_step = 4 + 7 + n_split
     else:
-        # q/k/v 3+1, o 1+1, gate/up 1+1 (pair transform), swiglu 1, down 1+1 (+ 4 barriers)
-        launches_per_step = 11 if world == 1 else 15
+        # q/k/v 1+1, o 1+1, gate/up 1+1, SwiGLU + down 1+1 (+ 4 barriers)
+        launches_per_step = 8 if world == 1 else 12
 
     x0 = torch.randn((M, HIDDEN), device=device, generator=gen).half()
 

@@ -185,6 +185,28 @@ int escha_scaled_had_pair(const void* rows, const float* rin0, const float* rin1
         "escha_scaled_had_pair");
 }
 
+int escha_scaled_had_many(const void* rows, const void* up, int n, const float* const* rins,
+                          void* const* outs, int M, int IC, float rs, void* stream) {
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE(IC > 0 && IC % 128 == 0, "%s: Hadamard dimension must be divisible by 128, got %d",
+            __func__, IC);
+    REQUIRE(n >= 1 && n <= 4, "%s: one to four transforms per launch, got %d", __func__, n);
+    REQUIRE_PTR(rows);
+    OPTIONAL_PTR(up);
+    REQUIRE_PTR(rins);
+    REQUIRE_PTR(outs);
+    __half* o[4] = {nullptr, nullptr, nullptr, nullptr};
+    for (int i = 0; i < n; ++i) {
+        REQUIRE(rins[i] != nullptr && outs[i] != nullptr, "%s: transform %d has a null pointer",
+                __func__, i);
+        o[i] = static_cast<__half*>(outs[i]);
+    }
+    return cuda_result(
+        escha::launch_scaled_had_many(static_cast<const __half*>(rows), static_cast<const __half*>(up),
+                                      n, rins, o, M, IC, rs, as_stream(stream)),
+        "escha_scaled_had_many");
+}
+
 int escha_scaled_had_out_pair(const float* mid0, const float* mid1, const float* rout0,
                               const float* rout1, int M, int OC0, int OC1, float rs, void* out0,
                               void* out1, void* stream) {

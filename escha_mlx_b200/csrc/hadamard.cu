@@ -68,6 +68,74 @@ scaled_had_kernel(HadShard s0, HadShard s1, const int32_t* __restrict__ row_expe
     *reinterpret_cast<uint2*>(s.out + off) = packed;
 }
 
+// Up to four input transforms of the SAME rows, each with its own scale vector (Q/K/V, gate/up),
+// in one launch: the rows are read once.  With `up` given the rows are the gate half of a
+// SwiGLU MLP and the input is h = f16( f16(silu(gate)) * up ) (ref.py:296-301), formed here
+// instead of by a kernel of its own and a round trip through memory -- the fusion of
+// _FusedMLP (escha_mlx/models/qwen3_5.py:63-198).  Bit-identical to the separate launches.
+struct HadMany {
+    const __half* rows;
+    const __half* up;        // nullptr: plain rows
+    const float* rin[4];
+    __half* out[4];
+    int n, dim;
+};
+
+__global__ void __launch_bounds__(256)
+scaled_had_many_kernel(HadMany s, int M, float rs) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t per_row = s.dim >> 7;
+    const uint32_t row = unit / per_row;
+    if (row >= static_cast<uint32_t>(M)) return;
+    const uint32_t blk = unit - row * per_row;
+    const size_t off = static_cast<size_t>(row) * s.dim + blk * 128u + lane * 4u;
+    const uint2 raw = *reinterpret_cast<const uint2*>(s.rows + off);
+    __half2 lo = as_half2(raw.x), hi = as_half2(raw.y);
+    if (s.up) {
+        const uint2 ur = *reinterpret_cast<const uint2*>(s.up + off);
+        const float2 g0 = __half22float2(lo), g1 = __half22float2(hi);
+        const __half2 u0 = as_half2(ur.x), u1 = as_half2(ur.y);
+        auto act = [](float g, __half u) {
+            const __half sg = __float2half_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))));
+            return __hmul(sg, u);
+        };
+        lo = __halves2half2(act(g0.x, __low2half(u0)), act(g0.y, __high2half(u0)));
+        hi = __halves2half2(act(g1.x, __low2half(u1)), act(g1.y, __high2half(u1)));
+    }
+    const float2 a = __half22float2(lo), b = __half22float2(hi);
+#pragma unroll 1
+    for (int i = 0; i < s.n; ++i) {
+        const float4 sc = *reinterpret_cast<const float4*>(s.rin[i] + blk * 128u + lane * 4u);
+        float v[4] = {__fmul_rn(a.x, sc.x), __fmul_rn(a.y, sc.y), __fmul_rn(b.x, sc.z),
+                      __fmul_rn(b.y, sc.w)};
+        wht128_warp(v, lane);
+        uint2 packed;
+        packed.x = as_u32(__floats2half2_rn(__fmul_rn(v[0], rs), __fmul_rn(v[1], rs)));
+        packed.y = as_u32(__floats2half2_rn(__fmul_rn(v[2], rs), __fmul_rn(v[3], rs)));
+        *reinterpret_cast<uint2*>(s.out[i] + off) = packed;
+    }
+}
+
+cudaError_t launch_scaled_had_many(const __half* rows, const __half* up, int n,
+                                   const float* const* rins, __half* const* outs, int M, int dim,
+                                   float rs, cudaStream_t st) {
+    HadMany s{};
+    s.rows = rows;
+    s.up = up;
+    s.n = n;
+    s.dim = dim;
+    for (int i = 0; i < n; ++i) {
+        s.rin[i] = rins[i];
+        s.out[i] = outs[i];
+    }
+    const long units = static_cast<long>(M) * (dim / 128);
+    return launch_chained(scaled_had_many_kernel, dim3(static_cast<unsigned>((units + 7) / 8)),
+                          dim3(256), 0, st, s, M, rs);
+}
+
 // Plain unnormalised H128 on f32 blocks (the reference's moe.had_blocks, which
 // calls mx.hadamard_transform(scale=1.0): escha_mlx/moe.py:19-27).
 __global__ void __launch_bounds__(256)

@@ -122,6 +122,9 @@ struct Q8Params {
 cudaError_t launch_lut_init(__half* lut, cudaStream_t st);
 cudaError_t launch_decode_tiles(const uint32_t* code, int K, int IC, int OC, const __half* lut,
                                 __half* w, cudaStream_t st);
+cudaError_t launch_scaled_had_many(const __half* rows, const __half* up, int n,
+                                   const float* const* rins, __half* const* outs, int M, int dim,
+                                   float rs, cudaStream_t st);
 cudaError_t launch_scaled_had(bool output, const void* src0, const float* vec0, __half* out0,
                               int dim0, const void* src1, const float* vec1, __half* out1,
                               int dim1, const int32_t* row_expert, int M, float rs,

@@ -208,18 +208,19 @@ class EschaLinear(torch.nn.Module):
             y = msl.coded_projections(rows, [w.code], [w.rin], [w.rout], w.K, w.IC, [w.OC],
                                       input_mode=msl.INPUT_RAW, rs=RS)[0]
             return self._finish(y, shape, x.dtype)
-        xh = self._input_rows(rows)
-        if msl.use_prefill_kernel(rows.shape[0]):
-            # prefill: decode once per 256 rows into shared memory, contract on tcgen05
-            w = self._w
-            y = msl.dense_gemm_tc(xh, w.code, w.K, w.IC, w.OC, rout=w.rout, rs=RS)
-        elif self._fused_had:
-            y = msl.dense_gemm_rows_direct_out(
-                xh, self._w.code, self._w.rout, self.K, self._w.IC, self._w.OC,
-                msl.dense_block_r(rows.shape[0], self._block_r_pin), RS)
-        else:
-            y = self._output_rows(self._gemv(xh))
-        return self._finish(y, shape, x.dtype)
+        return self._finish(self._product_rows(self._input_rows(rows)), shape, x.dtype)
+
+    def _product_rows(self, xh: torch.Tensor) -> torch.Tensor:
+        """Transformed rows -> f16 output rows: product and output transform."""
+        w = self._w
+        if msl.use_prefill_kernel(xh.shape[0]):
+            # prefill: decode once per 256 rows into tensor memory, contract on tcgen05
+            return msl.dense_gemm_tc(xh, w.code, w.K, w.IC, w.OC, rout=w.rout, rs=RS)
+        if self._fused_had:
+            return msl.dense_gemm_rows_direct_out(
+                xh, w.code, w.rout, self.K, w.IC, w.OC,
+                msl.dense_block_r(xh.shape[0], self._block_r_pin), RS)
+        return self._output_rows(self._gemv(xh))
 
     def _single_launch(self, m: int) -> bool:
         """Whether a forward over m rows runs as one fused kernel (small decode
@@ -250,6 +251,12 @@ def project_many(linears, x: torch.Tensor):
         and all(lin._w.IC == rows.shape[-1] and lin.K == first.K for lin in linears)
         and rows.dtype == torch.float16
     )
+    same_input = (1 < len(linears) <= 4 and rows.dtype == torch.float16
+                  and all(lin._w.IC == rows.shape[-1] for lin in linears))
+    if same_input and msl.use_prefill_kernel(rows.shape[0]):
+        # prefill: one launch for all input transforms, then one tcgen05 GEMM per projection
+        xhs = msl.dense_scaled_had_many(rows.contiguous(), [lin._w.rin for lin in linears], RS)
+        return [lin._finish(lin._product_rows(xh), shape, x.dtype) for lin, xh in zip(linears, xhs)]
     if not joint or msl.use_prefill_kernel(rows.shape[0]):
         return [lin(x) for lin in linears]
     rows = rows.contiguous()
@@ -259,8 +266,7 @@ def project_many(linears, x: torch.Tensor):
         outs = msl.coded_projections(rows, codes, [w.rin for w in ws], routs, first.K, first._w.IC,
                                      ocs, input_mode=msl.INPUT_RAW, rs=RS)
     else:
-        xhs = [lin._input_rows(rows) for lin in linears] if len(linears) != 2 else list(
-            msl.dense_scaled_had_pair(rows, ws[0].rin, ws[1].rin, RS))
+        xhs = msl.dense_scaled_had_many(rows, [w.rin for w in ws], RS)
         outs = msl.coded_projections(xhs[0], codes, None, routs, first.K, first._w.IC, ocs,
                                      rs=RS, xs=xhs)
     return [lin._finish(y, shape, x.dtype) for lin, y in zip(linears, outs)]
@@ -290,8 +296,9 @@ def swiglu_project(down: EschaLinear, gate: torch.Tensor, up: torch.Tensor) -> t
         y = msl.coded_projections(g, [w.code], [w.rin], [w.rout], w.K, w.IC, [w.OC],
                                   input_mode=msl.INPUT_SWIGLU, x_up=u, rs=RS)[0]
         return down._finish(y, shape, gate.dtype)
-    h = msl.swiglu_pair(g.to(torch.float16), u.to(torch.float16))
-    return down(h.reshape(*shape[:-1], down._w.IC).to(gate.dtype))
+    # SwiGLU inside the input transform: one launch, no activation round trip
+    xh = msl.dense_scaled_had_many(g.to(torch.float16), [down._w.rin], RS, up=u.to(torch.float16))[0]
+    return down._finish(down._product_rows(xh), shape, gate.dtype)
 
 
 def build(group: dict, device=None) -> EschaLinear:

@@ -204,6 +204,29 @@ def dense_scaled_had_pair(rows: torch.Tensor, rin0: torch.Tensor, rin1: torch.Te
     return out0, out1
 
 
+def dense_scaled_had_many(rows: torch.Tensor, rins, rs: float, up: torch.Tensor | None = None):
+    """One to four dense input transforms of the same rows in one launch (the pair dispatch of
+    :1491-1504 widened to Q/K/V); with ``up`` the rows are a SwiGLU gate and the input is
+    ``f16(f16(silu(rows)) * up)`` (the SwiGLU-into-down-input fusion of
+    models/qwen3_5.py:63-198).  Bit-identical to the separate launches."""
+    m, ic = rows.shape
+    rins = list(rins)
+    if not 1 <= len(rins) <= 4:
+        raise ValueError(f"one to four transforms per launch, got {len(rins)}")
+    if up is not None and up.shape != rows.shape:
+        raise ValueError("SwiGLU input needs gate and up of equal shape")
+    outs = [torch.empty((m, ic), dtype=torch.float16, device=rows.device) for _ in rins]
+    rin_ptrs = (ctypes.c_void_p * len(rins))(*[r.data_ptr() for r in rins])
+    out_ptrs = (ctypes.c_void_p * len(rins))(*[o.data_ptr() for o in outs])
+    for r in rins:
+        if r.dtype != torch.float32 or r.numel() != ic or not r.is_contiguous():
+            raise ValueError("scale vectors must be contiguous f32 [IC]")
+    check(lib.escha_scaled_had_many(ptr(rows, torch.float16),
+                                    ptr(up, torch.float16) if up is not None else None,
+                                    len(rins), rin_ptrs, out_ptrs, m, ic, float(rs), stream()))
+    return outs
+
+
 def dense_scaled_had_out_pair(mid0: torch.Tensor, mid1: torch.Tensor, rout0: torch.Tensor,
                               rout1: torch.Tensor, rs: float):
     """Two dense output transforms in one launch (:1507-1527)."""

@@ -74,6 +74,15 @@ int escha_scaled_had_out(const float *mid, const float *rout, const int32_t *row
 int escha_scaled_had_pair(const void *rows, const float *rin0, const float *rin1, int M, int IC,
                           float rs, void *out0, void *out1, void *stream);
 
+/* One to four dense input transforms of the same rows in one launch, each with its own
+ * scale vector: rins[i] f32 [IC] -> outs[i] f16 [M, IC].  With `up` non-null the rows are the
+ * gate half of a SwiGLU MLP and the transformed input is f16(f16(silu(rows)) * up)
+ * (ref.py:296-301), i.e. SwiGLU fused into the down projection's input transform as in
+ * _FusedMLP (models/qwen3_5.py:63-198); msl.dense_scaled_had_pair (msl.py:1491-1504) is the
+ * n = 2 case.  rins / outs are HOST arrays of n device pointers. */
+int escha_scaled_had_many(const void *rows, const void *up, int n, const float *const *rins,
+                          void *const *outs, int M, int IC, float rs, void *stream);
+
 /* Two dense output transforms in one launch (equal row counts).
  * Replaces msl.dense_scaled_had_out_pair (msl.py:1507-1527). */
 int escha_scaled_had_out_pair(const float *mid0, const float *mid1, const float *rout0,

@@ -386,3 +386,20 @@ def test_tree_verify_shapes(cuda, oracle, monkeypatch, L):
         ri, ro = oracle.fold_scales(rin, rout)
         want = oracle.dense_linear(x.reshape(L, IC), code, ri, ro, K)
         assert rel_err(host(y).reshape(L, -1), want) < 2e-3
+
+
+@pytest.mark.parametrize("n,with_up", [(1, False), (3, False), (4, False), (1, True), (2, True)])
+def test_scaled_had_many_equals_separate_launches(cuda, n, with_up):
+    """One launch for several input transforms of the same rows (and SwiGLU formed inside it)
+    is bit-identical to the separate kernels."""
+    rng = np.random.default_rng(90 + n)
+    M, IC = 37, 640
+    x = dev(synth.activations(rng, M, IC), cuda)
+    up = dev(synth.activations(rng, M, IC), cuda) if with_up else None
+    rins = [dev((rng.standard_normal(IC) * 0.02).astype(np.float32), cuda) for _ in range(n)]
+    got = msl.dense_scaled_had_many(x, rins, msl.RS, up=up)
+    src = msl.swiglu_pair(x, up) if with_up else x
+    for g, rin in zip(got, rins):
+        assert torch.equal(g, msl.dense_scaled_had(src, rin, msl.RS))
+    with pytest.raises(ValueError):
+        msl.dense_scaled_had_many(x, [], msl.RS)
