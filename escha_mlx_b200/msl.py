@@ -22,6 +22,7 @@ Reference citations are to ``escha_mlx/msl.py`` unless stated otherwise.
 from __future__ import annotations
 
 import ctypes
+import os
 from functools import lru_cache
 
 import numpy as np
@@ -483,10 +484,11 @@ def dense_gemm_rows_direct(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC:
     return dense_gemv(xh, code_u32, K, IC, OC)
 
 
-#: From this many rows on the dense modules run the product on tcgen05 (decode once
-#: per 256 rows into shared memory) instead of the register-fragment kernel, which
-#: decodes once per 16 rows.  Measured crossover on the 27B-class shapes: ~40 rows.
-PREFILL_MIN_ROWS = 48
+#: From this many rows on the dense modules run the product on tcgen05 (decode once per 256
+#: rows into tensor memory) instead of the register-fragment kernel, which decodes once per 16
+#: rows.  Measured on the 27B-class layer: equal at 16 rows (185 us per layer step), and at 24 /
+#: 32 / 40 / 48 rows 187 / 189 / 190 / 193 us against 306 / 323 / 437 / 457 us.
+PREFILL_MIN_ROWS = int(os.environ.get("ESCHA_B200_PREFILL_MIN_ROWS", "17"))
 
 
 def use_prefill_kernel(m: int) -> bool:
