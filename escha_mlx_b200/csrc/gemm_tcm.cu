@@ -21,7 +21,7 @@
 //   warp 0           issues tcgen05.mma (A from tensor memory, B = activations from shared
 //                    memory, fp32 accumulators in tensor memory: 128 channels x 128 or 256 rows
 //                    x 16 per instruction).  Its loop is warp-uniform with one elected lane
-//                    issuing; tcgen05.commit hands ring slots back.  Measured: a commit returns
+//                    issuing; one tcgen05.commit per stage hands its ring slots back.  Measured: a commit returns
 //                    only when the instructions before it have run, so this warp is paced by
 //                    the tensor core (about 128 cycles per instruction) and must not also wait
 //                    for issue slots behind the decode warps -- hence the CTA's first warp.
@@ -53,6 +53,7 @@ constexpr uint32_t kWStageCols = kStageK / 2;     // two binary16 per 32-bit col
 constexpr uint32_t kWCol0 = 256;                  // weight stages follow the accumulators
 constexpr uint32_t kTmemCols = 512;
 constexpr int kXStages = 3;                       // activation ring slots (128 channels each)
+constexpr int kFreeBars = 12;                     // a common multiple of the two ring depths
 constexpr int kXChunkK = 64;
 constexpr int kXBytesPerMt = 128 * kXChunkK * 2;  // 16 KiB of activations per 128 rows
 constexpr int kDecodeWarps = 16;
@@ -146,8 +147,12 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
     constexpr uint32_t kRowBytes = 8u * WPT * 4u;          // one tile row of the CTA's 8 tile columns
     constexpr uint32_t kCodeStageBytes = 8u * kRowBytes;   // eight tile rows = 128 input channels
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_wfull[kWStages], s_wempty[kWStages];
-    __shared__ __align__(8) uint64_t s_xfull[kXStages], s_xempty[kXStages];
+    // s_free[c % kFreeBars] completes when the tensor core is done with stage c: ONE commit per
+    // stage releases both the stage's weight columns and its activation slot (a tcgen05.commit
+    // holds the issuing thread until the instructions before it have run, so every commit saved
+    // is time on the critical path).  The ring depths differ, hence a barrier per stage modulo
+    // their common multiple.
+    __shared__ __align__(8) uint64_t s_wfull[kWStages], s_xfull[kXStages], s_free[kFreeBars];
     __shared__ __align__(8) uint64_t s_cfull[kCodeStages], s_cempty[kCodeStages], s_done;
     __shared__ uint32_t s_tmem;
 
@@ -155,8 +160,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
     const uint32_t ocb = blockIdx.x, split = blockIdx.y, r0 = blockIdx.z * (128u * MT);
     const uint32_t xring = (smem_u32(smem_raw) + 1023u) & ~1023u;   // [kXStages][2][rows][128 B]
     const uint32_t code0 = xring + kXStages * kXBytes;              // [kCodeStages][8][kRowBytes]
-    const uint32_t wfull0 = smem_u32(s_wfull), wempty0 = smem_u32(s_wempty);
-    const uint32_t xfull0 = smem_u32(s_xfull), xempty0 = smem_u32(s_xempty);
+    const uint32_t wfull0 = smem_u32(s_wfull), xfull0 = smem_u32(s_xfull), free0 = smem_u32(s_free);
     const uint32_t cfull0 = smem_u32(s_cfull), cempty0 = smem_u32(s_cempty), done = smem_u32(&s_done);
 
     const uint32_t nstage_all = static_cast<uint32_t>(p.IC) / kStageK;
@@ -167,15 +171,11 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
     grid_launch_dependents();
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < kWStages; ++s) {
-            mbar_init(wfull0 + 8u * s, kDecodeWarps);
-            mbar_init(wempty0 + 8u * s, 1u);
-        }
+        for (int s = 0; s < kWStages; ++s) mbar_init(wfull0 + 8u * s, kDecodeWarps);
 #pragma unroll
-        for (int s = 0; s < kXStages; ++s) {
-            mbar_init(xfull0 + 8u * s, 1u);
-            mbar_init(xempty0 + 8u * s, 1u);
-        }
+        for (int s = 0; s < kXStages; ++s) mbar_init(xfull0 + 8u * s, 1u);
+#pragma unroll
+        for (int s = 0; s < kFreeBars; ++s) mbar_init(free0 + 8u * s, 1u);
 #pragma unroll
         for (int s = 0; s < kCodeStages; ++s) {
             mbar_init(cfull0 + 8u * s, 1u);
@@ -238,8 +238,8 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
                 }
             }
             const uint32_t wslot = c % kWStages;
-            if (c >= kWStages &&
-                !mbar_wait_relaxed(wempty0 + 8u * wslot, ((c / kWStages) - 1u) & 1u)) {
+            if (c >= kWStages && !mbar_wait_relaxed(free0 + 8u * ((c - kWStages) % kFreeBars),
+                                                    ((c - kWStages) / kFreeBars) & 1u)) {
                 ok = false;
                 break;
             }
@@ -272,9 +272,8 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
                                 smem_desc_sw128(xslot + (k16 >> 2) * kXHalfBytes + 32u * (k16 & 3u)),
                                 idesc, (c | k16) != 0u);
                 }
-                // both slots are free once these MMAs have read them
-                umma_commit(xempty0 + 8u * xs);
-                umma_commit(wempty0 + 8u * ws);
+                // the stage's weight columns and activation slot are free once these have run
+                umma_commit(free0 + 8u * (c % kFreeBars));
                 if (c + 1u == nstage) umma_commit(done);
             }
             __syncwarp();
@@ -284,7 +283,8 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
         if (lane == 0) {
             for (uint32_t c = 0; c < nstage; ++c) {
                 const uint32_t slot = c % kXStages;
-                if (c >= kXStages && !mbar_wait_relaxed(xempty0 + 8u * slot, ((c / kXStages) - 1u) & 1u)) {
+                if (c >= kXStages && !mbar_wait_relaxed(free0 + 8u * ((c - kXStages) % kFreeBars),
+                                                        ((c - kXStages) / kFreeBars) & 1u)) {
                     ok = false;
                     break;
                 }

@@ -132,3 +132,33 @@ def test_shared_memory_operand_kernel_still_matches(cuda):
                          text=True, timeout=240)
     assert run.returncode == 0, run.stderr[-2000:]
     assert float(run.stdout.split("WORST")[1]) < GEMV_TOL
+
+
+PDL_OFF_CHILD = r"""
+import sys
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+import numpy as np, torch
+from escha_mlx_b200 import dense, synth
+from oracle import escha_oracle as oracle
+dev = torch.device("cuda", 0)
+rng = np.random.default_rng(5)
+K, IC, OC, M = 3, 512, 384, 100
+code, rin, rout = synth.coded_projection(rng, IC, OC, K)
+x = synth.activations(rng, M, IC)
+lin = dense.EschaLinear(dense.EschaWeight(code, rin, rout, device=dev))
+y = lin(torch.from_numpy(x).to(dev)).cpu().numpy()
+ri, ro = oracle.fold_scales(rin, rout)
+want = oracle.dense_linear(x, code, ri, ro, K)
+print("WORST", float(np.abs(y.astype(np.float64) - want).max() / np.abs(want).max()))
+"""
+
+
+@pytest.mark.timeout(300)
+def test_unchained_launches_give_the_same_linear(cuda):
+    """ESCHA_B200_PDL=off: transforms and the prefill GEMM launched without programmatic
+    dependent launch (the in-kernel waits become no-ops)."""
+    env = dict(os.environ, ESCHA_B200_PDL="off")
+    run = subprocess.run([sys.executable, "-c", PDL_OFF_CHILD, ROOT], env=env, capture_output=True,
+                         text=True, timeout=240)
+    assert run.returncode == 0, run.stderr[-2000:]
+    assert float(run.stdout.split("WORST")[1]) < 2e-3
