@@ -574,12 +574,19 @@ def main() -> None:
     if M <= msl.FUSE_INPUT_MAX_ROWS:
         launches_per_step = 4 if world == 1 else 8      # 4 fused GEMV + 4 peer barriers
     elif msl.use_prefill_kernel(M) and world == 1:
-        # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), seven tcgen05 GEMMs,
+        # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), the tcgen05 GEMMs,
         # and a plane sum + output transform for every projection the policy splits along K
         from escha_mlx_b200._lib import lib as _lib
-        n_split = sum(1 for _, ic, oc, _k in LAYER
-                      if _lib.escha_coded_gemm_tc_splits(ic, oc, 0) > 1)
-        launches_per_step = 4 + 7 + n_split
+        def split(ic, oc):
+            return _lib.escha_coded_gemm_tc_splits(ic, oc, 0) > 1
+        dims = {name: (ic, oc) for name, ic, oc, _k in LAYER}
+        qkv_oc = sum(dims[n][1] for n in ("q_proj", "k_proj", "v_proj"))
+        # q/k/v share one GEMM launch (their column blocks fit one wave); each still has its own
+        # plane sum when the launch is split
+        gemms = 1 + 1 + 2 + 1
+        sums = (3 if split(HIDDEN, qkv_oc) else 0) + sum(
+            1 for n in ("o_proj", "gate_proj", "up_proj", "down_proj") if split(*dims[n]))
+        launches_per_step = 4 + gemms + sums
     else:
         # q/k/v 1+1, o 1+1, gate/up 1+1, SwiGLU + down 1+1 (+ 4 barriers)
         launches_per_step = 8 if world == 1 else 12

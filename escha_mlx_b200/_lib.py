@@ -29,6 +29,7 @@ SIGNATURES = {
     "escha_scaled_had": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp, _vp]),
     "escha_scaled_had_out": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp, _vp]),
     "escha_scaled_had_pair": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp, _vp, _vp]),
+    "escha_coded_gemm_tc_many": (_i, [_i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _f, _vp, _vp, _vp]),
     "escha_scaled_had_many": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _f, _vp]),
     "escha_scaled_had_out_pair": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _vp, _vp]),
     "escha_had128": (_i, [_vp, ctypes.c_long, _vp, _vp]),

@@ -719,6 +719,66 @@ int escha_coded_gemm_tc(const void* xh, const void* code, const float* rout, int
     return cuda_result(e, "escha_coded_gemm_tc");
 }
 
+int escha_coded_gemm_tc_many(int n, const void* const* xhs, const void* const* codes,
+                             const float* const* routs, int M, int IC, const int* OCs, int K,
+                             int splits, float rs, float* const* planes, void* const* outs,
+                             void* stream) {
+    REQUIRE(n >= 1 && n <= 3, "%s: one to three projections per launch, got %d", __func__, n);
+    REQUIRE_PTR(xhs);
+    REQUIRE_PTR(codes);
+    REQUIRE_PTR(routs);
+    REQUIRE_PTR(OCs);
+    REQUIRE_PTR(outs);
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE((M + 255) / 256 <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
+    int oc_total = 0;
+    for (int i = 0; i < n; ++i) {
+        if (int rc = check_shape(__func__, K, IC, OCs[i], 128)) return rc;
+        REQUIRE(xhs[i] != nullptr && codes[i] != nullptr && routs[i] != nullptr && outs[i] != nullptr,
+                "%s: projection %d has a null pointer", __func__, i);
+        oc_total += OCs[i];
+    }
+    if (splits <= 0) splits = escha_coded_gemm_tc_splits(IC, oc_total, 0);
+    REQUIRE(splits <= IC / 128 && splits <= 65535, "%s: splits=%d exceeds the %d 128-channel stages",
+            __func__, splits, IC / 128);
+    const bool fused_out = splits == 1;
+    if (!fused_out) {
+        REQUIRE_PTR(planes);
+        for (int i = 0; i < n; ++i)
+            REQUIRE(planes[i] != nullptr, "%s: projection %d needs a plane workspace", __func__, i);
+    }
+    escha::GemmTcParams p{};
+    p.code = static_cast<const uint32_t*>(codes[0]);
+    p.xh = static_cast<const __half*>(xhs[0]);
+    p.out = fused_out ? nullptr : planes[0];
+    p.rout = fused_out ? routs[0] : nullptr;
+    p.y16 = fused_out ? static_cast<__half*>(outs[0]) : nullptr;
+    p.rs = rs;
+    p.M = M; p.IC = IC; p.OC = OCs[0]; p.K = K; p.splits = splits;
+    p.hash_mask = 0x8FFF8FFFu;
+    p.hash_xor = 0x3B603B60u;
+    p.mul2 = 2u; p.mul4 = 4u; p.mul16 = 16u; p.mul32 = 32u; p.mul64 = 64u; p.mul128 = 128u;
+    p.nproj = n;
+    const __half* xh_more[2] = {nullptr, nullptr};
+    int cb = OCs[0] / 128;
+    for (int i = 1; i < n; ++i) {
+        escha::GemmTcParams::More& m = p.more[i - 1];
+        m.code = static_cast<const uint32_t*>(codes[i]);
+        m.out = fused_out ? nullptr : planes[i];
+        m.rout = fused_out ? routs[i] : nullptr;
+        m.y16 = fused_out ? static_cast<__half*>(outs[i]) : nullptr;
+        m.OC = OCs[i];
+        m.cb0 = cb;
+        cb += OCs[i] / 128;
+        xh_more[i - 1] = static_cast<const __half*>(xhs[i]);
+    }
+    cudaError_t e = escha::launch_gemm_tcm_many(p, xh_more, as_stream(stream));
+    for (int i = 0; i < n && e == cudaSuccess && !fused_out; ++i)
+        e = escha::launch_planes_out(planes[i], routs[i], static_cast<__half*>(outs[i]), M, OCs[i],
+                                     splits, rs, as_stream(stream));
+    return cuda_result(e, "escha_coded_gemm_tc_many");
+}
+
 int escha_coded_gemm_tc_status(void) {
     int st = 0;
     if (escha::gemm_tc_status(&st) != cudaSuccess) return -1;

@@ -140,7 +140,8 @@ struct ChannelLane<3> {
 
 template <int K, int MT>
 __global__ void __launch_bounds__(kThreadsTcm, 1)
-gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ CUtensorMap xmap) {
+gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ CUtensorMap xmap0,
+                const __grid_constant__ CUtensorMap xmap1, const __grid_constant__ CUtensorMap xmap2) {
     constexpr int WPT = 8 * K;
     constexpr uint32_t kXHalfBytes = MT * kXBytesPerMt;    // one 64-channel box of activations
     constexpr uint32_t kXBytes = 2u * kXHalfBytes;         // a stage: 128 channels
@@ -157,7 +158,25 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
     __shared__ uint32_t s_tmem;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t ocb = blockIdx.x, split = blockIdx.y, r0 = blockIdx.z * (128u * MT);
+    const uint32_t split = blockIdx.y, r0 = blockIdx.z * (128u * MT);
+    // which projection of the launch this column block belongs to
+    uint32_t ocb = blockIdx.x;
+    const uint32_t* code_p = p.code;
+    float* out_p = p.out;
+    const float* rout_p = p.rout;
+    __half* y16_p = p.y16;
+    uint32_t OCp = static_cast<uint32_t>(p.OC);
+    const CUtensorMap* xm = &xmap0;
+    if (p.nproj > 1 && ocb >= static_cast<uint32_t>(p.more[0].cb0)) {
+        const int j = (p.nproj > 2 && ocb >= static_cast<uint32_t>(p.more[1].cb0)) ? 1 : 0;
+        ocb -= static_cast<uint32_t>(p.more[j].cb0);
+        code_p = p.more[j].code;
+        out_p = p.more[j].out;
+        rout_p = p.more[j].rout;
+        y16_p = p.more[j].y16;
+        OCp = static_cast<uint32_t>(p.more[j].OC);
+        xm = j ? &xmap2 : &xmap1;
+    }
     const uint32_t xring = (smem_u32(smem_raw) + 1023u) & ~1023u;   // [kXStages][2][rows][128 B]
     const uint32_t code0 = xring + kXStages * kXBytes;              // [kCodeStages][8][kRowBytes]
     const uint32_t wfull0 = smem_u32(s_wfull), xfull0 = smem_u32(s_xfull), free0 = smem_u32(s_free);
@@ -290,17 +309,17 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
                 }
                 mbar_arrive_expect_tx(xfull0 + 8u * slot, kXBytes);
                 const int32_t x0 = static_cast<int32_t>((s_first + c) * kStageK);
-                tma_load_2d(xring + slot * kXBytes, &xmap, x0, static_cast<int32_t>(r0),
+                tma_load_2d(xring + slot * kXBytes, xm, x0, static_cast<int32_t>(r0),
                             xfull0 + 8u * slot);
-                tma_load_2d(xring + slot * kXBytes + kXHalfBytes, &xmap, x0 + kXChunkK,
+                tma_load_2d(xring + slot * kXBytes + kXHalfBytes, xm, x0 + kXChunkK,
                             static_cast<int32_t>(r0), xfull0 + 8u * slot);
             }
         }
     } else if (warp == 2) {
         // ---- code warp: bulk copies (untiled, no multicast), one per tile row, eight per stage
-        const uint32_t TN = static_cast<uint32_t>(p.OC) >> 4;
+        const uint32_t TN = OCp >> 4;
         const size_t kt_words = static_cast<size_t>(TN) * WPT;   // words from tile row kt to kt+1
-        const uint32_t* grow = p.code + (static_cast<size_t>(s_first) * 8u + lane) * kt_words +
+        const uint32_t* grow = code_p + (static_cast<size_t>(s_first) * 8u + lane) * kt_words +
                                static_cast<size_t>(ocb) * 8u * WPT;
         for (uint32_t c = 0; c < nstage; ++c) {
             const uint32_t cslot = c % kCodeStages;
@@ -320,7 +339,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
     if (!ok && lane == 0) atomicExch(&g_gemm_tcm_status, 1);
 
     // ---- epilogue: accumulator lanes are output channels of the block, columns activation rows
-    const bool fused_out = p.rout != nullptr;   // only with splits == 1 (checked by the host)
+    const bool fused_out = rout_p != nullptr;   // only with splits == 1 (checked by the host)
     float* const stage = reinterpret_cast<float*>(smem_raw + (xring - smem_u32(smem_raw)));
     if (warp >= kServiceWarps) {
         // warp w reads lanes 32(w&3).. (the only ones it may address) and a quarter of the columns
@@ -332,7 +351,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
         }
         tc_fence_after_sync();
         if (ready) {
-            float* plane = p.out + static_cast<size_t>(split) * p.M * p.OC + ocb * 128u + 32u * qd + lane;
+            float* plane = out_p + static_cast<size_t>(split) * p.M * OCp + ocb * 128u + 32u * qd + lane;
 #pragma unroll 1
             for (uint32_t col = cq * (32u * MT); col < (cq + 1u) * (32u * MT); col += 16u) {
                 if (r0 + col >= static_cast<uint32_t>(p.M)) break;   // uniform: no rows left
@@ -349,7 +368,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
                     for (uint32_t i = 0; i < 16u; ++i) {
                         const uint32_t row = r0 + col + i;
                         if (row < static_cast<uint32_t>(p.M))
-                            plane[static_cast<size_t>(row) * p.OC] = __uint_as_float(v[i]);
+                            plane[static_cast<size_t>(row) * OCp] = __uint_as_float(v[i]);
                     }
                 }
             }
@@ -361,7 +380,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
         __syncthreads();
         const uint32_t nwarps = kThreadsTcm / 32u;
         const uint32_t rows_here = min(128u * MT, static_cast<uint32_t>(p.M) - r0);
-        const float4 sc = *reinterpret_cast<const float4*>(p.rout + ocb * 128u + lane * 4u);
+        const float4 sc = *reinterpret_cast<const float4*>(rout_p + ocb * 128u + lane * 4u);
         for (uint32_t r = warp; r < rows_here; r += nwarps) {
             const float4 a = *reinterpret_cast<const float4*>(stage + r * 128u + lane * 4u);
             float v[4] = {a.x, a.y, a.z, a.w};
@@ -371,7 +390,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
                                                 __fmul_rn(__fmul_rn(v[1], p.rs), sc.y)));
             packed.y = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[2], p.rs), sc.z),
                                                 __fmul_rn(__fmul_rn(v[3], p.rs), sc.w)));
-            *reinterpret_cast<uint2*>(p.y16 + static_cast<size_t>(r0 + r) * p.OC + ocb * 128u + lane * 4u) = packed;
+            *reinterpret_cast<uint2*>(y16_p + static_cast<size_t>(r0 + r) * OCp + ocb * 128u + lane * 4u) = packed;
         }
     }
     tc_fence_before_sync();
@@ -380,7 +399,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
 }
 
 template <int K, int MT>
-cudaError_t launch_tcm(const GemmTcParams& p, cudaStream_t st) {
+cudaError_t launch_tcm(const GemmTcParams& p, const __half* const* xh_more, cudaStream_t st) {
     const size_t smem = static_cast<size_t>(kXStages) * 2u * MT * kXBytesPerMt +
                         static_cast<size_t>(kCodeStages) * 8u * (8u * 8u * K * 4u) + 1024;
     static bool configured[64] = {false};
@@ -393,11 +412,20 @@ cudaError_t launch_tcm(const GemmTcParams& p, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    CUtensorMap xmap;
-    e = encode_x_map(&xmap, p.xh, p.M, p.IC, 128 * MT);
+    CUtensorMap xmap[3];
+    e = encode_x_map(&xmap[0], p.xh, p.M, p.IC, 128 * MT);
     if (e != cudaSuccess) return e;
-    const dim3 grid(p.OC / 128, p.splits, (p.M + 128 * MT - 1) / (128 * MT));
-    return launch_chained(gemm_tcm_kernel<K, MT>, grid, dim3(kThreadsTcm), smem, st, p, xmap);
+    xmap[1] = xmap[0];
+    xmap[2] = xmap[0];
+    int blocks = p.OC / 128;
+    for (int j = 0; j + 1 < p.nproj; ++j) {
+        e = encode_x_map(&xmap[1 + j], xh_more[j], p.M, p.IC, 128 * MT);
+        if (e != cudaSuccess) return e;
+        blocks += p.more[j].OC / 128;
+    }
+    const dim3 grid(blocks, p.splits, (p.M + 128 * MT - 1) / (128 * MT));
+    return launch_chained(gemm_tcm_kernel<K, MT>, grid, dim3(kThreadsTcm), smem, st, p, xmap[0], xmap[1],
+                          xmap[2]);
 }
 
 }  // namespace
@@ -406,10 +434,16 @@ bool gemm_tcm_supports(const GemmTcParams& p) {
     return p.IC % kStageK == 0 && p.splits >= 1 && p.splits <= p.IC / kStageK;
 }
 
-cudaError_t launch_gemm_tcm(const GemmTcParams& p, cudaStream_t st) {
+cudaError_t launch_gemm_tcm_many(const GemmTcParams& p, const __half* const* xh_more, cudaStream_t st) {
     const bool two = p.M > 128;
-    if (p.K == 2) return two ? launch_tcm<2, 2>(p, st) : launch_tcm<2, 1>(p, st);
-    return two ? launch_tcm<3, 2>(p, st) : launch_tcm<3, 1>(p, st);
+    if (p.K == 2) return two ? launch_tcm<2, 2>(p, xh_more, st) : launch_tcm<2, 1>(p, xh_more, st);
+    return two ? launch_tcm<3, 2>(p, xh_more, st) : launch_tcm<3, 1>(p, xh_more, st);
+}
+
+cudaError_t launch_gemm_tcm(const GemmTcParams& p, cudaStream_t st) {
+    GemmTcParams one = p;
+    one.nproj = 1;
+    return launch_gemm_tcm_many(one, nullptr, st);
 }
 
 

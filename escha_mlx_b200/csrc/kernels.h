@@ -171,6 +171,18 @@ struct GemmTcParams {
     int M, IC, OC, K, splits;
     uint32_t hash_mask, hash_xor;
     uint32_t mul2, mul4, mul16, mul32, mul64, mul128;
+    // Up to two more projections of the same IC and K in the same launch (Q/K/V), each with its
+    // own activations (tensor map), code, outputs; column blocks from cb0 on belong to it.
+    // Only the tensor-memory kernel reads these.
+    struct More {
+        const uint32_t* code;
+        float* out;
+        const float* rout;
+        __half* y16;
+        int OC, cb0;
+    };
+    int nproj;      // 0 or 1: just the projection above
+    More more[2];
 };
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);
 cudaError_t launch_planes_out(const float* planes, const float* rout, __half* y, int M, int OC,
@@ -180,6 +192,8 @@ cudaError_t gemm_tc_status(int* host_status);
 // the same product with the decoded weights handed over through tensor memory (gemm_tcm.cu)
 bool gemm_tcm_supports(const GemmTcParams& p);
 cudaError_t launch_gemm_tcm(const GemmTcParams& p, cudaStream_t st);
+// the same for p.nproj projections; xh_more[i] are the activations of p.more[i]
+cudaError_t launch_gemm_tcm_many(const GemmTcParams& p, const __half* const* xh_more, cudaStream_t st);
 cudaError_t gemm_tcm_status(int* host_status);
 
 // Cross-GPU barrier over peer-mapped flag words (peer.cu).

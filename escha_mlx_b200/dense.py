@@ -235,6 +235,13 @@ class EschaLinear(torch.nn.Module):
         return y.reshape(*shape[:-1], self._w.OC).to(dtype)
 
 
+def _joint_prefill(linears) -> bool:
+    """Whether a group of prefill projections runs as one tcgen05 launch: only when their
+    column blocks together still fit one wave (one CTA per SM holds a whole SM), i.e. when each
+    alone would be split along K and pay a launch's fixed cost for little work."""
+    return sum(lin._w.OC // 128 for lin in linears) <= msl.sm_count()
+
+
 def project_many(linears, x: torch.Tensor):
     """Evaluate up to four coded projections of the same input (Q/K/V, gate/up) in
     as few launches as their rates allow.  Outputs equal ``[lin(x) for lin in
@@ -256,6 +263,12 @@ def project_many(linears, x: torch.Tensor):
     if same_input and msl.use_prefill_kernel(rows.shape[0]):
         # prefill: one launch for all input transforms, then one tcgen05 GEMM per projection
         xhs = msl.dense_scaled_had_many(rows.contiguous(), [lin._w.rin for lin in linears], RS)
+        if len(linears) <= 3 and all(lin.K == first.K for lin in linears) and _joint_prefill(linears):
+            # projections too narrow to fill the GPU on their own share one launch
+            ys = msl.dense_gemm_tc_many(xhs, [lin._w.code for lin in linears], first.K, first._w.IC,
+                                        [lin._w.OC for lin in linears],
+                                        [lin._w.rout for lin in linears], RS)
+            return [lin._finish(y, shape, x.dtype) for lin, y in zip(linears, ys)]
         return [lin._finish(lin._product_rows(xh), shape, x.dtype) for lin, xh in zip(linears, xhs)]
     if not joint or msl.use_prefill_kernel(rows.shape[0]):
         return [lin(x) for lin in linears]

@@ -690,3 +690,41 @@ def dense_gemm_tc(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int, OC:
                                   ptr(rout, torch.float32) if rout is not None else None,
                                   m, IC, OC, K, s, float(rs), ptr(planes), ptr(out), stream()))
     return out
+
+
+@lru_cache(maxsize=None)
+def _sm_count(device_index: int) -> int:
+    return int(torch.cuda.get_device_properties(device_index).multi_processor_count)
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device."""
+    return _sm_count(torch.cuda.current_device())
+
+
+def dense_gemm_tc_many(xhs, codes, K: int, IC: int, OCs, routs, rs: float = RS,
+                       splits: int | None = None):
+    """One to three prefill projections of equal IC and K in one tcgen05 launch (Q/K/V; the
+    launch-sharing of dense_gemm_pair_out, msl.py:1880-1950, widened).  ``xhs[i]`` f16 [M, IC]
+    are the transformed activations of projection i; returns the transformed outputs f16
+    [M, OCs[i]].  The split factor is chosen for the summed width, so outputs are
+    tolerance-equal, not bit-equal, to separate ``dense_gemm_tc`` calls."""
+    n = len(codes)
+    if not (1 <= n <= 3 and len(xhs) == n and len(OCs) == n and len(routs) == n):
+        raise ValueError("dense_gemm_tc_many takes one to three projections with matching lists")
+    m = xhs[0].shape[0]
+    if m < 1 or any(x.shape != (m, IC) for x in xhs):
+        raise ValueError("dense_gemm_tc_many needs equal [M, IC] activations for every projection")
+    for c in codes:
+        _check_code(c)
+    s = int(lib.escha_coded_gemm_tc_splits(IC, int(sum(OCs)), 0)) if splits is None else int(splits)
+    dev = xhs[0].device
+    outs = [torch.empty((m, oc), dtype=torch.float16, device=dev) for oc in OCs]
+    planes = [torch.empty((s, m, oc), dtype=torch.float32, device=dev) for oc in OCs] if s > 1 else None
+    arr = ctypes.c_void_p * n
+    check(lib.escha_coded_gemm_tc_many(
+        n, arr(*[ptr(x, torch.float16) for x in xhs]), arr(*[ptr(c) for c in codes]),
+        arr(*[ptr(r, torch.float32) for r in routs]), m, IC, (ctypes.c_int * n)(*[int(o) for o in OCs]),
+        K, s, float(rs), arr(*[ptr(t) for t in planes]) if planes else None,
+        arr(*[ptr(o) for o in outs]), stream()))
+    return outs

@@ -355,6 +355,18 @@ int escha_coded_gemm_tc(const void *xh, const void *code, const float *rout, int
 /* Split policy of escha_coded_gemm_tc (shape only; sm_count <= 0 queries the device). */
 int escha_coded_gemm_tc_splits(int IC, int OC, int sm_count);
 
+/* One to three prefill projections of equal IC and K in ONE tcgen05 launch (Q/K/V), each with
+ * its own transformed activations xhs[i] f16 [M, IC], code, transform vector routs[i] f32 [OCs[i]]
+ * (required) and f16 output outs[i] [M, OCs[i]].  splits <= 0 picks the policy value for the
+ * summed width; with splits > 1, planes[i] is an f32 workspace of splits * M * OCs[i].
+ * The reference dispatches the pair form of this (dense_gemm_pair_out, msl.py:1880-1950) for
+ * gate/up and K/V; here it also removes two launches whose fixed cost exceeds their work.
+ * xhs, codes, routs, planes, outs are HOST arrays of n device pointers, OCs a host int array. */
+int escha_coded_gemm_tc_many(int n, const void *const *xhs, const void *const *codes,
+                             const float *const *routs, int M, int IC, const int *OCs, int K,
+                             int splits, float rs, float *const *planes, void *const *outs,
+                             void *stream);
+
 /* 0 if no tensor-core GEMM launch on the current device has given up a bounded wait
  * since the library was loaded; synchronises the device.  For tests and diagnostics. */
 int escha_coded_gemm_tc_status(void);

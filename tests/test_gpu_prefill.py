@@ -162,3 +162,33 @@ def test_unchained_launches_give_the_same_linear(cuda):
                          text=True, timeout=240)
     assert run.returncode == 0, run.stderr[-2000:]
     assert float(run.stdout.split("WORST")[1]) < 2e-3
+
+
+@pytest.mark.parametrize("M,ocs,splits", [(100, (384, 128, 128), None), (200, (256, 128), 1),
+                                          (40, (128, 128, 256), 3), (130, (256,), 2)])
+def test_prefill_projections_sharing_one_launch(cuda, oracle, M, ocs, splits):
+    """Up to three projections of equal IC and K in one tcgen05 launch: every output within
+    tolerance of the oracle and of its own separate launch."""
+    rng = np.random.default_rng(M + len(ocs))
+    K, IC = 2, 1024
+    xhs, codes, routs, raw = [], [], [], []
+    for oc in ocs:
+        code, _, rout = synth.coded_projection(rng, IC, oc, K)
+        xh = (rng.standard_normal((M, IC)) * 0.25).astype(np.float16)
+        raw.append((code, xh, rout))
+        xhs.append(dev(xh, cuda))
+        codes.append(msl.code_tensor(code, cuda))
+        routs.append(dev(rout.astype(np.float32), cuda))
+    got = msl.dense_gemm_tc_many(xhs, codes, K, IC, list(ocs), routs, msl.RS, splits=splits)
+    torch.cuda.synchronize()
+    assert lib.escha_coded_gemm_tc_status() == 0
+    again = msl.dense_gemm_tc_many(xhs, codes, K, IC, list(ocs), routs, msl.RS, splits=splits)
+    for y, y2, (code, xh, rout), xd, c, ro, oc in zip(got, again, raw, xhs, codes, routs, ocs):
+        assert y.shape == (M, oc) and torch.equal(y, y2)       # deterministic
+        want = oracle.output_transform(oracle.gemv_f64(xh, code, None, K, IC, oc).astype(np.float32),
+                                       rout.astype(np.float32))
+        assert rel_err(host(y), want) < 2e-3
+        alone = msl.dense_gemm_tc(xd, c, K, IC, oc, rout=ro)
+        assert rel_err(host(y), host(alone)) < 2e-3
+    with pytest.raises(ValueError):
+        msl.dense_gemm_tc_many(xhs, codes, K, IC, list(ocs) + [128], routs)
