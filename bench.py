@@ -581,10 +581,10 @@ def main() -> None:
             return _lib.escha_coded_gemm_tc_splits(ic, oc, 0) > 1
         dims = {name: (ic, oc) for name, ic, oc, _k in LAYER}
         qkv_oc = sum(dims[n][1] for n in ("q_proj", "k_proj", "v_proj"))
-        # q/k/v share one GEMM launch (their column blocks fit one wave); each still has its own
-        # plane sum when the launch is split
+        # q/k/v share one GEMM launch (their column blocks fit one wave) and, up to 128 rows,
+        # one plane-sum launch
         gemms = 1 + 1 + 2 + 1
-        sums = (3 if split(HIDDEN, qkv_oc) else 0) + sum(
+        sums = ((1 if M <= 128 else 3) if split(HIDDEN, qkv_oc) else 0) + sum(
             1 for n in ("o_proj", "gate_proj", "up_proj", "down_proj") if split(*dims[n]))
         launches_per_step = 4 + gemms + sums
     else:

@@ -404,7 +404,69 @@ planes_out_kernel(const float* __restrict__ planes, const float* __restrict__ ro
                                         __fmul_rn(__fmul_rn(v[3], rs), sc.w)));
     *reinterpret_cast<uint2*>(y + off) = packed;
 }
+// the same for up to three projections of one launch
+struct PlanesOutMany {
+    const float* planes[3];
+    const float* rout[3];
+    __half* y[3];
+    int OC[3];
+    int n;
+};
+__global__ void __launch_bounds__(256)
+planes_out_many_kernel(PlanesOutMany s, int M, int splits, float rs) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const uint32_t lane = threadIdx.x & 31u;
+    uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    // units are laid out projection after projection, M * (OC / 128) each
+    uint32_t pj = 0;
+    while (pj + 1u < static_cast<uint32_t>(s.n) &&
+           unit >= static_cast<uint32_t>(M) * (static_cast<uint32_t>(s.OC[pj]) >> 7)) {
+        unit -= static_cast<uint32_t>(M) * (static_cast<uint32_t>(s.OC[pj]) >> 7);
+        ++pj;
+    }
+    const uint32_t OC = static_cast<uint32_t>(s.OC[pj]);
+    const uint32_t per_row = OC >> 7;
+    const uint32_t row = unit / per_row;
+    if (row >= static_cast<uint32_t>(M)) return;
+    const uint32_t blk = unit - row * per_row;
+    const size_t off = static_cast<size_t>(row) * OC + blk * 128u + lane * 4u;
+    const size_t plane = static_cast<size_t>(M) * OC;
+    const float* planes = s.planes[pj];
+    const float4 a = *reinterpret_cast<const float4*>(planes + off);
+    float v[4] = {a.x, a.y, a.z, a.w};
+    for (int i = 1; i < splits; ++i) {
+        const float4 b = *reinterpret_cast<const float4*>(planes + i * plane + off);
+        v[0] = __fadd_rn(v[0], b.x); v[1] = __fadd_rn(v[1], b.y);
+        v[2] = __fadd_rn(v[2], b.z); v[3] = __fadd_rn(v[3], b.w);
+    }
+    wht128_warp(v, lane);
+    const float4 sc = *reinterpret_cast<const float4*>(s.rout[pj] + blk * 128u + lane * 4u);
+    uint2 packed;
+    packed.x = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[0], rs), sc.x),
+                                        __fmul_rn(__fmul_rn(v[1], rs), sc.y)));
+    packed.y = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[2], rs), sc.z),
+                                        __fmul_rn(__fmul_rn(v[3], rs), sc.w)));
+    *reinterpret_cast<uint2*>(s.y[pj] + off) = packed;
+}
 }  // namespace
+
+cudaError_t launch_planes_out_many(int n, const float* const* planes, const float* const* routs,
+                                   __half* const* ys, const int* OCs, int M, int splits, float rs,
+                                   cudaStream_t st) {
+    PlanesOutMany s{};
+    s.n = n;
+    long units = 0;
+    for (int i = 0; i < n; ++i) {
+        s.planes[i] = planes[i];
+        s.rout[i] = routs[i];
+        s.y[i] = ys[i];
+        s.OC[i] = OCs[i];
+        units += static_cast<long>(M) * (OCs[i] / 128);
+    }
+    return launch_chained(planes_out_many_kernel, dim3(static_cast<unsigned>((units + 7) / 8)),
+                          dim3(256), 0, st, s, M, splits, rs);
+}
 
 cudaError_t launch_planes_out(const float* planes, const float* rout, __half* y, int M, int OC,
                               int splits, float rs, cudaStream_t st) {

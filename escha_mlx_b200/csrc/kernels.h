@@ -187,6 +187,9 @@ struct GemmTcParams {
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);
 cudaError_t launch_planes_out(const float* planes, const float* rout, __half* y, int M, int OC,
                               int splits, float rs, cudaStream_t st);
+cudaError_t launch_planes_out_many(int n, const float* const* planes, const float* const* routs,
+                                   __half* const* ys, const int* OCs, int M, int splits, float rs,
+                                   cudaStream_t st);
 cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int splits, cudaStream_t st);
 cudaError_t gemm_tc_status(int* host_status);
 // the same product with the decoded weights handed over through tensor memory (gemm_tcm.cu)
