@@ -486,9 +486,10 @@ def dense_gemm_rows_direct(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC:
 
 #: From this many rows on the dense modules run the product on tcgen05 (decode once per 256
 #: rows into tensor memory) instead of the register-fragment kernel, which decodes once per 16
-#: rows.  Measured on the 27B-class layer: equal at 16 rows (185 us per layer step), and at 24 /
-#: 32 / 40 / 48 rows 187 / 189 / 190 / 193 us against 306 / 323 / 437 / 457 us.
-PREFILL_MIN_ROWS = int(os.environ.get("ESCHA_B200_PREFILL_MIN_ROWS", "17"))
+#: rows.  Measured on the 27B-class layer (us per layer step, tcgen05 vs register-fragment):
+#: 9 rows 202 vs 170, 12 rows 203 vs 176, 16 rows 172 vs 186, 24 rows 175 vs 306, 32 rows 178 vs
+#: 323, 48 rows 193 vs 457.
+PREFILL_MIN_ROWS = int(os.environ.get("ESCHA_B200_PREFILL_MIN_ROWS", "16"))
 
 
 def use_prefill_kernel(m: int) -> bool:
@@ -500,7 +501,9 @@ def dense_gemm_mat(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int,
     """Matrix-unit dense GEMM (:1762-1782): the tcgen05 kernel at prefill row counts,
     the register-fragment tensor-core kernel below them."""
     _check_code(code_u32)
-    if use_prefill_kernel(xh.shape[0]):
+    # up to one 16-row block (the reference's DENSE_MAT_R) the register-fragment kernel, whose
+    # rows are bit-identical to the per-row GEMV
+    if xh.shape[0] > DENSE_MAT_R and use_prefill_kernel(xh.shape[0]):
         return dense_gemm_tc(xh, code_u32, K, IC, OC)
     return _gemv_mma_dense(xh, code_u32, None, K, IC, OC, None)
 
