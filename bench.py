@@ -548,8 +548,10 @@ def main() -> None:
         return outs
 
     def layer_step(layer, x, bufs=None):
-        if world > 1 and pg is None:
+        if world > 1 and (pg is None or msl.use_prefill_kernel(M)):
             # NCCL form of the same exchange: an all-gather of every projection's f16 output
+            # (also from 16 rows on, where each rank's shard runs on the tcgen05 kernel, whose
+            # epilogue does not store to peers)
             ag = sharding.all_gather_columns
             q, k, v = (ag(t) for t in dense.project_many(
                 [layer["q_proj"], layer["k_proj"], layer["v_proj"]], x))
@@ -573,13 +575,14 @@ def main() -> None:
     # gate/up, swiglu+down (4); larger batches add the separate input transforms
     if M <= msl.FUSE_INPUT_MAX_ROWS:
         launches_per_step = 4 if world == 1 else 8      # 4 fused GEMV + 4 peer barriers
-    elif msl.use_prefill_kernel(M) and world == 1:
+    elif msl.use_prefill_kernel(M):
         # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), the tcgen05 GEMMs,
         # and a plane sum + output transform for every projection the policy splits along K
         from escha_mlx_b200._lib import lib as _lib
         def split(ic, oc):
             return _lib.escha_coded_gemm_tc_splits(ic, oc, 0) > 1
-        dims = {name: (ic, oc) for name, ic, oc, _k in LAYER}
+        # a rank holds 1/world of every projection's output channels (split-N)
+        dims = {name: (ic, oc // world) for name, ic, oc, _k in LAYER}
         qkv_oc = sum(dims[n][1] for n in ("q_proj", "k_proj", "v_proj"))
         # q/k/v share one GEMM launch (their column blocks fit one wave) and, up to 128 rows,
         # one plane-sum launch
@@ -772,7 +775,8 @@ def main() -> None:
                                                           "avg_launch_us", "traffic")}})
         if world > 1:
             line["config"]["exchange"] = ("GEMV epilogue stores into every GPU's gathered row "
-                                          "(peer memory) + barrier kernel" if pg is not None
+                                          "(peer memory) + barrier kernel"
+                                          if pg is not None and not msl.use_prefill_kernel(M)
                                           else "NCCL all-gather per projection")
             line["peer_barrier_gave_up"] = bool(barrier_gave_up)   # must be false for a valid run
         if tensor_leg:
