@@ -547,11 +547,14 @@ def main() -> None:
         pg.barrier()
         return outs
 
+    tc_shards = world > 1 and msl.use_prefill_kernel(M) and M >= 32
+
     def layer_step(layer, x, bufs=None):
-        if world > 1 and (pg is None or msl.use_prefill_kernel(M)):
+        if world > 1 and (pg is None or tc_shards):
             # NCCL form of the same exchange: an all-gather of every projection's f16 output
-            # (also from 16 rows on, where each rank's shard runs on the tcgen05 kernel, whose
-            # epilogue does not store to peers)
+            # (also from 32 rows on, where each rank's shard runs on the tcgen05 kernel, whose
+            # epilogue does not store to peers; measured on 2 GPUs: 16 rows 178 us through the
+            # GEMV's peer stores, 32 rows 275 us that way and 247 us this way)
             ag = sharding.all_gather_columns
             q, k, v = (ag(t) for t in dense.project_many(
                 [layer["q_proj"], layer["k_proj"], layer["v_proj"]], x))
@@ -575,7 +578,7 @@ def main() -> None:
     # gate/up, swiglu+down (4); larger batches add the separate input transforms
     if M <= msl.FUSE_INPUT_MAX_ROWS:
         launches_per_step = 4 if world == 1 else 8      # 4 fused GEMV + 4 peer barriers
-    elif msl.use_prefill_kernel(M):
+    elif msl.use_prefill_kernel(M) and (world == 1 or tc_shards):
         # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), the tcgen05 GEMMs,
         # and a plane sum + output transform for every projection the policy splits along K
         from escha_mlx_b200._lib import lib as _lib
@@ -776,7 +779,7 @@ def main() -> None:
         if world > 1:
             line["config"]["exchange"] = ("GEMV epilogue stores into every GPU's gathered row "
                                           "(peer memory) + barrier kernel"
-                                          if pg is not None and not msl.use_prefill_kernel(M)
+                                          if pg is not None and not tc_shards
                                           else "NCCL all-gather per projection")
             line["peer_barrier_gave_up"] = bool(barrier_gave_up)   # must be false for a valid run
         if tensor_leg:
