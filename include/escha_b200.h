@@ -339,8 +339,9 @@ int escha_peer_barrier(int32_t *local_flags, int32_t *const *peer_flags, int ran
  * hundreds of rows:  mid[r,:] = f32(xh[r,:]) @ f32(decode(code)),  f32 [M,OC].
  * Replaces msl.dense_gemm_mat and the row-blocked msl.dense_gemm_rows at prefill
  * sizes (msl.py:1608-1782, :1785-1841): every weight is decoded once per 256 rows
- * into shared memory as binary16 and contracted by tcgen05.mma with fp32
- * accumulators in tensor memory.  Reassociated like dense_gemm_mat, deterministic:
+ * into tensor memory as binary16 (the A operand of tcgen05.mma; into a shared-memory
+ * ring with ESCHA_B200_TC_WEIGHTS=smem) and contracted with fp32 accumulators in
+ * tensor memory.  Reassociated like dense_gemm_mat, deterministic:
  * tolerance-equal to escha_gemv_ref, bit-reproducible for fixed (shape, splits).
  *   xh [M,IC] binary16 (already input-transformed), code [IC/16, OC/16, 8K].
  *   rout == NULL: out is f32 mid [M,OC];  rout != NULL: out is binary16
