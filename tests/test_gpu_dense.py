@@ -403,3 +403,15 @@ def test_scaled_had_many_equals_separate_launches(cuda, n, with_up):
         assert torch.equal(g, msl.dense_scaled_had(src, rin, msl.RS))
     with pytest.raises(ValueError):
         msl.dense_scaled_had_many(x, [], msl.RS)
+
+
+def test_scaled_had_many_large_swiglu_form(cuda):
+    """The several-blocks-per-warp instantiation (large SwiGLU inputs) is bit-identical too,
+    including a ragged tail of blocks."""
+    rng = np.random.default_rng(77)
+    M, IC = 131, 128 * 129            # 16899 blocks: not a multiple of four
+    x = dev((rng.standard_normal((M, IC)) * 0.5).astype(np.float16), cuda)
+    up = dev((rng.standard_normal((M, IC)) * 0.5).astype(np.float16), cuda)
+    rin = dev((rng.standard_normal(IC) * 0.02).astype(np.float32), cuda)
+    got = msl.dense_scaled_had_many(x, [rin], msl.RS, up=up)[0]
+    assert torch.equal(got, msl.dense_scaled_had(msl.swiglu_pair(x, up), rin, msl.RS))
