@@ -692,8 +692,15 @@ int escha_coded_gemm_tc(const void* xh, const void* code, const float* rout, int
     REQUIRE(splits <= IC / 64 && splits <= 65535, "%s: splits=%d exceeds the %d 64-channel chunks",
             __func__, splits, IC / 64);
     REQUIRE((M + 255) / 256 <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
-    const bool fused_out = rout != nullptr && splits == 1;   // transform inside the GEMM's epilogue
-    const bool need_planes = splits > 1;
+    // transform inside the GEMM's epilogue: unsplit, or split with the split-order sum done by a
+    // cluster of CTAs inside the kernel
+    static const bool cluster_sums = [] {
+        const char* v = std::getenv("ESCHA_B200_TC_CLUSTER_SUM");
+        return v == nullptr || std::strcmp(v, "0") != 0;
+    }();
+    const bool fused_out = rout != nullptr &&
+        (splits == 1 || (cluster_sums && escha::gemm_tc_uses_tmem() && escha::gemm_tcm_cluster_sum(IC, splits)));
+    const bool need_planes = splits > 1 && !fused_out;
     if (need_planes) REQUIRE_PTR(planes);
     escha::GemmTcParams p{};
     p.code = static_cast<const uint32_t*>(code);
@@ -713,7 +720,7 @@ int escha_coded_gemm_tc(const void* xh, const void* code, const float* rout, int
     if (e == cudaSuccess && rout != nullptr && !fused_out)
         e = escha::launch_planes_out(planes, rout, static_cast<__half*>(out), M, OC, splits, rs,
                                      as_stream(stream));
-    else if (e == cudaSuccess && splits > 1)
+    else if (e == cudaSuccess && need_planes)
         e = escha::launch_sum_planes(planes, static_cast<float*>(out), static_cast<size_t>(M) * OC,
                                      splits, as_stream(stream));
     return cuda_result(e, "escha_coded_gemm_tc");
@@ -741,7 +748,11 @@ int escha_coded_gemm_tc_many(int n, const void* const* xhs, const void* const* c
     if (splits <= 0) splits = escha_coded_gemm_tc_splits(IC, oc_total, 0);
     REQUIRE(splits <= IC / 128 && splits <= 65535, "%s: splits=%d exceeds the %d 128-channel stages",
             __func__, splits, IC / 128);
-    const bool fused_out = splits == 1;
+    static const bool cluster_sums = [] {
+        const char* v = std::getenv("ESCHA_B200_TC_CLUSTER_SUM");
+        return v == nullptr || std::strcmp(v, "0") != 0;
+    }();
+    const bool fused_out = splits == 1 || (cluster_sums && escha::gemm_tcm_cluster_sum(IC, splits));
     if (!fused_out) {
         REQUIRE_PTR(planes);
         for (int i = 0; i < n; ++i)

@@ -344,13 +344,17 @@ cudaError_t launch_tc(const GemmTcParams& p, cudaStream_t st) {
 
 }  // namespace
 
-cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
-    // ESCHA_B200_TC_WEIGHTS=tmem (default) | smem: which operand path the decoded weights take
+// ESCHA_B200_TC_WEIGHTS=tmem (default) | smem: which operand path the decoded weights take
+bool gemm_tc_uses_tmem() {
     static const bool through_tmem = [] {
         const char* e = std::getenv("ESCHA_B200_TC_WEIGHTS");
         return e == nullptr || std::strcmp(e, "smem") != 0;
     }();
-    if (through_tmem && gemm_tcm_supports(p)) return launch_gemm_tcm(p, st);
+    return through_tmem;
+}
+
+cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
+    if (gemm_tc_uses_tmem() && gemm_tcm_supports(p)) return launch_gemm_tcm(p, st);
     const bool two = p.M > 128;
     if (p.K == 2) return two ? launch_tc<2, 2>(p, st) : launch_tc<2, 1>(p, st);
     return two ? launch_tc<3, 2>(p, st) : launch_tc<3, 1>(p, st);

@@ -339,7 +339,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
     if (!ok && lane == 0) atomicExch(&g_gemm_tcm_status, 1);
 
     // ---- epilogue: accumulator lanes are output channels of the block, columns activation rows
-    const bool fused_out = rout_p != nullptr;   // only with splits == 1 (checked by the host)
+    const bool fused_out = rout_p != nullptr;   // splits == 1, or a cluster launch of S <= 8 CTAs
     float* const stage = reinterpret_cast<float*>(smem_raw + (xring - smem_u32(smem_raw)));
     if (warp >= kServiceWarps) {
         // warp w reads lanes 32(w&3).. (the only ones it may address) and a quarter of the columns
@@ -376,14 +376,34 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
     }
     if (fused_out) {
         // every warp of the CTA: one row per step, four consecutive channels per lane ->
-        // 128-point butterflies across the warp, scales, binary16 store
+        // 128-point butterflies across the warp, scales, binary16 store.
+        // A launch split along K runs as clusters of S CTAs (one per split, same output block):
+        // every CTA leaves its partial tile in its own shared memory, and after a cluster barrier
+        // CTA s sums rows s, s+S, ... over all S tiles in split order through distributed shared
+        // memory -- the split-order plane sum without planes, a second launch or memory traffic.
         __syncthreads();
+        const bool cluster_sum = S > 1u;
+        if (cluster_sum) cluster_sync_all();
         const uint32_t nwarps = kThreadsTcm / 32u;
         const uint32_t rows_here = min(128u * MT, static_cast<uint32_t>(p.M) - r0);
         const float4 sc = *reinterpret_cast<const float4*>(rout_p + ocb * 128u + lane * 4u);
-        for (uint32_t r = warp; r < rows_here; r += nwarps) {
-            const float4 a = *reinterpret_cast<const float4*>(stage + r * 128u + lane * 4u);
-            float v[4] = {a.x, a.y, a.z, a.w};
+        const uint32_t r_first = cluster_sum ? split + S * warp : warp;
+        const uint32_t r_step = cluster_sum ? S * nwarps : nwarps;
+        for (uint32_t r = r_first; r < rows_here; r += r_step) {
+            float v[4];
+            if (cluster_sum) {
+                const uint32_t at = xring + (r * 128u + lane * 4u) * 4u;
+                const float4 a = ld_cluster_f4(at, 0u);
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+                for (uint32_t i = 1; i < S; ++i) {
+                    const float4 b = ld_cluster_f4(at, i);
+                    v[0] = __fadd_rn(v[0], b.x); v[1] = __fadd_rn(v[1], b.y);
+                    v[2] = __fadd_rn(v[2], b.z); v[3] = __fadd_rn(v[3], b.w);
+                }
+            } else {
+                const float4 a = *reinterpret_cast<const float4*>(stage + r * 128u + lane * 4u);
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            }
             wht128_warp(v, lane);
             uint2 packed;
             packed.x = as_u32(__floats2half2_rn(__fmul_rn(__fmul_rn(v[0], p.rs), sc.x),
@@ -392,6 +412,8 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
                                                 __fmul_rn(__fmul_rn(v[3], p.rs), sc.w)));
             *reinterpret_cast<uint2*>(y16_p + static_cast<size_t>(r0 + r) * OCp + ocb * 128u + lane * 4u) = packed;
         }
+        // no CTA may leave while another still reads its tile
+        if (cluster_sum) cluster_sync_all();
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -424,11 +446,20 @@ cudaError_t launch_tcm(const GemmTcParams& p, const __half* const* xh_more, cuda
         blocks += p.more[j].OC / 128;
     }
     const dim3 grid(blocks, p.splits, (p.M + 128 * MT - 1) / (128 * MT));
+    if (p.rout != nullptr && p.splits > 1)   // the splits of an output block form a cluster
+        return launch_chained_cluster(gemm_tcm_kernel<K, MT>, grid, dim3(kThreadsTcm), smem, st,
+                                      static_cast<unsigned>(p.splits), p, xmap[0], xmap[1], xmap[2]);
     return launch_chained(gemm_tcm_kernel<K, MT>, grid, dim3(kThreadsTcm), smem, st, p, xmap[0], xmap[1],
                           xmap[2]);
 }
 
 }  // namespace
+
+// whether a launch with a transform vector and `splits` > 1 can sum its splits inside the kernel
+// (clusters of up to 8 CTAs, the portable limit)
+bool gemm_tcm_cluster_sum(int IC, int splits) {
+    return splits > 1 && splits <= 8 && IC % kStageK == 0 && splits <= IC / kStageK;
+}
 
 bool gemm_tcm_supports(const GemmTcParams& p) {
     return p.IC % kStageK == 0 && p.splits >= 1 && p.splits <= p.IC / kStageK;

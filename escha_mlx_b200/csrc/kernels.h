@@ -194,6 +194,9 @@ cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int spl
 cudaError_t gemm_tc_status(int* host_status);
 // the same product with the decoded weights handed over through tensor memory (gemm_tcm.cu)
 bool gemm_tcm_supports(const GemmTcParams& p);
+bool gemm_tcm_cluster_sum(int IC, int splits);
+// whether launch_gemm_tc would take the tensor-memory kernel at all (environment switch)
+bool gemm_tc_uses_tmem();
 cudaError_t launch_gemm_tcm(const GemmTcParams& p, cudaStream_t st);
 // the same for p.nproj projections; xh_more[i] are the activations of p.more[i]
 cudaError_t launch_gemm_tcm_many(const GemmTcParams& p, const __half* const* xh_more, cudaStream_t st);

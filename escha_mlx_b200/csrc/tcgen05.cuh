@@ -142,6 +142,21 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
         ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// ---- thread-block clusters: barrier over all CTAs of the cluster, and reads of another CTA's
+// shared memory (distributed shared memory)
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 16 bytes at shared address `addr` (an address of this CTA's window) of the cluster's CTA `rank`
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
 // Tensor map of the [M, IC] binary16 activations for boxes of 64 channels x rows_per_box rows,
 // 128-byte swizzle (defined with the shared-memory-operand kernel).
 cudaError_t encode_x_map(CUtensorMap* map, const __half* xh, int M, int IC, int rows_per_box);
