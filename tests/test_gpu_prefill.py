@@ -156,8 +156,9 @@ print("WORST", float(np.abs(y.astype(np.float64) - want).max() / np.abs(want).ma
 @pytest.mark.timeout(300)
 def test_unchained_launches_give_the_same_linear(cuda):
     """ESCHA_B200_PDL=off: transforms and the prefill GEMM launched without programmatic
-    dependent launch (the in-kernel waits become no-ops)."""
-    env = dict(os.environ, ESCHA_B200_PDL="off")
+    dependent launch (the in-kernel waits become no-ops); ESCHA_B200_TC_CLUSTER_SUM=0: the split
+    launch writes f32 planes and a second kernel sums and transforms them."""
+    env = dict(os.environ, ESCHA_B200_PDL="off", ESCHA_B200_TC_CLUSTER_SUM="0")
     run = subprocess.run([sys.executable, "-c", PDL_OFF_CHILD, ROOT], env=env, capture_output=True,
                          text=True, timeout=240)
     assert run.returncode == 0, run.stderr[-2000:]
