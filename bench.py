@@ -580,12 +580,12 @@ def main() -> None:
         launches_per_step = 4 if world == 1 else 8      # 4 fused GEMV + 4 peer barriers
     elif msl.use_prefill_kernel(M) and (world == 1 or tc_shards):
         # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), the tcgen05 GEMMs,
-        # and a plane sum + output transform for every projection split more than 8 ways along K
+        # and a plane sum + output transform for every projection split more than 4 ways along K
         from escha_mlx_b200._lib import lib as _lib
         def split(ic, oc):
-            # splits of up to 8 are summed inside the GEMM by a cluster of CTAs; more need a
+            # splits of up to 4 are summed inside the GEMM by a cluster of CTAs; more need a
             # plane-sum launch
-            return _lib.escha_coded_gemm_tc_splits(ic, oc, 0) > 8
+            return _lib.escha_coded_gemm_tc_splits(ic, oc, 0) > 4
         # a rank holds 1/world of every projection's output channels (split-N)
         dims = {name: (ic, oc // world) for name, ic, oc, _k in LAYER}
         qkv_oc = sum(dims[n][1] for n in ("q_proj", "k_proj", "v_proj"))

@@ -348,7 +348,7 @@ int escha_peer_barrier(int32_t *local_flags, int32_t *const *peer_flags, int ran
  *     y = f16((H128(mid)*rs)*rout), the split-order sum and the output transform
  *     (msl.dense_scaled_had_out, ref.py:226-228) running as one second kernel.
  *     With splits == 1 the transform runs in the GEMM's own epilogue instead, and with
- *     2..8 splits the splits of an output block run as a thread-block cluster that sums
+ *     2..4 splits the splits of an output block run as a thread-block cluster that sums
  *     them in split order through distributed shared memory and transforms (same bits).
  *   splits <= 0 selects escha_coded_gemm_tc_splits().  `planes` is scratch of
  *     splits*M*OC floats, needed when splits > 1. */
