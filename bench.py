@@ -447,6 +447,10 @@ def main() -> None:
                          "profiler captures, where less device memory must be saved and restored)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0,
                     help="bounded CPU-baseline sample (rank 0, N=1)")
+    ap.add_argument("--group", default="layer", choices=["layer", "model"],
+                    help="launch grouping at small batch: layer = the projections that read the "
+                         "step input share one launch (2 launches per step); model = q/k/v | o | "
+                         "gate/up | SwiGLU+down (4 launches)")
     ap.add_argument("--no-moe-leg", action="store_true",
                     help="skip the short MoE-layer measurement appended to the default line")
     ap.add_argument("--only", default=None,
@@ -548,6 +552,12 @@ def main() -> None:
         return outs
 
     tc_shards = world > 1 and msl.use_prefill_kernel(M) and M >= 32
+    # launch grouping of the fused small-batch path: "layer" follows this step's own data flow
+    # (q/k/v, o, gate, up all read the step input: one launch; SwiGLU + down: a second);
+    # "model" keeps the four launches a transformer layer with attention between q/k/v and o
+    # needs (q/k/v | o | gate/up | SwiGLU + down)
+    joint_launches = (args.group == "layer" and world == 1 and M <= msl.FUSE_INPUT_MAX_ROWS
+                      and msl.mixed_rates_supported())
 
     def layer_step(layer, x, bufs=None):
         if world > 1 and (pg is None or tc_shards):
@@ -568,16 +578,22 @@ def main() -> None:
             g, u = tp_launch(layer, bufs, ("gate_proj", "up_proj"), x)
             (d,) = tp_launch(layer, bufs, ("down_proj",), g, u)   # full-width SwiGLU input
             return q, k, v, o, d
-        q, k, v = dense.project_many([layer["q_proj"], layer["k_proj"], layer["v_proj"]], x)
-        o = layer["o_proj"](x)
-        g, u = dense.project_pair(layer["gate_proj"], layer["up_proj"], x)
+        if joint_launches:
+            # every projection that reads the step's input in ONE launch (2-bit and 3-bit
+            # streams side by side), SwiGLU + down in a second
+            q, k, v, o, g, u = dense.project_many(
+                [layer[n] for n in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj")], x)
+        else:
+            q, k, v = dense.project_many([layer["q_proj"], layer["k_proj"], layer["v_proj"]], x)
+            o = layer["o_proj"](x)
+            g, u = dense.project_pair(layer["gate_proj"], layer["up_proj"], x)
         d = dense.swiglu_project(layer["down_proj"], g, u)
         return q, k, v, o, d
 
     # launches of this library's kernels per step: fused small-batch path = q/k/v, o,
     # gate/up, swiglu+down (4); larger batches add the separate input transforms
     if M <= msl.FUSE_INPUT_MAX_ROWS:
-        launches_per_step = 4 if world == 1 else 8      # 4 fused GEMV + 4 peer barriers
+        launches_per_step = (2 if joint_launches else 4) if world == 1 else 8   # + 4 peer barriers
     elif msl.use_prefill_kernel(M) and (world == 1 or tc_shards):
         # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), the tcgen05 GEMMs,
         # and a plane sum + output transform for every projection split more than 4 ways along K
@@ -771,11 +787,12 @@ def main() -> None:
             # the per-projection profiler captures
             sep = dict(line["roofline"])
             line["roofline"].update({
-                "achieved": value, "frac": value / peak, "launches_timed": 4 * args.steps,
-                "avg_launch_us": ms_total * 1e3 / (4 * args.steps),
-                "algorithmic_bytes_per_launch_avg": LAYER_BYTES / 4,
-                "traffic": (traffic * 7 / 4) if traffic else None,
-                "timed": "the timed steps themselves: four fused launches per step",
+                "achieved": value, "frac": value / peak,
+                "launches_timed": launches_per_step * args.steps,
+                "avg_launch_us": ms_total * 1e3 / (launches_per_step * args.steps),
+                "algorithmic_bytes_per_launch_avg": LAYER_BYTES / launches_per_step,
+                "traffic": (traffic * 7 / launches_per_step) if traffic else None,
+                "timed": f"the timed steps themselves: {launches_per_step} fused launches per step",
                 "separate_launches": {k: sep[k] for k in ("achieved", "frac", "launches_timed",
                                                           "avg_launch_us", "traffic")}})
         if world > 1:

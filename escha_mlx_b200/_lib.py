@@ -14,7 +14,8 @@ import os
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libescha_b200.so")
+# ESCHA_B200_LIBRARY points at another build of the same library (kernel experiments)
+LIB_PATH = os.environ.get("ESCHA_B200_LIBRARY") or os.path.join(_PKG, "libescha_b200.so")
 
 ESCHA_OK, ESCHA_EINVAL, ESCHA_ECUDA = 0, -1, -2
 
@@ -45,6 +46,9 @@ SIGNATURES = {
     "escha_coded_projections_gather": (_i, [_vp, _vp, _vp, ctypes.c_long, _i, _i, _i, _vp, _vp, _vp,
                                            _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _f, _vp,
                                            _sz, _vp, _i, _vp, _vp, _vp]),
+    "escha_coded_projections_mixed": (_i, [_vp, _vp, _vp, ctypes.c_long, _i, _i, _i, _vp, _vp, _vp,
+                                          _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp,
+                                          _sz, _vp, _i, _vp, _vp, _vp]),
     "escha_peer_barrier": (_i, [_vp, _vp, _i, _i, _vp]),
     "escha_moe_jobs_bound": (_i, [_i, _i, _i]),
     "escha_moe_group_rows": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _vp]),
@@ -56,6 +60,8 @@ SIGNATURES = {
     "escha_coded_gemm_tc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
     "escha_coded_gemm_tc_splits": (_i, [_i, _i, _i]),
     "escha_coded_gemm_tc_status": (_i, []),
+    "escha_coded_gemv_status": (_i, []),
+    "escha_debug_gemv_stall": (None, [_i, ctypes.c_uint]),
     "escha_moe_route": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
                             _vp, _i, _vp, _sz, _vp]),
     "escha_moe_shared_finish": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),

@@ -67,6 +67,9 @@ constexpr size_t kMaxCounters = kCounterBytes / sizeof(int32_t);
 // escha_moe_route's counters (one per tile of 8 tokens + one) at the end of the region
 constexpr size_t kRouteTiles = 4096;
 constexpr size_t kRouteCounters = kRouteTiles + 1;
+// the persistent GEMV's two scheduling words sit just below them
+constexpr size_t kSchedCounters = 2;
+constexpr size_t kSchedIndex = kMaxCounters - kRouteCounters - kSchedCounters;
 
 }  // namespace
 
@@ -317,17 +320,16 @@ int escha_coded_gemv_splits(int IC, int OC, int njobs, int sm_count) {
     }
     if (njobs < 1) njobs = 1;
     const int nblk = IC / 128;
-    const long ctas = static_cast<long>(OC / 128) * njobs;
-    // Fill the GPU's resident-CTA slots (three CTAs of this kernel fit on an SM)
-    // without exceeding them: with every slot taken the blocks of a launch spread
-    // evenly over the SMs however they are placed, which also holds when a launch
-    // is scheduled early (programmatic dependent launch) into the slots the
-    // previous kernel frees one by one.  Measured on the dense 27B-class shapes this
-    // beats "two CTAs per SM" by 7 to 20 percent per projection.  At least two
-    // 128-channel blocks per split keep the copy pipeline busy.  Depends on the
-    // shape only.
-    const long smax = nblk >= 2 ? nblk / 2 : 1;
-    long s = 3L * sm_count / ctas;
+    const long units = static_cast<long>(OC / 128) * njobs;   // (row job, output block) pairs
+    // The persistent kernel keeps three CTAs per SM busy from a list of items; the list
+    // should be several times longer than the CTA count so that the CTAs finish together,
+    // while an item should still hold a few 128-channel blocks so that its fixed work
+    // (staging the rows, publishing a partial) stays small.  Depends on the shape only.
+    static const int per_slot = [] { const char* v = std::getenv("ESCHA_B200_SPLIT_ITEMS"); return v && *v ? std::atoi(v) : 4; }();
+    static const int min_blocks = [] { const char* v = std::getenv("ESCHA_B200_SPLIT_MIN_BLOCKS"); return v && *v ? std::atoi(v) : 4; }();
+    const long want = static_cast<long>(per_slot) * 3L * sm_count;
+    long s = (want + units - 1) / units;
+    const long smax = nblk >= min_blocks ? nblk / min_blocks : 1;
     if (s > smax) s = smax;
     if (s < 1) s = 1;
     return static_cast<int>(s);
@@ -343,7 +345,8 @@ int coded_projections_impl(const char* fn, const void* x, const void* const* x_p
                            const void* jobs, int njobs, int rows_per_job, int M, int E, int IC,
                            int K, const int* splits, float rs, void* workspace,
                            size_t workspace_bytes, void* stream,
-                           void* const* peer_out, int npeers, const int* out_ld, const int* out_col0) {
+                           void* const* peer_out, int npeers, const int* out_ld, const int* out_col0,
+                           const int* Ks = nullptr) {
     REQUIRE(npeers >= 0 && npeers <= escha::kMaxPeers, "%s: npeers=%d outside [0, %d]", fn,
             npeers, escha::kMaxPeers);
     if (npeers > 0) REQUIRE(peer_out != nullptr, "%s: peer_out is NULL", fn);
@@ -361,7 +364,8 @@ int coded_projections_impl(const char* fn, const void* x, const void* const* x_p
     escha::GemvMmaParams p{};
     int total_ocb = 0;
     for (int i = 0; i < nproj; ++i) {
-        if (int rc = check_shape(fn, K, IC, OC[i], 128)) return rc;
+        if (int rc = check_shape(fn, Ks ? Ks[i] : K, IC, OC[i], 128)) return rc;
+        p.prob[i].K = Ks ? Ks[i] : K;
         REQUIRE_PTR(code[i]);
         REQUIRE_PTR(out[i]);
         OPTIONAL_PTR(rout[i]);
@@ -442,11 +446,16 @@ int coded_projections_impl(const char* fn, const void* x, const void* const* x_p
         REQUIRE(workspace_bytes >= need, "%s: workspace of %zu bytes is smaller than the %zu needed",
                 fn, workspace_bytes, need);
         // the tail of the counter region belongs to escha_moe_route
-        REQUIRE(static_cast<size_t>(njobs) * total_ocb <= kMaxCounters - kRouteCounters,
+        REQUIRE(static_cast<size_t>(njobs) * total_ocb <= kSchedIndex,
                 "%s: %d jobs x %d output blocks exceed the %zu split-K counters", fn, njobs,
                 total_ocb, kMaxCounters);
         p.counters = static_cast<int32_t*>(workspace);
         p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + kCounterBytes);
+    }
+    // with a workspace the persistent kernel hands items out through a counter in it
+    if (workspace != nullptr && workspace_bytes >= kCounterBytes) {
+        REQUIRE_PTR(workspace);
+        p.sched = static_cast<int32_t*>(workspace) + kSchedIndex;
     }
     return cuda_result(escha::launch_gemv_mma(p, as_stream(stream)), fn);
 }
@@ -481,6 +490,24 @@ int escha_coded_projections_gather(const void* x, const void* const* x_proj, con
                                   code, rin, rout, out, OC, jobs, njobs, rows_per_job, M, E, IC, K,
                                   splits, rs, workspace, workspace_bytes, stream, peer_out, npeers,
                                   out_ld, out_col0);
+}
+
+int escha_coded_projections_mixed(const void* x, const void* const* x_proj, const void* x_up,
+                                  long x_stride, int x_row_div, int input_mode,
+                                  int nproj, const void* const* code, const float* const* rin,
+                                  const float* const* rout, void* const* out, const int* OC,
+                                  const int* Ks, const void* jobs, int njobs, int rows_per_job,
+                                  int M, int E, int IC, const int* splits, float rs,
+                                  void* workspace, size_t workspace_bytes,
+                                  void* const* peer_out, int npeers, const int* out_ld,
+                                  const int* out_col0, void* stream) {
+    REQUIRE(Ks != nullptr, "%s: Ks is NULL", __func__);
+    if (npeers > 0) REQUIRE(out_ld != nullptr && out_col0 != nullptr,
+                            "%s: out_ld and out_col0 are required with peers", __func__);
+    return coded_projections_impl(__func__, x, x_proj, x_up, x_stride, x_row_div, input_mode, nproj,
+                                  code, rin, rout, out, OC, jobs, njobs, rows_per_job, M, E, IC,
+                                  Ks[0], splits, rs, workspace, workspace_bytes, stream, peer_out,
+                                  npeers, out_ld, out_col0, Ks);
 }
 
 int escha_peer_barrier(int32_t* local_flags, int32_t* const* peer_flags, int rank, int nranks,
@@ -797,6 +824,14 @@ int escha_coded_gemm_tc_many(int n, const void* const* xhs, const void* const* c
     }
     return cuda_result(e, "escha_coded_gemm_tc_many");
 }
+
+int escha_coded_gemv_status(void) {
+    int st = 0;
+    if (escha::gemv_stream_status(&st) != cudaSuccess) return -1;
+    return st;
+}
+
+void escha_debug_gemv_stall(int on, unsigned limit) { escha::gemv_stream_test_stall(on, limit); }
 
 int escha_coded_gemm_tc_status(void) {
     int st = 0;

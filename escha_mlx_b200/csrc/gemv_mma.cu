@@ -428,17 +428,20 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
 
 }  // namespace
 
-// ESCHA_B200_PDL = off | wait (default) | prefetch: how launches use programmatic
-// dependent launch; read once per process.  "prefetch" lets a dense launch read its
-// weight stream before the previous kernel of the stream has finished, so it is only
-// for callers whose weights are not written by work still in flight.
+// ESCHA_B200_PDL = off | wait | prefetch (default): how launches use programmatic
+// dependent launch; read once per process.  "prefetch" lets a dense launch request the
+// first stages of its weight stream before the previous kernel of the stream has
+// finished.  Only kernels that signal their dependents early can be overlapped that
+// way, which in a stream of this library's launches means this library's own kernels,
+// and none of them writes a code stream; "wait" is for a caller whose own kernels do
+// both.
 static int pdl_mode() {
     static const int mode = [] {
         const char* v = std::getenv("ESCHA_B200_PDL");
-        if (!v) return static_cast<int>(kPdlWaitFirst);
+        if (!v) return static_cast<int>(kPdlPrefetch);
         if (!std::strcmp(v, "off")) return static_cast<int>(kPdlOff);
-        if (!std::strcmp(v, "prefetch")) return static_cast<int>(kPdlPrefetch);
-        return static_cast<int>(kPdlWaitFirst);
+        if (!std::strcmp(v, "wait")) return static_cast<int>(kPdlWaitFirst);
+        return static_cast<int>(kPdlPrefetch);
     }();
     return mode;
 }
@@ -458,7 +461,22 @@ size_t gemv_mma_part_floats(int njobs, int splits, int total_ocb, int rows_per_j
     return static_cast<size_t>(njobs) * splits * total_ocb * rows_per_job * 128u;
 }
 
+// ESCHA_B200_GEMV_KERNEL=grid keeps this file's one-CTA-per-(block, split) kernel; anything
+// else, or unset: the persistent kernel.  Read once per process.
+static bool use_grid_kernel() {
+    static const bool on = [] {
+        const char* v = std::getenv("ESCHA_B200_GEMV_KERNEL");
+        return v != nullptr && !std::strcmp(v, "grid");
+    }();
+    return on;
+}
+
 cudaError_t launch_gemv_mma(const GemvMmaParams& params, cudaStream_t st) {
+    if (!use_grid_kernel()) {
+        GemvMmaParams q = params;
+        q.pdl = pdl_mode();
+        return launch_gemv_stream(q, st);
+    }
     GemvMmaParams p = params;
     const int rows = p.rows_per_job;
     const int xrows = p.jobs ? rows : (p.M < rows ? p.M : rows);

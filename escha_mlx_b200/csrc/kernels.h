@@ -16,12 +16,12 @@ struct RowJob {
     int32_t rows[16];
 };
 
-constexpr int kMaxProblems = 4;
+constexpr int kMaxProblems = 8;
 constexpr int kMaxPeers = 7;   // other GPUs of an 8-GPU node
 
 // One projection inside a (possibly multi-projection) launch.  All projections
-// of a launch share the input rows, IC and K; each has its own stream, vectors
-// and output.
+// of a launch share the input rows; each has its own stream, vectors, output and,
+// in the persistent kernel, its own rate and input width.
 struct GemvProblem {
     const uint32_t* code;   // [E?, TK, TN, 8K]
     const __half* x;        // this projection's own input rows, or nullptr for the shared ones
@@ -31,6 +31,15 @@ struct GemvProblem {
     int OC;
     int ocb0;               // index of this projection's first 128-channel block in the grid
     int splits;             // split-K factor of this projection (<= GemvMmaParams::splits)
+    // Filled in by the launcher: rate and input width of this projection (the launch-wide
+    // K / IC when the caller left them 0), its first index in the launch's item list, and how
+    // many consecutive output blocks one item covers (they share one staging of the rows).
+    int K, IC, item0, opi;
+    // ceil(2^40 / d) for d = splits and d = output-block groups: item index -> (job, group,
+    // split) without integer division in the kernel (exact for indices below 2^24)
+    unsigned long long magic_s, magic_g;
+    int ngroups;
+    int bbase, brem;        // input blocks per split: bbase, the first brem splits one more
     // Output placement.  out_ld = elements between output rows (0: OC), out_col0 = this
     // projection's first column inside a row.  peer[0..npeer) are the SAME buffer mapped
     // from other GPUs: the epilogue stores its block there too, so that a split-N shard
@@ -72,6 +81,18 @@ struct GemvMmaParams {
     int input;                // GemvInput
     int xcb;                  // activation blocks staged per chunk (set by the launcher)
     int pdl;                  // GemvPdl (set by the launcher)
+    // Persistent kernel only (set by the launcher): length of the item list, code-ring depth
+    // and slot size in words, rows an activation buffer holds.
+    int total_items, nstages, slot_words, xrows;
+    // Two int32 in the caller's workspace (zero on entry, zero on exit): the next item index
+    // beyond the first wave, and the number of CTAs that ran out of items.  nullptr: items
+    // are taken by block stride instead.
+    int32_t* sched;
+    // Tries (of about a microsecond) a bounded wait makes before it gives up.
+    uint32_t wait_limit;
+    // Test hook: the producer announces its copies but does not issue them, so the decode
+    // warps' bounded waits run out and the kernel reports it through the status word.
+    int test_stall;
     float rs;
     // codebook constants 0x8FFF8FFF / 0x3B603B60, passed as run-time values so the
     // decode's (p & mask) ^ x stays a single three-input logic instruction
@@ -134,6 +155,14 @@ cudaError_t launch_gemv_ref(const __half* xh, const uint32_t* code, const int32_
                             float* part, int M, int IC, int OC, int K, int splits,
                             cudaStream_t st);
 cudaError_t launch_gemv_mma(const GemvMmaParams& p, cudaStream_t st);
+// The persistent form of the same kernel (gemv_stream.cu); launch_gemv_mma routes to it
+// unless ESCHA_B200_GEMV_KERNEL=grid.
+cudaError_t launch_gemv_stream(const GemvMmaParams& p, cudaStream_t st);
+// Status word of the persistent kernel: nonzero after a bounded wait gave up; cleared on read.
+cudaError_t gemv_stream_status(int* host_status);
+// Test hook: from now on launches make their producers announce copies without issuing
+// them and give every bounded wait `limit` tries (0 restores normal operation).
+void gemv_stream_test_stall(int on, unsigned limit);
 cudaError_t launch_group_rows(const int32_t* row_expert, int m, int E, int R, RowJob* jobs,
                               int njobs_cap, int32_t* njobs_out, cudaStream_t st);
 cudaError_t launch_jobs_from_groups(const int32_t* rows_idx, const int32_t* group_expert,

@@ -243,19 +243,22 @@ def _joint_prefill(linears) -> bool:
 
 
 def project_many(linears, x: torch.Tensor):
-    """Evaluate up to four coded projections of the same input (Q/K/V, gate/up) in
-    as few launches as their rates allow.  Outputs equal ``[lin(x) for lin in
-    linears]`` bit for bit: every projection keeps the split factor and the
-    summation order it has when called alone."""
+    """Evaluate up to eight coded projections of the same input (Q/K/V, gate/up, or
+    everything that reads one hidden state) in one launch at decode batch sizes,
+    whatever their rates.  Outputs equal ``[lin(x) for lin in linears]`` bit for
+    bit: every projection keeps the split factor and the summation order it has
+    when called alone."""
     linears = list(linears)
     shape = x.shape
     rows = x.reshape(-1, shape[-1])
     first = linears[0]
+    mixed = any(lin.K != first.K for lin in linears)
     joint = (
-        1 < len(linears) <= 4
+        1 < len(linears) <= (msl.MAX_PROJECTIONS if first._single_launch(rows.shape[0]) else 4)
         and msl.gemv_family() == "mma"
         and all(lin._fused_had for lin in linears)
-        and all(lin._w.IC == rows.shape[-1] and lin.K == first.K for lin in linears)
+        and all(lin._w.IC == rows.shape[-1] for lin in linears)
+        and (not mixed or msl.mixed_rates_supported())
         and rows.dtype == torch.float16
     )
     same_input = (1 < len(linears) <= 4 and rows.dtype == torch.float16
@@ -276,12 +279,12 @@ def project_many(linears, x: torch.Tensor):
     ws = [lin._w for lin in linears]
     codes, routs, ocs = [w.code for w in ws], [w.rout for w in ws], [w.OC for w in ws]
     if first._single_launch(rows.shape[0]):
-        outs = msl.coded_projections(rows, codes, [w.rin for w in ws], routs, first.K, first._w.IC,
-                                     ocs, input_mode=msl.INPUT_RAW, rs=RS)
+        outs = msl.coded_projections(rows, codes, [w.rin for w in ws], routs, [w.K for w in ws],
+                                     first._w.IC, ocs, input_mode=msl.INPUT_RAW, rs=RS)
     else:
         xhs = msl.dense_scaled_had_many(rows, [w.rin for w in ws], RS)
-        outs = msl.coded_projections(xhs[0], codes, None, routs, first.K, first._w.IC, ocs,
-                                     rs=RS, xs=xhs)
+        outs = msl.coded_projections(xhs[0], codes, None, routs, [w.K for w in ws], first._w.IC,
+                                     ocs, rs=RS, xs=xhs)
     return [lin._finish(y, shape, x.dtype) for lin, y in zip(linears, outs)]
 
 

@@ -294,11 +294,11 @@ def _gemv_mma_dense(xh, code, rout, K, IC, OC, splits, rs=RS):
     njobs = (m + rows_per_job - 1) // rows_per_job
     out = torch.empty((m, OC), dtype=torch.float32 if rout is None else torch.float16,
                       device=xh.device)
-    ws, nbytes = None, 0
-    if s > 1:
-        nbytes = int(lib.escha_coded_gemv_workspace_bytes(njobs, OC, s, rows_per_job))
-        ws = workspaces.get(nbytes, xh.device)
-        nbytes = ws.numel()
+    # always a workspace: besides the split-K scratch it holds the counter the persistent
+    # kernel hands its work items out through
+    nbytes = int(lib.escha_coded_gemv_workspace_bytes(njobs, OC, s, rows_per_job))
+    ws = workspaces.get(nbytes, xh.device)
+    nbytes = ws.numel()
     check(lib.escha_coded_gemv(ptr(xh, torch.float16), ptr(code),
                                ptr(rout, torch.float32) if rout is not None else None, m, IC, OC,
                                K, s, float(rs), ptr(ws), ctypes.c_size_t(nbytes), ptr(out),
@@ -307,6 +307,16 @@ def _gemv_mma_dense(xh, code, rout, K, IC, OC, splits, rs=RS):
 
 
 INPUT_TRANSFORMED, INPUT_RAW, INPUT_SWIGLU = 0, 1, 2
+
+#: Projections one launch of the tensor-core kernel can hold.
+MAX_PROJECTIONS = 8
+
+
+def mixed_rates_supported() -> bool:
+    """Projections of different rates share a launch only in the persistent kernel
+    (the default; ``ESCHA_B200_GEMV_KERNEL=grid`` selects the one-CTA-per-block form)."""
+    return os.environ.get("ESCHA_B200_GEMV_KERNEL") != "grid"
+
 
 #: Up to this many rows the dense modules fuse the input transform into the GEMV
 #: launch (every output block's CTA redoes it for its slice of the input, which is
@@ -321,8 +331,9 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
                       rs: float = RS, rows_per_job: int = 8, outs=None,
                       policy_rows: int | None = None, xs=None, rows: int | None = None,
                       x_stride: int | None = None, x_row_div: int = 1, gather=None):
-    """One launch of the tensor-core kernel for 1..4 projections of the same rows.
+    """One launch of the tensor-core kernel for 1..8 projections of the same rows.
 
+    ``K`` is the rate of all of them, or a sequence with one rate per projection.
     ``codes``/``rins``/``routs``/``OCs`` are equal-length sequences (rins may be
     None for ``INPUT_TRANSFORMED``; a rout of None yields that projection's f32
     mid instead of its f16 output).  ``input_mode`` selects what ``x`` is: the
@@ -346,6 +357,11 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
     m = x.shape[0] if rows is None else rows
     if rins is None:
         rins = [None] * n
+    Ks = [int(k) for k in K] if isinstance(K, (list, tuple)) else [int(K)] * n
+    if len(Ks) != n:
+        raise ValueError(f"{len(Ks)} rates for {n} projections")
+    mixed = len(set(Ks)) > 1
+    K = Ks[0]
     dense = jobs is None
     pr = m if policy_rows is None else policy_rows
     total_oc = sum(OCs)
@@ -365,11 +381,9 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
     if outs is None and gather is None:
         outs = [torch.empty((m, oc), dtype=torch.float32 if ro is None else torch.float16,
                             device=x.device) for oc, ro in zip(OCs, routs)]
-    ws, nbytes = None, 0
-    if s > 1:
-        nbytes = int(lib.escha_coded_gemv_workspace_bytes(njobs, total_oc, s, rows_per_job))
-        ws = workspaces.get(nbytes, x.device)
-        nbytes = ws.numel()
+    nbytes = int(lib.escha_coded_gemv_workspace_bytes(njobs, total_oc, s, rows_per_job))
+    ws = workspaces.get(nbytes, x.device)
+    nbytes = ws.numel()
     vp = ctypes.c_void_p * n
 
     def table(ts, dtype=None):
@@ -386,6 +400,25 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
         x_stride = IC if x.shape[0] == 1 else x.stride(0)
     if x.stride(-1) != 1 or (x_up is not None and x_up.stride(-1) != 1):
         raise ValueError("activation rows must be contiguous along the channel axis")
+    if mixed:
+        locs, npeers, flat = None, 0, []
+        if gather is not None:
+            locs = [g[0].local for g in gather]
+            npeers = len(gather[0][0].peer_ptrs())
+            flat = [p for g in gather for p in g[0].peer_ptrs()]
+        dst = outs if gather is None else locs
+        check(lib.escha_coded_projections_mixed(
+            x_ptr, None if xs is None else table(xs, torch.float16), up_ptr,
+            x_stride, x_row_div, input_mode, n, table(codes), table(rins, torch.float32),
+            table(routs, torch.float32), table(dst), (ctypes.c_int * n)(*OCs),
+            (ctypes.c_int * n)(*Ks),
+            None if dense else ptr(jobs, torch.int32), njobs, rows_per_job, m, E, IC,
+            (ctypes.c_int * n)(*per), float(rs), ptr(ws), ctypes.c_size_t(nbytes),
+            (ctypes.c_void_p * len(flat))(*flat) if flat else None, npeers,
+            None if gather is None else (ctypes.c_int * n)(*[t.shape[-1] for t in locs]),
+            None if gather is None else (ctypes.c_int * n)(*[int(g[1]) for g in gather]),
+            stream()))
+        return dst
     if gather is not None:
         locs = [g[0].local for g in gather]
         npeers = len(gather[0][0].peer_ptrs())
@@ -425,11 +458,11 @@ def coded_gemv_jobs(xh: torch.Tensor, code_u32: torch.Tensor, jobs: torch.Tensor
     if out is None:
         out = torch.empty((m, OC), dtype=torch.float32 if rout is None else torch.float16,
                           device=xh.device)
-    ws, nbytes = None, 0
-    if s > 1:
-        nbytes = int(lib.escha_coded_gemv_workspace_bytes(njobs, OC, s, rows_per_job))
-        ws = workspaces.get(nbytes, xh.device)
-        nbytes = ws.numel()
+    # always a workspace: besides the split-K scratch it holds the counter the persistent
+    # kernel hands its work items out through
+    nbytes = int(lib.escha_coded_gemv_workspace_bytes(njobs, OC, s, rows_per_job))
+    ws = workspaces.get(nbytes, xh.device)
+    nbytes = ws.numel()
     check(lib.escha_coded_gemv_jobs(ptr(xh, torch.float16), ptr(code_u32),
                                     ptr(rout, torch.float32) if rout is not None else None,
                                     ptr(jobs, torch.int32), njobs, rows_per_job, m, E, IC, OC, K, s,

@@ -374,6 +374,41 @@ int escha_coded_gemm_tc_many(int n, const void *const *xhs, const void *const *c
  * since the library was loaded; synchronises the device.  For tests and diagnostics. */
 int escha_coded_gemm_tc_status(void);
 
+/* escha_coded_projections[_gather] for projections of DIFFERENT rates: Ks[i] in {2, 3} is
+ * projection i's bits per weight; up to 8 projections of the same input rows and IC share the
+ * launch (with npeers == 0, peer_out / out_ld / out_col0 may be NULL).  Every projection keeps
+ * the split factor it has when launched alone, so a joint launch changes no output bit.  The
+ * reference fuses the projections that share an input at module level (_FusedAttention q/k/v,
+ * _FusedMLP gate/up, escha_mlx/models/qwen3_5.py:63-198; pair kernels msl.py:1880-1950) but
+ * needs one kernel name per rate; here one persistent launch walks a work list over all of
+ * them, so e.g. 2-bit attention projections and 3-bit MLP projections of one hidden state
+ * cost one ramp-up and one tail. */
+int escha_coded_projections_mixed(const void *x, const void *const *x_proj, const void *x_up,
+                                  long x_stride, int x_row_div, int input_mode, int nproj,
+                                  const void *const *code, const float *const *rin,
+                                  const float *const *rout, void *const *out, const int *OC,
+                                  const int *Ks, const void *jobs, int njobs, int rows_per_job,
+                                  int M, int E, int IC, const int *splits, float rs,
+                                  void *workspace, size_t workspace_bytes,
+                                  void *const *peer_out, int npeers, const int *out_ld,
+                                  const int *out_col0, void *stream);
+
+/* 0 if no coded GEMV launch (escha_coded_gemv, escha_coded_projections[_gather],
+ * escha_coded_gemv_jobs, escha_coded_gemv_static) on the current device has given up a
+ * bounded wait since the last call; reading clears it; synchronises the device.  The
+ * reference's kernels cannot report such a condition (msl.py launches have no status);
+ * here every wait inside a kernel is bounded and a kernel that gives up returns, leaves
+ * its outputs undefined and raises this word.  After a nonzero status zero the first
+ * 1 MiB of the workspace the launch used before using it again. */
+int escha_coded_gemv_status(void);
+
+/* Test hook for the status path above, no counterpart in the reference.  on != 0: from
+ * now on GEMV launches announce their weight copies without issuing them and give every
+ * bounded wait `limit` tries of about a microsecond, so the waits run out, the kernel
+ * returns and escha_coded_gemv_status() reports it; nothing faults and the device stays
+ * usable.  on == 0 restores normal operation. */
+void escha_debug_gemv_stall(int on, unsigned limit);
+
 #ifdef __cplusplus
 }
 #endif
