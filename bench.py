@@ -556,8 +556,7 @@ def main() -> None:
     # (q/k/v, o, gate, up all read the step input: one launch; SwiGLU + down: a second);
     # "model" keeps the four launches a transformer layer with attention between q/k/v and o
     # needs (q/k/v | o | gate/up | SwiGLU + down)
-    joint_launches = (args.group == "layer" and world == 1 and M <= msl.FUSE_INPUT_MAX_ROWS
-                      and msl.mixed_rates_supported())
+    joint_launches = args.group == "layer" and world == 1 and M <= msl.FUSE_INPUT_MAX_ROWS
 
     def layer_step(layer, x, bufs=None):
         if world > 1 and (pg is None or tc_shards):
@@ -593,7 +592,9 @@ def main() -> None:
     # launches of this library's kernels per step: fused small-batch path = q/k/v, o,
     # gate/up, swiglu+down (4); larger batches add the separate input transforms
     if M <= msl.FUSE_INPUT_MAX_ROWS:
-        launches_per_step = (2 if joint_launches else 4) if world == 1 else 8   # + 4 peer barriers
+        # joint: one launch for all rates (persistent kernel) or one per rate
+        per_step = (2 if msl.mixed_rates_supported() else 3) if joint_launches else 4
+        launches_per_step = per_step if world == 1 else 8   # + 4 peer barriers
     elif msl.use_prefill_kernel(M) and (world == 1 or tc_shards):
         # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), the tcgen05 GEMMs,
         # and a plane sum + output transform for every projection split more than 4 ways along K

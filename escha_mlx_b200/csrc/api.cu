@@ -321,6 +321,21 @@ int escha_coded_gemv_splits(int IC, int OC, int njobs, int sm_count) {
     if (njobs < 1) njobs = 1;
     const int nblk = IC / 128;
     const long units = static_cast<long>(OC / 128) * njobs;   // (row job, output block) pairs
+    static const bool grid_kernel = [] {
+        const char* v = std::getenv("ESCHA_B200_GEMV_KERNEL");
+        return v == nullptr || std::strcmp(v, "stream") != 0;
+    }();
+    if (grid_kernel) {
+        // One CTA per (output block, split), one wave: fill the GPU's resident-CTA slots
+        // (three CTAs of the kernel fit on an SM) without exceeding them, at least two
+        // 128-channel blocks per split.  Measured on the dense 27B-class shapes this beats
+        // "two CTAs per SM" by 7 to 20 percent per projection.  Depends on the shape only.
+        const long smax = nblk >= 2 ? nblk / 2 : 1;
+        long s = 3L * sm_count / units;
+        if (s > smax) s = smax;
+        if (s < 1) s = 1;
+        return static_cast<int>(s);
+    }
     // The persistent kernel keeps three CTAs per SM busy from a list of items; the list
     // should be several times longer than the CTA count so that the CTAs finish together,
     // while an item should still hold a few 128-channel blocks so that its fixed work
@@ -826,9 +841,9 @@ int escha_coded_gemm_tc_many(int n, const void* const* xhs, const void* const* c
 }
 
 int escha_coded_gemv_status(void) {
-    int st = 0;
-    if (escha::gemv_stream_status(&st) != cudaSuccess) return -1;
-    return st;
+    int a = 0, b = 0;
+    if (escha::gemv_stream_status(&a) != cudaSuccess || escha::gemv_mma_status(&b) != cudaSuccess) return -1;
+    return a ? a : b;
 }
 
 void escha_debug_gemv_stall(int on, unsigned limit) { escha::gemv_stream_test_stall(on, limit); }

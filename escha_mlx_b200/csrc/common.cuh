@@ -361,6 +361,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// The same with the bound as a parameter: `limit` rounds of 32 tries (a try blocks in
+// hardware for some tens of cycles by itself).
+__device__ __forceinline__ bool mbar_wait_n(uint32_t bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t it = 0; it < limit; ++it)
+#pragma unroll 1
+        for (int k = 0; k < 32; ++k)
+            if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
 // global -> shared bulk copy (16-byte aligned addresses, size a multiple of 16),
 // completion signalled on an mbarrier of this CTA.  No multicast.
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
@@ -371,6 +380,12 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
 }
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Arrive at a named barrier without waiting (the waiting side uses named_barrier_sync with
+// the same thread count).
+__device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t threads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // mma.sync m16n8k16, f16 x f16 -> f32 accumulate.

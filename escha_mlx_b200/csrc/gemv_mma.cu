@@ -152,6 +152,7 @@ __device__ int g_gemv_status = 0;
 
 constexpr int kConsumerThreads = 256;   // 8 decode warps
 constexpr int kThreads = kConsumerThreads + 32;  // + 1 producer warp
+constexpr uint32_t kBarSlot0 = 2;       // named barriers 2..7: the ring's slots (1: the decode warps' own)
 
 // SUM = false (the default): each weight is rounded to binary16 exactly as the format
 // defines it, w = f16(lo) + f16(hi), kept as (w, w) against (x, 0).  SUM = true (opt-in,
@@ -169,7 +170,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     extern __shared__ __align__(128) uint32_t smem[];
     uint32_t* const s_code = smem;                    // [NS][8 kt][8 tiles][WPT]
     uint32_t* const s_x = smem + NS * STAGE_WORDS;    // [rows + 1][XS] as (x, 0) words
-    __shared__ __align__(8) uint64_t s_full[NS], s_empty[NS];
+    __shared__ __align__(8) uint64_t s_full[NS];
     __shared__ int s_rows[16];
     __shared__ int s_last;
 
@@ -220,12 +221,11 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     const uint32_t nb = bbase + (split < brem ? 1u : 0u);
 
     const uint32_t tile_row_words = TN * WPT;  // words between kt and kt+1 in the stream
-    const uint32_t full0 = smem_u32(s_full), empty0 = smem_u32(s_empty);
+    const uint32_t full0 = smem_u32(s_full);
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < NS; ++s) {
             mbar_init(full0 + 8u * s, 1u);    // the producer's arrive.expect_tx
-            mbar_init(empty0 + 8u * s, 8u);   // one arrival per decode warp
         }
         mbar_fence_init();
     }
@@ -240,13 +240,13 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
         const uint32_t dst0 = smem_u32(s_code) + lane * (ROW_WORDS * 4u);
         for (uint32_t i = 0; i < nb; ++i) {
             const uint32_t slot = i % NS;
-            if (i >= NS && !mbar_wait(empty0 + 8u * slot, ((i / NS) - 1u) & 1u)) {
-                if (lane == 0) atomicExch(&g_gemv_status, 1);
-                return;
-            }
+            // The slot is free once all eight decode warps have arrived at its barrier.  The
+            // producer is parked there by the hardware: a polling wait would take issue
+            // slots on its sub-partition, and the slowest sub-partition paces the CTA.
+            if (i >= NS) named_barrier_sync(kBarSlot0 + slot, kThreads);
             if (lane == 0) mbar_arrive_expect_tx(full0 + 8u * slot, STAGE_WORDS * 4u);
             __syncwarp();
-            if (lane < 8)
+            if (lane < 8 && !p.test_stall)
                 bulk_copy_g2s(dst0 + slot * (STAGE_WORDS * 4u), grow, ROW_WORDS * 4u,
                               full0 + 8u * slot);
             grow += static_cast<size_t>(8u) * tile_row_words;
@@ -286,14 +286,16 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
 
     bool ok = true;
     uint32_t slot = 0, phase = 0;
-    for (uint32_t c0 = 0; c0 < nb && ok; c0 += XCB) {
+    for (uint32_t c0 = 0; c0 < nb; c0 += XCB) {
         const uint32_t cnt = min(XCB, nb - c0);
         named_barrier_sync(1, kConsumerThreads);
         stage_activations(p, xsrc, rin, s_rows, nrows, b0 + c0, cnt, s_x, XS, tid,
                           SUM ? 0x10001u : 1u);
         named_barrier_sync(1, kConsumerThreads);
         for (uint32_t cb = 0; cb < cnt; ++cb) {
-            if (!mbar_wait(full0 + 8u * slot, phase)) { ok = false; break; }
+            // a wait that gives up is recorded; the warp stops waiting but keeps walking the
+            // stages and arriving everywhere, so that nobody in the CTA is left alone at a barrier
+            if (ok && !mbar_wait_n(full0 + 8u * slot, phase, p.wait_limit)) ok = false;
             const uint32_t* wa = wa0 + slot * STAGE_WORDS;
             const uint32_t* wb = wb0 + slot * STAGE_WORDS;
             const uint32_t* xr[MT];
@@ -315,17 +317,12 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
                     mma16816(dB[mt], a[1], a[5], a[3], a[7], b.z, b.w);
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8u * slot);  // this warp is done with the slot
+            named_barrier_arrive(kBarSlot0 + slot, kThreads);  // this warp is done with the slot
             if (++slot == NS) { slot = 0; phase ^= 1u; }
         }
     }
-    if (!ok) {
-        // a wait gave up: record it, give copies already in flight time to land, leave
-        if (lane == 0) atomicExch(&g_gemv_status, 2);
-        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
-        return;
-    }
+    // what this CTA computed after a give-up is void; the status word says so
+    if (!ok && lane == 0) atomicExch(&g_gemv_status, 2);
     named_barrier_sync(1, kConsumerThreads);
 
     // accumulators -> shared [ROWS][128] (aliases the drained code ring)
@@ -456,28 +453,51 @@ static bool weight_sum_in_tensor_core() {
     return on;
 }
 
+cudaError_t gemv_mma_status(int* host_status) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(host_status, g_gemv_status, sizeof(int));
+    if (e != cudaSuccess) return e;
+    if (*host_status != 0) e = cudaMemcpyToSymbol(g_gemv_status, &zero, sizeof(int));
+    return e;
+}
+
 size_t gemv_mma_part_floats(int njobs, int splits, int total_ocb, int rows_per_job) {
     if (splits <= 1) return 0;
     return static_cast<size_t>(njobs) * splits * total_ocb * rows_per_job * 128u;
 }
 
-// ESCHA_B200_GEMV_KERNEL=grid keeps this file's one-CTA-per-(block, split) kernel; anything
-// else, or unset: the persistent kernel.  Read once per process.
-static bool use_grid_kernel() {
+// ESCHA_B200_GEMV_KERNEL=stream selects the persistent kernel (gemv_stream.cu) for every
+// launch; otherwise this file's one-CTA-per-(block, split) kernel runs everything it can:
+// launches whose projections all have one rate and that do not ask for the shared-memory
+// table.  Read once per process.
+static bool prefer_stream_kernel() {
     static const bool on = [] {
         const char* v = std::getenv("ESCHA_B200_GEMV_KERNEL");
-        return v != nullptr && !std::strcmp(v, "grid");
+        return v != nullptr && !std::strcmp(v, "stream");
+    }();
+    return on;
+}
+static bool table_mode() {
+    static const bool on = [] {
+        const char* s = std::getenv("ESCHA_B200_LUT_STATES");
+        if (s && *s) return std::atoi(s) >= 2;
+        const char* l = std::getenv("ESCHA_MLX_LUT");
+        return l != nullptr && *l && std::strcmp(l, "0") != 0;
     }();
     return on;
 }
 
 cudaError_t launch_gemv_mma(const GemvMmaParams& params, cudaStream_t st) {
-    if (!use_grid_kernel()) {
+    bool mixed = false;
+    for (int i = 1; i < params.nprob; ++i)
+        if (params.prob[i].K && params.prob[i].K != params.prob[0].K) mixed = true;
+    if (prefer_stream_kernel() || table_mode() || mixed) {
         GemvMmaParams q = params;
         q.pdl = pdl_mode();
         return launch_gemv_stream(q, st);
     }
     GemvMmaParams p = params;
+    gemv_test_hooks(&p.test_stall, &p.wait_limit);
     const int rows = p.rows_per_job;
     const int xrows = p.jobs ? rows : (p.M < rows ? p.M : rows);
     p.xcb = x_chunk_blocks(xrows);

@@ -251,10 +251,6 @@ __device__ __forceinline__ void resolve_item(const GemvMmaParams& p, int id, Ite
 constexpr uint32_t kBarThreads = (kDecodeWarps + 1) * 32;
 constexpr uint32_t kBarSlot0 = 1;    // ids 1..8: code ring slots
 constexpr uint32_t kBarAcc0 = 9;     // ids 9, 10: accumulator buffers
-__device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t threads) {
-    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
 // mbarrier arrive by lane 0 without a divergent branch
 __device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, uint32_t lane) {
     asm volatile("{ .reg .pred p; setp.eq.u32 p, %1, 0; @p mbarrier.arrive.shared::cta.b64 _, [%0]; }"
@@ -399,7 +395,12 @@ __device__ __forceinline__ bool item_block(const GemvMmaParams& p, Shared& sh, c
             if (live && ok && !mbar_try_wait(full0 + rp.slot8, rp.phase) &&
                 !mbar_wait_slow(full0 + rp.slot8, rp.phase, limit)) ok = false;
             decode_block<K, MT, NLUT>(wa0 + rp.slot_off, wb0 + rp.slot_off, xr, dA, dB, lc, muls, hmask, hxor, lut);
+#ifdef FEEDER_SPIN
+            __syncwarp();
+            if (live) mbar_arrive_lane0(smem_u32(sh.empty) + rp.slot8, lane);
+#else
             if (live) named_barrier_arrive(kBarSlot0 + rp.slot, kBarThreads);   // done with the stage
+#endif
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) xr[mt] += 128;
             rp.slot_off += SLOT;
@@ -479,7 +480,11 @@ gemv_stream_kernel(const __grid_constant__ GemvMmaParams p) {
         // free right now and reports whether it did.
         auto issue_stage = [&](const uint32_t* grow, uint32_t row_bytes) {
             // the slot is free once all eight decode warps have arrived at its barrier
+#ifdef FEEDER_SPIN
+            if (lap > 0 && !mbar_wait(empty0 + 8u * rslot, (lap - 1u) & 1u)) ok = false;
+#else
             if (lap > 0) named_barrier_sync(kBarSlot0 + rslot, kBarThreads);
+#endif
             if (lane == 0) mbar_arrive_expect_tx(full0 + 8u * rslot, 8u * row_bytes);
             __syncwarp();
             if (lane < 8 && p.test_stall != 1)
@@ -776,6 +781,11 @@ int env_int(const char* name, int dflt) {
 void gemv_stream_test_stall(int on, unsigned limit) {
     g_test_stall = on;
     g_test_limit = limit;
+}
+
+void gemv_test_hooks(int* stall, unsigned* limit) {
+    *stall = g_test_stall;
+    *limit = g_test_limit ? g_test_limit : (1u << 21);
 }
 
 cudaError_t gemv_stream_status(int* host_status) {

@@ -163,6 +163,10 @@ cudaError_t gemv_stream_status(int* host_status);
 // Test hook: from now on launches make their producers announce copies without issuing
 // them and give every bounded wait `limit` tries (0 restores normal operation).
 void gemv_stream_test_stall(int on, unsigned limit);
+// the current values of that hook (limit: the default when the hook is off)
+void gemv_test_hooks(int* stall, unsigned* limit);
+// Status word of the one-CTA-per-block kernel (gemv_mma.cu), same convention.
+cudaError_t gemv_mma_status(int* host_status);
 cudaError_t launch_group_rows(const int32_t* row_expert, int m, int E, int R, RowJob* jobs,
                               int njobs_cap, int32_t* njobs_out, cudaStream_t st);
 cudaError_t launch_jobs_from_groups(const int32_t* rows_idx, const int32_t* group_expert,

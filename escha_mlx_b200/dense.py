@@ -253,6 +253,15 @@ def project_many(linears, x: torch.Tensor):
     rows = x.reshape(-1, shape[-1])
     first = linears[0]
     mixed = any(lin.K != first.K for lin in linears)
+    if (mixed and not msl.mixed_rates_supported() and first._single_launch(rows.shape[0])
+            and msl.gemv_family() == "mma"):
+        # one launch per rate: the projections of each rate together
+        outs: dict[int, torch.Tensor] = {}
+        for k in sorted({lin.K for lin in linears}):
+            idx = [i for i, lin in enumerate(linears) if lin.K == k]
+            for i, y in zip(idx, project_many([linears[i] for i in idx], x)):
+                outs[i] = y
+        return [outs[i] for i in range(len(linears))]
     joint = (
         1 < len(linears) <= (msl.MAX_PROJECTIONS if first._single_launch(rows.shape[0]) else 4)
         and msl.gemv_family() == "mma"

@@ -313,9 +313,11 @@ MAX_PROJECTIONS = 8
 
 
 def mixed_rates_supported() -> bool:
-    """Projections of different rates share a launch only in the persistent kernel
-    (the default; ``ESCHA_B200_GEMV_KERNEL=grid`` selects the one-CTA-per-block form)."""
-    return os.environ.get("ESCHA_B200_GEMV_KERNEL") != "grid"
+    """Whether projections of different rates should share a launch: they can (the
+    persistent kernel takes any mix), but by default a mixed group is split by rate and
+    each part runs on the one-CTA-per-block kernel, which measures faster per launch;
+    ``ESCHA_B200_GEMV_KERNEL=stream`` keeps the group together."""
+    return os.environ.get("ESCHA_B200_GEMV_KERNEL") == "stream"
 
 
 #: Up to this many rows the dense modules fuse the input transform into the GEMV

@@ -63,15 +63,13 @@ def test_pure_helpers():
     from escha_mlx_b200._lib import lib
     assert lib.escha_moe_jobs_bound(512, 256, 8) == (512 + 256 * 7) // 8
     assert lib.escha_moe_jobs_bound(8, 256, 8) == 8
-    # the item list should be about four times the 444 resident CTAs of a 148-SM part, an item
-    # at least four 128-channel blocks: 4096x4096 has 32 output blocks of 32 input blocks
-    assert lib.escha_coded_gemv_splits(4096, 4096, 1, 148) == 8
-    assert lib.escha_coded_gemv_splits(5120, 17408, 1, 148) == 10
-    assert lib.escha_coded_gemv_splits(17408, 5120, 1, 148) == 34
-    # wide enough that the output blocks alone make the list: no split
-    assert lib.escha_coded_gemv_splits(5120, 17408 * 16, 1, 148) == 1
-    # never fewer than four 128-channel blocks per split
-    assert lib.escha_coded_gemv_splits(1024, 128, 1, 148) == 2
-    assert lib.escha_coded_gemv_splits(512, 128, 1, 148) == 1
+    # 4096x4096: 32 output blocks -> floor(3*148/32) = 13 splits fill a 148-SM part's
+    # 444 resident-CTA slots without exceeding them
+    assert lib.escha_coded_gemv_splits(4096, 4096, 1, 148) == 13
+    assert lib.escha_coded_gemv_splits(5120, 17408, 1, 148) == 3
+    assert lib.escha_coded_gemv_splits(17408, 5120, 1, 148) == 11
+    assert lib.escha_coded_gemv_splits(5120, 17408 * 4, 1, 148) == 1
+    # never fewer than two 128-channel blocks per split
+    assert lib.escha_coded_gemv_splits(512, 128, 1, 148) == 2
     assert lib.escha_coded_gemv_workspace_bytes(1, 4096, 1, 8) == 0
     assert lib.escha_coded_gemv_workspace_bytes(1, 4096, 4, 8) == (1 << 20) + 4 * 32 * 8 * 128 * 4
