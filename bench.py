@@ -394,37 +394,96 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
         os._exit(0)     # see the note at the end of main()
 
 
-def moe_leg(device, tokens: int, replays: int = 10) -> dict:
+def moe_legs(device, token_counts=(1, 8, 64), replays: int = 10) -> dict:
     """Second half of the headline metric inside the default run: one 35B-A3B-class MoE
-    decode layer at `tokens` tokens (the `--workload moe` measurement, shortened)."""
+    decode layer at 1, 8 and 64 tokens (the `--workload moe` measurement, shortened): per
+    token count the time per layer, the bytes of the distinct routed experts it streams and
+    that rate as a fraction of the measured HBM peak."""
     import torch
     from escha_mlx_b200 import graphs, workloads
     cfg = workloads.MOE_35B
     layers = workloads.moe_stack(MOE_LAYERS, device)
-    gen = torch.Generator(device=device)
-    gen.manual_seed(99)
-    x0 = torch.randn((tokens, cfg["hidden"]), device=device, generator=gen).half()
+    peak, _ = measured_peak_gbs()
+    out = {"metric": "MoE decode-layer tokens/s", "layers_resident": MOE_LAYERS,
+           "workload": "moe35b_layer_decode_t{1,8,64} (see --workload moe)"}
+    for tokens in token_counts:
+        gen = torch.Generator(device=device)
+        gen.manual_seed(99)
+        x0 = torch.randn((tokens, cfg["hidden"]), device=device, generator=gen).half()
 
-    def pass_(x):
-        out = None
-        for layer in layers:
-            out = layer(x)
-        return out
-    g = graphs.GraphedCall(pass_, [x0])
-    for _ in range(3):
-        g.replay()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(replays):
-        g.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / (replays * MOE_LAYERS)
-    g.close()
-    return {"metric": "MoE decode-layer tokens/s", "tokens": tokens, "us_per_layer": us,
-            "tokens_per_s": tokens / (us * 1e-6), "layers_resident": MOE_LAYERS,
-            "workload": f"moe35b_layer_decode_t{tokens} (see --workload moe)"}
+        def pass_(x):
+            y = None
+            for layer in layers:
+                y = layer(x)
+            return y
+        with torch.no_grad():
+            routed = sum(layer.routed_experts(x0) for layer in layers)
+        g = graphs.GraphedCall(pass_, [x0])
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (replays * MOE_LAYERS)
+        g.close()
+        lay = layers[0]
+        code_bytes = routed * lay.expert_bytes / MOE_LAYERS
+        touched = code_bytes + lay.int8_bytes + lay.router_bytes
+        out[f"t{tokens}"] = {"us_per_layer": us, "tokens_per_s": tokens / (us * 1e-6),
+                             "distinct_expert_code_bytes_per_layer": code_bytes,
+                             "touched_gb_per_s": touched / (us * 1e-6) / 1e9,
+                             "frac": touched / (us * 1e-6) / 1e9 / peak}
+    return out
+
+
+def c1_leg(device, reps: int = 5) -> dict:
+    """The single dense coded projection of the reference's own gate (4096x4096, 2-bit, one
+    row; escha_mlx bench/p0_gates.py:111-118): 4 MiB of code, below launch latency and smaller
+    than L2, so two figures, both from CUDA-graph replays of 128 back-to-back launches:
+    HBM-resident (64 distinct weight buffers = 256 MiB rotated, every launch misses L2) and
+    L2-resident (one buffer)."""
+    import torch
+    from escha_mlx_b200 import dense, graphs
+    IC = OC = 4096
+    K, nbuf, launches = 2, 64, 128
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4096)
+
+    def vec(n):
+        scale = torch.randn(n, device=device, generator=gen).abs() * 0.02 + 1e-3
+        sign = torch.randint(0, 2, (n,), device=device, generator=gen).float() * 2 - 1
+        return (scale * sign).half().float()
+    rin, rout = vec(IC), vec(OC)
+    lins = [dense.EschaLinear(dense.EschaWeight.from_device(
+        torch.randint(-2**31, 2**31 - 1, (IC // 16, OC // 16, 8 * K), dtype=torch.int32,
+                      device=device, generator=gen), rin, rout)) for _ in range(nbuf)]
+    x = torch.randn((1, IC), device=device, generator=gen).half()
+    peak, _ = measured_peak_gbs()
+    out = {"workload": "dense_c1_4096x4096_k2_b1", "code_bytes": IC * OC * K // 8,
+           "launches_per_replay": launches}
+    for name, pick in (("hbm_resident", lambda i: lins[i % nbuf]), ("l2_resident", lambda i: lins[0])):
+        g = graphs.GraphedCall(lambda xx, pick=pick: [pick(i)(xx) for i in range(launches)][-1], [x])
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3 / launches)
+        g.close()
+        us = statistics.median(times)
+        gbs = IC * OC * K // 8 / (us * 1e-6) / 1e9
+        out[name] = {"us_per_launch": us, "gb_per_s": gbs, "frac_of_hbm_peak": gbs / peak,
+                     "weight_buffers": nbuf if name == "hbm_resident" else 1}
+    return out
 
 
 # --------------------------------------------------------------------------- GPU side
@@ -447,6 +506,8 @@ def main() -> None:
                          "profiler captures, where less device memory must be saved and restored)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0,
                     help="bounded CPU-baseline sample (rank 0, N=1)")
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="how many times the --steps region is timed (median reported)")
     ap.add_argument("--group", default="layer", choices=["layer", "model"],
                     help="launch grouping at small batch: layer = the projections that read the "
                          "step input share one launch (2 launches per step); model = q/k/v | o | "
@@ -496,15 +557,12 @@ def main() -> None:
         oc_local = oc // world
         code = torch.randint(-2**31, 2**31 - 1, (ic // 16, oc_local // 16, 8 * k),
                              dtype=torch.int32, device=device, generator=gen)
-        w = object.__new__(dense.EschaWeight)
-        w.K, w.IC, w.OC, w.code = k, ic, oc_local, code
 
         def vec(n):
             scale = torch.randn(n, device=device, generator=gen).abs() * 0.02 + 1e-3
             sign = torch.randint(0, 2, (n,), device=device, generator=gen).float() * 2 - 1
             return (scale * sign).half().float()   # f16-representable, held as f32
-        w.rin, w.rout = vec(ic), vec(oc_local)
-        return w
+        return dense.EschaWeight.from_device(code, vec(ic), vec(oc_local))
 
     for _, ic, oc, _ in LAYER:
         if (oc // 128) % world:
@@ -650,15 +708,24 @@ def main() -> None:
     sync_all()
 
     # ---- value: resident inputs, device-timed -----------------------------------------------
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # the K-step region is timed `--repeats` times back to back; the line reports the median
+    # repeat and how far the first and the last lie from it (drift control)
+    rep_ms = []
     with ClockSampler(local_rank) as clocks:
-        sync_all()
-        ev0.record(stream)
-        for i in range(args.steps):
-            step_graphs[i % n_sets].replay()
-        ev1.record(stream)
-        sync_all()
-    ms_total = ev0.elapsed_time(ev1)
+        for _ in range(max(1, args.repeats)):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            sync_all()
+            ev0.record(stream)
+            for i in range(args.steps):
+                step_graphs[i % n_sets].replay()
+            ev1.record(stream)
+            sync_all()
+            rep_ms.append(ev0.elapsed_time(ev1))
+    if world > 1:   # every rank must pick the same repeat: rank-wise maxima first
+        t = torch.tensor(rep_ms, device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rep_ms = [float(v) for v in t.tolist()]
+    ms_total = statistics.median(rep_ms)
 
     # ---- e2e: pinned host activations in, layer output back out, every step -------------------
     # A serving loop pipelines its copies: step i+1's input is uploaded and step i's output is
@@ -736,6 +803,27 @@ def main() -> None:
     sync_all()
     ms_gemv = er0.elapsed_time(er1)
 
+    def prefill_leg(rows: int = 256, steps: int = 12) -> dict:
+        """The same layer at 256 rows on the tcgen05 GEMM (`--workload prefill`, shortened)."""
+        xp = torch.randn((rows, HIDDEN), device=device, generator=gen).half()
+        pgraphs = [graphs.GraphedCall(lambda xx, L=L: layer_step(L, xx), [xp]) for L in sets]
+        for gph in pgraphs:
+            gph.replay()
+        torch.cuda.synchronize()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record(stream)
+        for i in range(steps):
+            pgraphs[i % n_sets].replay()
+        p1.record(stream)
+        torch.cuda.synchronize()
+        ms = p0.elapsed_time(p1) / steps
+        for gph in pgraphs:
+            gph.close()
+        tpeak, _ = measured_peak_tflops()
+        tf = 2.0 * rows * sum(ic * oc for _, ic, oc, _ in LAYER) / (ms * 1e-3) / 1e12
+        return {"workload": f"dense27b_layer_prefill_m{rows}", "ms_per_step": ms, "tflops": tf,
+                "frac_of_bf16_peak": tf / tpeak}
+
     def max_over_ranks(v: float) -> float:
         if world == 1:
             return v
@@ -780,6 +868,10 @@ def main() -> None:
                          "timed": "seven projections launched one by one (CUDA-graph replays)",
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
             "clocks": clocks.summary(),
+            "repeats": {"n": len(rep_ms), "ms_per_step": [m / args.steps for m in rep_ms],
+                        "reported": "median",
+                        "first_vs_median_pct": 100.0 * (rep_ms[0] / ms_total - 1.0),
+                        "last_vs_median_pct": 100.0 * (rep_ms[-1] / ms_total - 1.0)},
         }
         if world == 1 and M <= msl.FUSE_INPUT_MAX_ROWS:
             # at these batch sizes the timed step is nothing but four launches of this kernel
@@ -794,8 +886,20 @@ def main() -> None:
                 "algorithmic_bytes_per_launch_avg": LAYER_BYTES / launches_per_step,
                 "traffic": (traffic * 7 / launches_per_step) if traffic else None,
                 "timed": f"the timed steps themselves: {launches_per_step} fused launches per step",
+                "traffic_source": "scaled from the captures under profiles/ (not measured in this run)",
                 "separate_launches": {k: sep[k] for k in ("achieved", "frac", "launches_timed",
                                                           "avg_launch_us", "traffic")}})
+        if not tensor_leg:
+            # second fraction: warp instructions the decode cannot do without (41 per 16x16
+            # tile at 2 bits, 46 at 3: profiles/issue_rates.md) over the issue slots the step
+            # had, one per sub-partition and clock at the sampled SM clock
+            tiles = {k: sum(ic * oc // 256 for _, ic, oc, kk in LAYER if kk == k) for k in (2, 3)}
+            need = (41 * tiles[2] + 46 * tiles[3]) / world
+            mhz = line["clocks"].get("sm_mhz") or 1965.0
+            have = 4 * 148 * mhz * 1e6 * (ms_total * 1e-3 / args.steps)
+            line["roofline"]["issue_frac"] = need / have
+            line["roofline"]["issue_note"] = ("minimal decode warp instructions per step / issue "
+                                              "slots in the step time (4 per SM per clock)")
         if world > 1:
             line["config"]["exchange"] = ("GEMV epilogue stores into every GPU's gathered row "
                                           "(peer memory) + barrier kernel"
@@ -821,7 +925,14 @@ def main() -> None:
                                  "unit": "TFLOP/s", "h2d_bytes_per_step": M * HIDDEN * 2,
                                  "d2h_bytes_per_step": M * HIDDEN * 2}})
         if world == 1 and not prefill and not args.no_moe_leg:
-            line["moe"] = moe_leg(device, 8)
+            # the other configurations of the published table, as short legs of the same run
+            line["prefill"] = prefill_leg()
+            line["c1"] = c1_leg(device)
+            for sg in step_graphs + gemv_graphs:
+                sg.close()
+            del sets[1:]
+            torch.cuda.empty_cache()
+            line["moe"] = moe_legs(device)
         if world == 1:
             cpu_rows = min(M, 16)
             cpu_gbs, passes, dt, cores = time_cpu(cpu_rows, args.cpu_seconds, 200)

@@ -848,6 +848,8 @@ int escha_coded_gemv_status(void) {
 
 void escha_debug_gemv_stall(int on, unsigned limit) { escha::gemv_stream_test_stall(on, limit); }
 
+void escha_debug_peer_poll_limit(unsigned polls) { escha::peer_barrier_poll_limit(polls); }
+
 int escha_coded_gemm_tc_status(void) {
     int st = 0;
     if (escha::gemm_tc_status(&st) != cudaSuccess) return -1;

@@ -242,6 +242,8 @@ struct PeerBarrierParams {
     int rank, nranks;
 };
 cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t st);
+// Test hook: polls a barrier launch makes before it gives up (0 restores the default).
+void peer_barrier_poll_limit(unsigned polls);
 
 cudaError_t launch_moe_route(const RouteParams& p, cudaStream_t st);
 size_t route_shared_bytes(int T, int top_k, int e_lo, int e_hi);

@@ -24,6 +24,7 @@ namespace escha {
 namespace {
 
 constexpr uint32_t kPollLimit = 1u << 24;
+uint32_t g_poll_limit = kPollLimit;   // host side; a test shortens it
 
 __device__ __forceinline__ void store_release_sys(int32_t* p, int32_t v) {
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -35,7 +36,7 @@ __device__ __forceinline__ int32_t load_acquire_sys(const int32_t* p) {
 }
 
 __global__ void __launch_bounds__(32)
-peer_barrier_kernel(const PeerBarrierParams p) {
+peer_barrier_kernel(const PeerBarrierParams p, const uint32_t poll_limit) {
     const int lane = threadIdx.x, n = p.nranks;
     int32_t epoch = 0;
     if (lane == 0) {
@@ -48,7 +49,7 @@ peer_barrier_kernel(const PeerBarrierParams p) {
     if (talks) store_release_sys(p.peer[lane] + p.rank, epoch);
     if (talks) {
         bool seen = false;
-        for (uint32_t it = 0; it < kPollLimit; ++it) {
+        for (uint32_t it = 0; it < poll_limit; ++it) {
             if (load_acquire_sys(p.local + lane) - epoch >= 0) {
                 seen = true;
                 break;
@@ -62,8 +63,10 @@ peer_barrier_kernel(const PeerBarrierParams p) {
 
 }  // namespace
 
+void peer_barrier_poll_limit(unsigned polls) { g_poll_limit = polls ? polls : kPollLimit; }
+
 cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t st) {
-    peer_barrier_kernel<<<1, 32, 0, st>>>(p);
+    peer_barrier_kernel<<<1, 32, 0, st>>>(p, g_poll_limit);
     return cudaGetLastError();
 }
 

@@ -1,0 +1,245 @@
+// Tile-body probe (a standalone program, not part of the library): cycles per 16x16 tile per
+// SM sub-partition for variants of the coded GEMV's decode loop -- the kernel's own form for
+// 2 and 3 bits, the same without the binary16 add, three instruction orders pinned with
+// volatile asm, and 1, 2, 3, 4 or 8 of a lane's eight states looked up in a 65536-entry table
+// in shared memory -- at 2/4/6/8 warps per scheduler, one CTA per SM, everything resident in
+// shared memory (no global traffic, no barriers).  Results of exact variants are checked
+// against variant 0 bit for bit.  With any argument it runs only variants 0 and 1 at 24 warps
+// (the form profiled with ncu).
+//
+//   nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 -o tile_probe tile_probe.cu
+#include <cstdio>
+#include <vector>
+#include "../common.cuh"
+using namespace escha;
+
+#define DI __device__ __forceinline__
+
+DI uint32_t v_prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d; asm volatile("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel)); return d;
+}
+DI uint32_t v_mul(uint32_t a, uint32_t b) {
+    uint32_t d; asm volatile("mul.lo.u32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+}
+DI uint32_t v_lop(uint32_t a, uint32_t m, uint32_t x) {
+    uint32_t d; asm volatile("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(m), "r"(x)); return d;
+}
+DI uint32_t v_hadd_dup(uint32_t r) {
+    uint32_t d;
+    asm volatile("{ .reg .b16 lo, hi; .reg .b32 a, b; mov.b32 {lo, hi}, %1; mov.b32 a, {lo, lo}; mov.b32 b, {hi, hi}; add.rn.f16x2 %0, a, b; }"
+                 : "=r"(d) : "r"(r));
+    return d;
+}
+DI uint32_t v_lds16(uint32_t addr) {
+    uint32_t d;
+    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(d) : "r"(addr));
+    return d;
+}
+
+struct Ctx {
+    uint32_t hm, hx, hc;       // mask, xor, multiplier (run-time registers)
+    ShiftMuls m;
+    uint32_t lut;              // shared address of the table
+};
+
+// ---- variant bodies: produce a[8] for one tile from the two code words
+// 0: the kernel's current form (stage-major, compiler-scheduled)
+template <int K>
+DI void dec_base(const LaneConsts<K>& lc, uint32_t wa, uint32_t wb, const Ctx& c, uint32_t a[8]) {
+    uint32_t s[8];
+    lc.states(wa, wb, c.m, s);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = cba_decode_dup(s[j], c.hm, c.hx);
+}
+// 2: no binary16 add (halves un-added)
+DI void dec_sum(const LaneConsts<2>& lc, uint32_t wa, uint32_t wb, const Ctx& c, uint32_t a[8]) {
+    uint32_t s[8];
+    lc.states(wa, wb, c.m, s);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = cba_hash_halves(s[j], c.hm, c.hx);
+}
+// K2 extraction pieces with pinned order
+DI void k2_prep(const LaneConsts<2>& lc, uint32_t wa, uint32_t wb, const Ctx& c, uint32_t z[4]) {
+    z[0] = v_prmt(wb, wa, lc.sel);
+    z[1] = v_mul(z[0], c.m.m4); z[2] = v_mul(z[0], c.m.m16); z[3] = v_mul(z[0], c.m.m64);
+}
+// state j of K2: source register and selector
+template <int J> DI uint32_t k2_ext(const uint32_t z[4]) {
+    // s7: z0 0x4410, s3: z0 0x4421, s6: z3 0x4421, s2: z3 0x4432, s5: z2 0x4421, s1: z2 0x4432, s4: z1 0x4421, s0: z1 0x4432
+    constexpr int src = (J == 7 || J == 3) ? 0 : (J == 6 || J == 2) ? 3 : (J == 5 || J == 1) ? 2 : 1;
+    constexpr uint32_t sel = (J == 7) ? 0x4410u : (J >= 4 || J == 3) ? 0x4421u : 0x4432u;
+    return v_prmt(z[src], 0u, sel);
+}
+// 3: chain-major, pinned: each weight finished before the next starts
+DI void dec_chain(const LaneConsts<2>& lc, uint32_t wa, uint32_t wb, const Ctx& c, uint32_t a[8]) {
+    uint32_t z[4]; k2_prep(lc, wa, wb, c, z);
+#define CH1(J) a[J] = v_hadd_dup(v_lop(v_mul(k2_ext<J>(z), c.hc), c.hm, c.hx));
+    CH1(0) CH1(1) CH1(2) CH1(3) CH1(4) CH1(5) CH1(6) CH1(7)
+#undef CH1
+}
+// 4: skewed software pipeline inside a tile, pinned: int, mul, int, mul per step
+DI void dec_skew(const LaneConsts<2>& lc, uint32_t wa, uint32_t wb, const Ctx& c, uint32_t a[8]) {
+    uint32_t z[4]; k2_prep(lc, wa, wb, c, z);
+    uint32_t e[8], p[8], r[8];
+#define E(J) e[J] = k2_ext<J>(z);
+#define M(J) p[J] = v_mul(e[J], c.hc);
+#define L(J) r[J] = v_lop(p[J], c.hm, c.hx);
+#define H(J) a[J] = v_hadd_dup(r[J]);
+    E(0)
+    E(1) M(0)
+    E(2) M(1) L(0)
+    E(3) M(2) L(1) H(0)
+    E(4) M(3) L(2) H(1)
+    E(5) M(4) L(3) H(2)
+    E(6) M(5) L(4) H(3)
+    E(7) M(6) L(5) H(4)
+         M(7) L(6) H(5)
+              L(7) H(6)
+                   H(7)
+#undef E
+#undef M
+#undef L
+#undef H
+}
+// 5: stage-major, pinned order (what the source of variant 0 says, without compiler freedom)
+DI void dec_stage(const LaneConsts<2>& lc, uint32_t wa, uint32_t wb, const Ctx& c, uint32_t a[8]) {
+    uint32_t z[4]; k2_prep(lc, wa, wb, c, z);
+    uint32_t e[8];
+    e[0] = k2_ext<0>(z); e[1] = k2_ext<1>(z); e[2] = k2_ext<2>(z); e[3] = k2_ext<3>(z);
+    e[4] = k2_ext<4>(z); e[5] = k2_ext<5>(z); e[6] = k2_ext<6>(z); e[7] = k2_ext<7>(z);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = v_mul(e[j], c.hc);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = v_lop(e[j], c.hm, c.hx);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = v_hadd_dup(e[j]);
+}
+// 6..8: table in shared memory for NL of the eight weights (the rest hashed); NL = 8, 2, 4
+template <int NL>
+DI void dec_lut(const LaneConsts<2>& lc, uint32_t wa, uint32_t wb, const Ctx& c, uint32_t a[8]) {
+    uint32_t s[8];
+    lc.states(wa, wb, c.m, s);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (j < NL) a[j] = v_lds16(c.lut + s[j] + s[j]);
+        else a[j] = cba_decode_dup(s[j], c.hm, c.hx);
+    }
+}
+
+template <int VAR>
+DI void decode_tile(const LaneConsts<2>& l2, const LaneConsts<3>& l3, uint32_t wa, uint32_t wb, const Ctx& c, uint32_t a[8]) {
+    if (VAR == 0) dec_base<2>(l2, wa, wb, c, a);
+    else if (VAR == 1) dec_base<3>(l3, wa, wb, c, a);
+    else if (VAR == 2) dec_sum(l2, wa, wb, c, a);
+    else if (VAR == 3) dec_chain(l2, wa, wb, c, a);
+    else if (VAR == 4) dec_skew(l2, wa, wb, c, a);
+    else if (VAR == 5) dec_stage(l2, wa, wb, c, a);
+    else if (VAR == 6) dec_lut<8>(l2, wa, wb, c, a);
+    else if (VAR == 7) dec_lut<2>(l2, wa, wb, c, a);
+    else if (VAR == 8) dec_lut<4>(l2, wa, wb, c, a);
+    else if (VAR == 9) dec_lut<1>(l2, wa, wb, c, a);
+    else if (VAR == 10) dec_lut<3>(l2, wa, wb, c, a);
+}
+
+constexpr int kStages = 6;
+constexpr int kLutBytes = 131072;
+
+template <int VAR, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
+probe(uint32_t seed, int iters, float* out, long long* cyc, uint32_t hm, uint32_t hx, uint32_t hc, ShiftMuls mu) {
+    constexpr int K = (VAR == 1) ? 3 : 2;
+    constexpr int WPT = 8 * K, ROW_WORDS = 8 * WPT, STAGE_WORDS = 8 * ROW_WORDS;
+    extern __shared__ __align__(128) uint32_t sm[];
+    // [table 128 KiB][code kStages stages][x 2 rows of 16 blocks]
+    __half* lut = reinterpret_cast<__half*>(sm);
+    uint32_t* s_code = sm + kLutBytes / 4;
+    uint32_t* s_x = s_code + kStages * STAGE_WORDS;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (uint32_t i = tid; i < 65536; i += NW * 32) lut[i] = cba_decode(i);
+    for (uint32_t i = tid; i < kStages * STAGE_WORDS; i += NW * 32) s_code[i] = (seed + i) * 2654435761u ^ ((seed * 40503u + i * 97u) << 7);
+    for (uint32_t i = tid; i < 2 * (16 * 128 + 16); i += NW * 32)
+        s_x[i] = __half_as_ushort(__float2half_rn(((i * 37u) % 64u) * 0.03125f - 1.0f));
+    __syncthreads();
+    const LaneConsts<2> l2(lane); const LaneConsts<3> l3(lane);
+    Ctx c{hm, hx, hc, mu, smem_u32(lut)};
+    const uint32_t team = warp & 7u;
+    const uint32_t* wa0 = s_code + team * WPT + (K == 2 ? l2.ia() : l3.ia());
+    const uint32_t* wb0 = s_code + team * WPT + (K == 2 ? l2.ib() : l3.ib());
+    const uint32_t* xr0 = s_x + 4u * (lane & 3u);
+    float dA[4] = {0, 0, 0, 0}, dB[4] = {0, 0, 0, 0};
+    const long long t0 = clock64();
+    for (int it = 0; it < iters; ++it) {
+        for (int slot = 0; slot < kStages; ++slot) {
+            const uint32_t* wa = wa0 + slot * STAGE_WORDS;
+            const uint32_t* wb = wb0 + slot * STAGE_WORDS;
+            const uint32_t* xr = xr0 + slot * 128;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                uint32_t a[8];
+                decode_tile<VAR>(l2, l3, wa[kk * ROW_WORDS], wb[kk * ROW_WORDS], c, a);
+                const uint4 b = *reinterpret_cast<const uint4*>(xr + kk * 16);
+                mma16816(dA, a[0], a[4], a[2], a[6], b.x, b.y);
+                mma16816(dB, a[1], a[5], a[3], a[7], b.z, b.w);
+            }
+        }
+    }
+    const long long t1 = clock64();
+    out[blockIdx.x * (NW * 32) + tid] = dA[0] + dA[1] + dA[2] + dA[3] + dB[0] + dB[1] + dB[2] + dB[3];
+    if (lane == 0) cyc[blockIdx.x * NW + warp] = t1 - t0;
+}
+
+static std::vector<float> g_ref[4];
+
+template <int VAR, int NW>
+void run(const char* name, int sms, bool exact, int slotidx) {
+    constexpr int K = (VAR == 1) ? 3 : 2;
+    const int iters = 200;
+    const size_t smem = kLutBytes + (kStages * 8 * 8 * 8 * K + 2 * (16 * 128 + 16)) * 4;
+    cudaFuncSetAttribute(probe<VAR, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    float* out; long long* cyc;
+    cudaMalloc(&out, (size_t)sms * NW * 32 * 4); cudaMalloc(&cyc, (size_t)sms * NW * 8);
+    ShiftMuls mu{2, 4, 16, 32, 64, 128};
+    probe<VAR, NW><<<sms, NW * 32, smem>>>(7, 2, out, cyc, 0x8FFF8FFFu, 0x3B603B60u, 0xCBAC1FEDu, mu);
+    probe<VAR, NW><<<sms, NW * 32, smem>>>(12345, iters, out, cyc, 0x8FFF8FFFu, 0x3B603B60u, 0xCBAC1FEDu, mu);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) { printf("var %d nw %d: %s\n", VAR, NW, cudaGetErrorString(e)); return; }
+    std::vector<long long> h(sms * NW); std::vector<float> o((size_t)sms * NW * 32);
+    cudaMemcpy(h.data(), cyc, h.size() * 8, cudaMemcpyDeviceToHost);
+    cudaMemcpy(o.data(), out, o.size() * 4, cudaMemcpyDeviceToHost);
+    long long mx = 0; double mean = 0;
+    for (auto v : h) { mx = v > mx ? v : mx; mean += v; }
+    mean /= h.size();
+    const double tiles_per_warp = (double)iters * kStages * 8;
+    const char* chk = "";
+    if (exact) {
+        std::vector<float>& ref = g_ref[slotidx];
+        if (VAR == 0) ref = o;
+        else if (!ref.empty()) chk = (memcmp(ref.data(), o.data(), o.size() * 4) == 0) ? " bits==var0" : " BITS DIFFER";
+    }
+    printf("var %2d %-30s warps/SMSP %d: %7.1f clk/tile/SMSP (mean)  %7.1f (max)%s\n", VAR, name, NW / 4,
+           mean / (tiles_per_warp * (NW / 4)), mx / (tiles_per_warp * (NW / 4)), chk);
+    cudaFree(out); cudaFree(cyc);
+}
+
+template <int VAR> void runall(const char* name, int sms, bool exact) {
+    run<VAR, 8>(name, sms, exact, 0); run<VAR, 16>(name, sms, exact, 1);
+    run<VAR, 24>(name, sms, exact, 2); run<VAR, 32>(name, sms, exact, 3);
+}
+
+int main(int argc, char** argv) {
+    cudaDeviceProp p; cudaGetDeviceProperties(&p, 0); int sms = p.multiProcessorCount;
+    printf("%s sms=%d\n", p.name, sms);
+    if (argc > 1) { run<0, 24>("k2 current", sms, true, 2); run<1, 24>("k3 current", sms, false, 2); return 0; }
+    runall<0>("k2 current", sms, true);
+    runall<1>("k3 current", sms, false);
+    runall<2>("k2 no f16 add", sms, false);
+    runall<3>("k2 chain-major pinned", sms, true);
+    runall<4>("k2 skewed pinned", sms, true);
+    runall<5>("k2 stage-major pinned", sms, true);
+    runall<6>("k2 table x8", sms, true);
+    runall<9>("k2 table x1 + hash x7", sms, true);
+    runall<7>("k2 table x2 + hash x6", sms, true);
+    runall<10>("k2 table x3 + hash x5", sms, true);
+    runall<8>("k2 table x4 + hash x4", sms, true);
+    return 0;
+}

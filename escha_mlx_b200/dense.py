@@ -71,6 +71,59 @@ def pack_code(code_i16: np.ndarray, device=None) -> torch.Tensor:
     return msl.code_tensor(code_i16, device)
 
 
+class _StreamGeometry:
+    """What a code array's shape says about the linear: rate, input and output width."""
+
+    def __init__(self, K: int, IC: int, OC: int) -> None:
+        self.K, self.IC, self.OC = K, IC, OC
+
+    @classmethod
+    def of(cls, shape: tuple, packed: bool) -> "_StreamGeometry":
+        if len(shape) != 3:
+            raise ValueError(f"escha code must be [TK, TN, words per tile], got shape {shape}")
+        words = 8 if packed else 16          # 32-bit or 16-bit words per tile and bit of rate
+        if shape[2] % words:
+            raise ValueError(f"{'packed ' if packed else ''}escha code last dim must be "
+                             f"{words}*K, got {shape[2]}")
+        return cls(shape[2] // words, shape[0] * 16, shape[1] * 16)
+
+    def require(self, rin, rout, s_in, s_out, config) -> None:
+        """Raise ValueError for the first contract violation, in the order the reference
+        checks them: rate, vector shapes, alignment, the export's config record, scales."""
+        shapes = (tuple(np.shape(rin)), tuple(np.shape(rout)))
+        problems = (
+            (self.K not in SUPPORTED_K,
+             f"escha code implies K={self.K}; this runtime implements K in {sorted(SUPPORTED_K)}"),
+            (shapes != ((self.IC,), (self.OC,)),
+             f"transform vectors {shapes[0]}/{shapes[1]} do not match the code stream's "
+             f"{self.IC}x{self.OC}; both must be 1-D ({self.IC},)/({self.OC},)"),
+            (self.IC % 128 != 0 or self.OC % 128 != 0,
+             f"escha linear dimensions must be multiples of 128, got {self.IC}x{self.OC}"),
+        )
+        for bad, message in problems:
+            if bad:
+                raise ValueError(message)
+        if config is not None:
+            self._require_config([int(v) for v in np.asarray(config).ravel()])
+        _check_scale("escha_s_in", s_in, self.IC)
+        _check_scale("escha_s_out", s_out, self.OC)
+
+    def _require_config(self, record: list) -> None:
+        if len(record) != _CONFIG_LEN:
+            raise ValueError(
+                f"escha_config has {len(record)} fields, expected {_CONFIG_LEN} ([L, K, V, "
+                f"codebook_id, in_features, out_features]); this export was written by an "
+                f"incompatible version")
+        claimed = (record[1], record[4], record[5])
+        if claimed != (self.K, self.IC, self.OC):
+            raise ValueError(f"escha_config {claimed} disagrees with the code stream "
+                             f"{(self.K, self.IC, self.OC)}")
+        if record[3] != _PRODUCTION_CODEBOOK:
+            raise ValueError(
+                f"escha_config selects codebook id {record[3]}; this runtime implements the "
+                f"production codebook (id {_PRODUCTION_CODEBOOK}) only")
+
+
 class EschaWeight:
     """One dense linear's coded stream plus its folded transform vectors.
 
@@ -79,58 +132,34 @@ class EschaWeight:
     """
 
     def __init__(self, code, rin, rout, s_in=None, s_out=None, config=None, device=None) -> None:
-        if isinstance(code, torch.Tensor):
-            tk, tn, wpt = code.shape          # already packed: 8K 32-bit words
-            if wpt % 8:
-                raise ValueError(f"packed escha code last dim must be 8*K, got {wpt}")
-            self.K = wpt // 8
-            code_dev = code
-            device = code.device
-        else:
-            tk, tn, wpt2 = np.shape(code)     # raw export: 16K int16 words
-            if wpt2 % 16:
-                raise ValueError(f"escha code last dim must be 16*K, got {wpt2}")
-            self.K = wpt2 // 16
-            code_dev = None
-        if self.K not in SUPPORTED_K:
-            raise ValueError(
-                f"escha code implies K={self.K}; this runtime implements "
-                f"K in {sorted(SUPPORTED_K)}")
-        self.IC, self.OC = tk * 16, tn * 16
-        if np.shape(rin) != (self.IC,) or np.shape(rout) != (self.OC,):
-            raise ValueError(
-                f"transform vectors {np.shape(rin)}/{np.shape(rout)} do not match "
-                f"the code stream's {self.IC}x{self.OC}; both must be 1-D "
-                f"({self.IC},)/({self.OC},)")
-        if self.IC % 128 or self.OC % 128:
-            raise ValueError(
-                f"escha linear dimensions must be multiples of 128, got "
-                f"{self.IC}x{self.OC}")
-        if config is not None:
-            cfg = [int(v) for v in np.asarray(config).ravel()]
-            if len(cfg) != _CONFIG_LEN:
-                raise ValueError(
-                    f"escha_config has {len(cfg)} fields, expected {_CONFIG_LEN} "
-                    f"([L, K, V, codebook_id, in_features, out_features]); this "
-                    f"export was written by an incompatible version")
-            _, k_cfg, _, cb, ic_cfg, oc_cfg = cfg
-            if (k_cfg, ic_cfg, oc_cfg) != (self.K, self.IC, self.OC):
-                raise ValueError(
-                    f"escha_config {(k_cfg, ic_cfg, oc_cfg)} disagrees with the "
-                    f"code stream {(self.K, self.IC, self.OC)}")
-            if cb != _PRODUCTION_CODEBOOK:
-                raise ValueError(
-                    f"escha_config selects codebook id {cb}; this runtime "
-                    f"implements the production codebook "
-                    f"(id {_PRODUCTION_CODEBOOK}) only")
-        _check_scale("escha_s_in", s_in, self.IC)
-        _check_scale("escha_s_out", s_out, self.OC)
-        if code_dev is None:
-            code_dev = pack_code(code, device)
-        self.code = code_dev                                   # [TK, TN, 8K] 32-bit words
+        """``code`` is the export's int16 [TK, TN, 16K] array or an already packed device
+        tensor [TK, TN, 8K] of 32-bit words; ``rin``/``rout`` are the folded sign*scale
+        vectors, ``s_in``/``s_out`` optional extra scales, ``config`` the export's
+        [L, K, V, codebook, IC, OC] record.  Refuses what the reference's constructor
+        refuses (escha_mlx/dense.py:168-242), before anything reaches a kernel."""
+        packed = isinstance(code, torch.Tensor)
+        geo = _StreamGeometry.of(tuple(code.shape) if packed else tuple(np.shape(code)), packed)
+        geo.require(rin, rout, s_in, s_out, config)
+        self.K, self.IC, self.OC = geo.K, geo.IC, geo.OC
+        self.code = code if packed else pack_code(code, device)   # [TK, TN, 8K] 32-bit words
         ri, ro = fold_scales(_to_numpy(rin), _to_numpy(rout), _to_numpy(s_in), _to_numpy(s_out))
-        self.rin = torch.from_numpy(ri).to(code_dev.device)    # [IC] f32
-        self.rout = torch.from_numpy(ro).to(code_dev.device)   # [OC] f32
+        self.rin = torch.from_numpy(ri).to(self.code.device)      # [IC] f32
+        self.rout = torch.from_numpy(ro).to(self.code.device)     # [OC] f32
+
+    @classmethod
+    def from_device(cls, code: torch.Tensor, rin: torch.Tensor, rout: torch.Tensor) -> "EschaWeight":
+        """A weight whose packed stream and already folded f32 vectors live on the device
+        (synthetic workloads, weights produced by another stage).  Same refusals as the
+        constructor; nothing is copied."""
+        geo = _StreamGeometry.of(tuple(code.shape), True)
+        geo.require(rin, rout, None, None, None)
+        for name, v in (("rin", rin), ("rout", rout)):
+            if v.dtype != torch.float32 or v.device != code.device or not v.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous float32 tensor on the code's device")
+        w = cls.__new__(cls)
+        w.K, w.IC, w.OC = geo.K, geo.IC, geo.OC
+        w.code, w.rin, w.rout = code.contiguous(), rin, rout
+        return w
 
     def weight_numpy(self) -> np.ndarray:
         """Decoded bare weight [IC, OC] as f32 (debug/inspection; decoded on the GPU)."""

@@ -8,11 +8,13 @@ contract is the un-repacked one, ``ref.w8a16`` (escha_mlx/ref.py:308-311):
 
     y = f16( f32(x) @ f32( f16( f32(w8) * f32(scale) ) )^T )
 
-On B200 the kernel reads the export's own layout, so there is nothing to repack;
-``pack_q8``/``validate_pack`` are kept as exact, trivially invertible
-passthroughs so loader code written against the reference keeps working, and
-``group_size`` arguments are accepted and ignored (the reference documents group
-size as numerically free, tests/test_mlx_cpu.py:19-41).
+On B200 the kernel reads the export's own layout, so there is nothing to repack:
+``pack_q8`` validates and returns ``(w8, f16 scale)`` instead of the reference's MLX
+triple ``(u32 weight, scales, biases)``; ``validate_pack(group_size)`` is, as in the
+reference, a one-time on-device check that the dequantised weight equals
+``f16(w8 * scale)`` bit for bit; ``group_size`` arguments are accepted everywhere and do
+not change the arithmetic (the reference documents group size as numerically free,
+tests/test_mlx_cpu.py:19-41).
 """
 from __future__ import annotations
 
@@ -45,11 +47,27 @@ def pack_q8(w8: np.ndarray, scale: np.ndarray, group_size: int = DEFAULT_GROUP):
     return w8, scale.astype(np.float16)
 
 
-def validate_pack(w8: np.ndarray, scale: np.ndarray, packed) -> None:
-    """Refuse to serve unless the packed form reproduces the export exactly."""
-    pw, ps = packed
-    if not (np.array_equal(pw, w8) and np.array_equal(ps, np.asarray(scale).astype(np.float16))):
-        raise ValueError("int8 repack is not bit-exact")
+_VALIDATED: set[int] = set()
+
+
+def validate_pack(group_size: int = DEFAULT_GROUP, device=None) -> None:
+    """One-time on-device check, per group size like the reference's (:100-122): the int8
+    linear fed one-hot rows must reproduce ``f16(w8 * scale)`` exactly, i.e. what the
+    kernel dequantises is the export's weight bit for bit.  ``group_size`` only keys the
+    cache: the kernel's layout has one scale per output row whatever the export's groups."""
+    if group_size in _VALIDATED:
+        return
+    rng = np.random.default_rng(0)
+    w8 = rng.integers(-128, 128, size=(16, 512), dtype=np.int8)
+    scale = (rng.random(16, dtype=np.float32) * 0.05 + 1e-3).astype(np.float16)
+    pw, ps = pack_q8(w8, scale, fit_group(512, group_size))
+    dev = torch.device(device or "cuda")
+    eye = torch.eye(512, dtype=torch.float16, device=dev)
+    got = w8a16(eye, torch.from_numpy(pw).to(dev), torch.from_numpy(ps).to(dev)).T.cpu().numpy()
+    want = (w8.astype(np.float32) * scale.astype(np.float32)[:, None]).astype(np.float16)
+    if not np.array_equal(got.view(np.uint16), want.view(np.uint16)):
+        raise ValueError(f"int8 repack is not bit-exact for group size {group_size}")
+    _VALIDATED.add(group_size)
 
 
 def w8a16(x: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
@@ -81,8 +99,8 @@ class EschaQ8Linear(torch.nn.Module):
             self.out_features, self.in_features = w8.shape
             return
         pw, ps = pack_q8(w8, scale, group_size)
-        validate_pack(w8, scale, (pw, ps))
         dev = device or "cuda"
+        validate_pack(group_size, dev)
         self._w8 = torch.from_numpy(pw).to(dev)
         self._scale = torch.from_numpy(ps).to(dev)
         self.out_features, self.in_features = pw.shape
@@ -99,9 +117,11 @@ class EschaQ8Linear(torch.nn.Module):
 Q8_HEAD_MAX_ROWS = 8
 
 
-def q8_head(x: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+def q8_head(x: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor,
+            group_size: int = DEFAULT_GROUP) -> torch.Tensor:
     """Project 1..8 flattened rows through an int8 vocabulary matrix (reference
-    :211-240).  The reference needs a separate small-row kernel for this; here it is
+    :203-240; ``group_size`` is accepted for the reference's signature and unused, the
+    scales here are per output row).  The reference needs a separate small-row kernel for this; here it is
     the same tensor-core int8 linear, which streams a 311 MB head at 85% of the HBM
     peak at one row."""
     rows = x.reshape(-1, x.shape[-1])

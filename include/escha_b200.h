@@ -409,6 +409,12 @@ int escha_coded_gemv_status(void);
  * usable.  on == 0 restores normal operation. */
 void escha_debug_gemv_stall(int on, unsigned limit);
 
+/* Test hook, no counterpart in the reference: the number of polls (about 100 ns apart) an
+ * escha_peer_barrier launch makes for a peer before it gives up, raises word nranks+1 of
+ * local_flags (see escha_peer_barrier) and returns; 0 restores the default
+ * (about two seconds).  Lets a test watch the barrier give up on a peer that never arrives. */
+void escha_debug_peer_poll_limit(unsigned polls);
+
 #ifdef __cplusplus
 }
 #endif

@@ -407,6 +407,14 @@ def test_single_pass_block_matches_op_by_op(cuda, monkeypatch):
 
 # --------------------------------------------------------------------------- int8 head / embedding
 
+def test_validate_pack_on_device(cuda):
+    from escha_mlx_b200 import quant
+    quant._VALIDATED.clear()
+    quant.validate_pack(64, cuda)
+    quant.validate_pack(32, cuda)
+    assert quant._VALIDATED == {64, 32}
+
+
 def test_q8_head_and_embedding(cuda, oracle):
     rng = np.random.default_rng(8)
     V, Kd = 1024, 256

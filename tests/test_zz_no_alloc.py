@@ -6,8 +6,10 @@ host allocator -- so they cannot provide the split-K workspace the regular entry
 point takes.  For them the library carries a static device array.  This test
 calls that entry point straight through the C ABI, twice in a row (the second
 call sees whatever the first left in the shared array), and checks both results
-against the regular entry point given a caller workspace.  Equal split factors
-mean equal summation order, so the comparison is exact.
+against the regular entry point given a caller workspace (equal split factors
+mean equal summation order, so that comparison is exact) and against the CPU
+oracle (an fp64 product of oracle-decoded weights, then the oracle's output
+transform where the launch fuses it) within the path's 1e-3 bar.
 
 Collected last on purpose: if it fails, `pytest -x` has already run everything else.
 """
@@ -48,7 +50,7 @@ def _static(xh, code, rout, K, IC, OC, splits):
 @pytest.mark.parametrize("K,IC,OC,M,splits,fused", [(2, 1024, 384, 1, 4, True),
                                                     (3, 1536, 256, 7, 3, False),
                                                     (2, 512, 128, 12, 2, True)])
-def test_static_scratch_matches_caller_workspace_twice(cuda, K, IC, OC, M, splits, fused):
+def test_static_scratch_matches_caller_workspace_twice(cuda, oracle, K, IC, OC, M, splits, fused):
     rng = np.random.default_rng(K * 100 + M)
     code, _, rout = synth.coded_projection(rng, IC, OC, K)
     c = msl.code_tensor(code, cuda)
@@ -60,6 +62,12 @@ def test_static_scratch_matches_caller_workspace_twice(cuda, K, IC, OC, M, split
     torch.cuda.synchronize()
     for g, w in zip(got, want):
         assert torch.equal(g, w)
+    for g, x in zip(got, xs):
+        exact = oracle.gemv_f64(x.cpu().numpy(), code, None, K, IC, OC)
+        if fused:   # y = f16((H128(mid) * RS) * rout): the oracle's transform of the exact product
+            exact = oracle.output_transform(exact.astype(np.float32), rout.astype(np.float32)).astype(np.float64)
+        err = np.abs(g.float().cpu().numpy().astype(np.float64) - exact).max() / np.abs(exact).max()
+        assert err < 1e-3, err
     assert not torch.equal(got[0], got[1])   # different inputs really produced different outputs
 
 
