@@ -508,6 +508,10 @@ def main() -> None:
                     help="bounded CPU-baseline sample (rank 0, N=1)")
     ap.add_argument("--repeats", type=int, default=5,
                     help="how many times the --steps region is timed (median reported)")
+    ap.add_argument("--wave", type=int, default=1,
+                    help="1: split factors of a joint launch chosen for the launch as a whole "
+                         "(dense.project_many(one_wave=True)); 0: every projection keeps the factor "
+                         "it has alone (bit-identical to separate calls)")
     ap.add_argument("--group", default="layer", choices=["layer", "model"],
                     help="launch grouping at small batch: layer = the projections that read the "
                          "step input share one launch (2 launches per step); model = q/k/v | o | "
@@ -547,14 +551,19 @@ def main() -> None:
     args.warmup = max(args.warmup, 3)
     M = args.batch
 
+    # From 32 rows on (the tcgen05 kernel) the rows are the independent unit: every rank holds the
+    # full weights and runs its own `--batch` rows, with nothing to exchange (weak scaling: the
+    # job's batch is N x --batch).  Below that, split-N tensor parallelism (strong scaling).
+    replica = world > 1 and M >= 32
+    shards = 1 if replica else world
     # weight sets: enough distinct layers that a step's per-GPU code bytes never sit in L2
-    per_gpu = LAYER_BYTES // world
+    per_gpu = LAYER_BYTES // shards
     n_sets = max(2, -(-3 * L2_BYTES // per_gpu))
     gen = torch.Generator(device=device)
     gen.manual_seed(1234 + rank)
 
     def make_weight(ic: int, oc: int, k: int) -> dense.EschaWeight:
-        oc_local = oc // world
+        oc_local = oc // shards
         code = torch.randint(-2**31, 2**31 - 1, (ic // 16, oc_local // 16, 8 * k),
                              dtype=torch.int32, device=device, generator=gen)
 
@@ -565,14 +574,14 @@ def main() -> None:
         return dense.EschaWeight.from_device(code, vec(ic), vec(oc_local))
 
     for _, ic, oc, _ in LAYER:
-        if (oc // 128) % world:
-            raise SystemExit(f"{oc // 128} output blocks do not split over {world} GPUs")
+        if (oc // 128) % shards:
+            raise SystemExit(f"{oc // 128} output blocks do not split over {shards} GPUs")
     sets = [{name: dense.EschaLinear(make_weight(ic, oc, k)) for name, ic, oc, k in LAYER}
             for _ in range(n_sets)]
 
     ROW = sum(oc for _, _, oc, _ in LAYER)     # gathered halves per activation row and layer
     pg, arena, gathered = None, None, []
-    if world > 1:
+    if world > 1 and not replica:
         # split-N tensor parallel: the GEMV epilogue stores each rank's columns into every
         # GPU's gathered row (peer-mapped memory), one bounded cross-GPU barrier per launch.
         # One buffer set per weight set: a buffer is rewritten n_sets barriers later.
@@ -609,15 +618,15 @@ def main() -> None:
         pg.barrier()
         return outs
 
-    tc_shards = world > 1 and msl.use_prefill_kernel(M) and M >= 32
+    tc_shards = False   # from 32 rows on ranks are row replicas (above); shards stay on the GEMV
     # launch grouping of the fused small-batch path: "layer" follows this step's own data flow
     # (q/k/v, o, gate, up all read the step input: one launch; SwiGLU + down: a second);
     # "model" keeps the four launches a transformer layer with attention between q/k/v and o
     # needs (q/k/v | o | gate/up | SwiGLU + down)
-    joint_launches = args.group == "layer" and world == 1 and M <= msl.FUSE_INPUT_MAX_ROWS
+    joint_launches = args.group == "layer" and (world == 1 or replica) and M <= msl.FUSE_INPUT_MAX_ROWS
 
     def layer_step(layer, x, bufs=None):
-        if world > 1 and (pg is None or tc_shards):
+        if world > 1 and not replica and (pg is None or tc_shards):
             # NCCL form of the same exchange: an all-gather of every projection's f16 output
             # (also from 32 rows on, where each rank's shard runs on the tcgen05 kernel, whose
             # epilogue does not store to peers; measured on 2 GPUs: 16 rows 178 us through the
@@ -629,9 +638,9 @@ def main() -> None:
             g, u = (ag(t) for t in dense.project_pair(layer["gate_proj"], layer["up_proj"], x))
             d = ag(dense.swiglu_project(layer["down_proj"], g, u))
             return q, k, v, o, d
-        if world > 1:
-            q, k, v = tp_launch(layer, bufs, ("q_proj", "k_proj", "v_proj"), x)
-            (o,) = tp_launch(layer, bufs, ("o_proj",), x)
+        if world > 1 and not replica:
+            # one launch (and one cross-GPU join) per rate among the projections of the input
+            q, k, v, o = tp_launch(layer, bufs, ("q_proj", "k_proj", "v_proj", "o_proj"), x)
             g, u = tp_launch(layer, bufs, ("gate_proj", "up_proj"), x)
             (d,) = tp_launch(layer, bufs, ("down_proj",), g, u)   # full-width SwiGLU input
             return q, k, v, o, d
@@ -639,7 +648,8 @@ def main() -> None:
             # every projection that reads the step's input in ONE launch (2-bit and 3-bit
             # streams side by side), SwiGLU + down in a second
             q, k, v, o, g, u = dense.project_many(
-                [layer[n] for n in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj")], x)
+                [layer[n] for n in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj")], x,
+                one_wave=args.wave)
         else:
             q, k, v = dense.project_many([layer["q_proj"], layer["k_proj"], layer["v_proj"]], x)
             o = layer["o_proj"](x)
@@ -652,8 +662,8 @@ def main() -> None:
     if M <= msl.FUSE_INPUT_MAX_ROWS:
         # joint: one launch for all rates (persistent kernel) or one per rate
         per_step = (2 if msl.mixed_rates_supported() else 3) if joint_launches else 4
-        launches_per_step = per_step if world == 1 else 8   # + 4 peer barriers
-    elif msl.use_prefill_kernel(M) and (world == 1 or tc_shards):
+        launches_per_step = per_step if world == 1 else 6   # 3 fused GEMV + 3 peer barriers
+    elif msl.use_prefill_kernel(M) and (world == 1 or replica):
         # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), the tcgen05 GEMMs,
         # and a plane sum + output transform for every projection split more than 4 ways along K
         from escha_mlx_b200._lib import lib as _lib
@@ -662,7 +672,7 @@ def main() -> None:
             # plane-sum launch
             return _lib.escha_coded_gemm_tc_splits(ic, oc, 0) > 4
         # a rank holds 1/world of every projection's output channels (split-N)
-        dims = {name: (ic, oc // world) for name, ic, oc, _k in LAYER}
+        dims = {name: (ic, oc // shards) for name, ic, oc, _k in LAYER}
         qkv_oc = sum(dims[n][1] for n in ("q_proj", "k_proj", "v_proj"))
         # q/k/v share one GEMM launch (their column blocks fit one wave) and, up to 128 rows,
         # one plane-sum launch
@@ -675,6 +685,36 @@ def main() -> None:
         launches_per_step = 8 if world == 1 else 12
 
     x0 = torch.randn((M, HIDDEN), device=device, generator=gen).half()
+
+    # Split-N parity, once, before any timing: on a small projection every rank builds the
+    # same full weight, runs its shard through the exchange the timed steps use and compares
+    # the gathered rows with the unsharded product of the same kernel, bit for bit.
+    tp_parity = None
+    if world > 1 and not replica:
+        pgen = torch.Generator(device=device)
+        pgen.manual_seed(777)
+        pic, poc, pk = 1024, 128 * world * 2, 2
+        pcode = torch.randint(-2**31, 2**31 - 1, (pic // 16, poc // 16, 8 * pk), dtype=torch.int32,
+                              device=device, generator=pgen)
+        pvec = lambda n: (torch.randn(n, device=device, generator=pgen) * 0.02).half().float()
+        full = dense.EschaWeight.from_device(pcode, pvec(pic), pvec(poc))
+        px = torch.randn((1, pic), device=device, generator=pgen).half()
+        want = dense.EschaLinear(full)(px)
+        mine = full.shard_out(rank, world)
+        if pg is not None:
+            pbuf = pg.empty((1, poc), torch.float16)
+            msl.coded_projections(px, [mine.code], [mine.rin], [mine.rout], pk, pic, [mine.OC],
+                                  input_mode=msl.INPUT_RAW, rs=msl.RS,
+                                  gather=[(pbuf, rank * mine.OC)])
+            pg.barrier()
+            got = pbuf.local
+        else:
+            from escha_mlx_b200 import sharding as _sh
+            got = _sh.all_gather_columns(dense.EschaLinear(mine)(px))
+        torch.cuda.synchronize()
+        same = torch.tensor([1.0 if torch.equal(got, want) else 0.0], device=device)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        tp_parity = "bit-exact" if same.item() == 1.0 else "MISMATCH"
 
     if args.only:
         # profiling aid: K launches of one projection's product kernel, rotating weight sets
@@ -836,26 +876,29 @@ def main() -> None:
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
-        value = LAYER_BYTES * args.steps / (ms_total * 1e-3) / 1e9
-        e2e = LAYER_BYTES * args.steps / (ms_e2e * 1e-3) / 1e9
+        # replicas: every rank streams the whole layer for its own rows, so the job's bytes
+        # and rows per step are `world` times one rank's
+        job = world if replica else 1
+        value = job * LAYER_BYTES * args.steps / (ms_total * 1e-3) / 1e9
+        e2e = job * LAYER_BYTES * args.steps / (ms_e2e * 1e-3) / 1e9
         launches = 7 * reps
-        achieved = (LAYER_BYTES / world) * reps / (ms_gemv * 1e-3) / 1e9   # per GPU
+        achieved = (LAYER_BYTES / shards) * reps / (ms_gemv * 1e-3) / 1e9   # per GPU
         # DRAM bytes per GEMV launch from the ncu captures summarised under profiles/
         # (gemv_mma_gate_proj_k3_m1.md: 33,567,744 B read for 33,423,360 B of code, 1.004x;
         # gemv_mma_q_proj_k2_m1.md: 7,962,880 B for 7,864,320 B, 1.013x; no writes to DRAM).
         # Traffic grows with the code bytes, so the other projections are scaled by their rate's
         # factor; this is the average over the seven launches timed above, per GPU.
         traffic = (sum(ic * oc * k // 8 * (1.013 if k == 2 else 1.004) for _, ic, oc, k in LAYER)
-                   / 7 / world) if M == 1 else None
-        flops_step = 2.0 * M * sum(ic * oc for _, ic, oc, _ in LAYER)
+                   / 7 / shards) if M == 1 else None
+        flops_step = 2.0 * job * M * sum(ic * oc for _, ic, oc, _ in LAYER)
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "weak" if replica else "strong", "vs_baseline": None,
             "dtype": "f16 weights, f32 accumulate", "data": "synthetic",
             "config": workload_config(args, n_sets),
             "pct_of_hbm_peak": 100.0 * value / (peak * world),
-            "tokens_per_s": M * args.steps / (ms_total * 1e-3),
+            "tokens_per_s": job * M * args.steps / (ms_total * 1e-3),
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": M * HIDDEN * 2,
                     "d2h_bytes_per_step": M * HIDDEN * 2},
             "gpu_launches": launches_per_step * args.steps,
@@ -864,7 +907,7 @@ def main() -> None:
                          "kernel": "gemv_mma_kernel (coded GEMV + fused output transform)",
                          "launches_timed": launches,
                          "avg_launch_us": ms_gemv * 1e3 / launches,
-                         "algorithmic_bytes_per_launch_avg": LAYER_BYTES / world / 7,
+                         "algorithmic_bytes_per_launch_avg": LAYER_BYTES / shards / 7,
                          "timed": "seven projections launched one by one (CUDA-graph replays)",
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
             "clocks": clocks.summary(),
@@ -894,18 +937,22 @@ def main() -> None:
             # tile at 2 bits, 46 at 3: profiles/issue_rates.md) over the issue slots the step
             # had, one per sub-partition and clock at the sampled SM clock
             tiles = {k: sum(ic * oc // 256 for _, ic, oc, kk in LAYER if kk == k) for k in (2, 3)}
-            need = (41 * tiles[2] + 46 * tiles[3]) / world
+            need = (41 * tiles[2] + 46 * tiles[3]) / shards
             mhz = line["clocks"].get("sm_mhz") or 1965.0
             have = 4 * 148 * mhz * 1e6 * (ms_total * 1e-3 / args.steps)
             line["roofline"]["issue_frac"] = need / have
             line["roofline"]["issue_note"] = ("minimal decode warp instructions per step / issue "
                                               "slots in the step time (4 per SM per clock)")
-        if world > 1:
+        if world > 1 and replica:
+            line["config"]["parallelism"] = f"{world} row replicas (full weights per GPU, no exchange)"
+            line["config"]["global_batch"] = world * M
+        elif world > 1:
             line["config"]["exchange"] = ("GEMV epilogue stores into every GPU's gathered row "
                                           "(peer memory) + barrier kernel"
                                           if pg is not None and not tc_shards
                                           else "NCCL all-gather per projection")
             line["peer_barrier_gave_up"] = bool(barrier_gave_up)   # must be false for a valid run
+            line["tp_parity"] = tp_parity
         if tensor_leg:
             tpeak, tkind = measured_peak_tflops()
             tf = flops_step / world * reps / (ms_gemv * 1e-3) / 1e12      # per GPU

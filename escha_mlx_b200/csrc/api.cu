@@ -330,7 +330,8 @@ int escha_coded_gemv_splits(int IC, int OC, int njobs, int sm_count) {
         // (three CTAs of the kernel fit on an SM) without exceeding them, at least two
         // 128-channel blocks per split.  Measured on the dense 27B-class shapes this beats
         // "two CTAs per SM" by 7 to 20 percent per projection.  Depends on the shape only.
-        const long smax = nblk >= 2 ? nblk / 2 : 1;
+        static const int min_blocks_grid = [] { const char* v = std::getenv("ESCHA_B200_SPLIT_MIN_BLOCKS"); return v && *v ? std::atoi(v) : 2; }();
+        const long smax = nblk >= min_blocks_grid ? nblk / min_blocks_grid : 1;
         long s = 3L * sm_count / units;
         if (s > smax) s = smax;
         if (s < 1) s = 1;

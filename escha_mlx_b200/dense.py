@@ -271,12 +271,14 @@ def _joint_prefill(linears) -> bool:
     return sum(lin._w.OC // 128 for lin in linears) <= msl.sm_count()
 
 
-def project_many(linears, x: torch.Tensor):
+def project_many(linears, x: torch.Tensor, one_wave: bool = False):
     """Evaluate up to eight coded projections of the same input (Q/K/V, gate/up, or
     everything that reads one hidden state) in one launch at decode batch sizes,
     whatever their rates.  Outputs equal ``[lin(x) for lin in linears]`` bit for
     bit: every projection keeps the split factor and the summation order it has
-    when called alone."""
+    when called alone.  ``one_wave=True`` gives that identity up for speed: split factors
+    are chosen for each launch as a whole (``msl.wave_splits``), so sums are formed in an
+    order of their own (deterministic, within the path's tolerance of the separate calls)."""
     linears = list(linears)
     shape = x.shape
     rows = x.reshape(-1, shape[-1])
@@ -288,7 +290,7 @@ def project_many(linears, x: torch.Tensor):
         outs: dict[int, torch.Tensor] = {}
         for k in sorted({lin.K for lin in linears}):
             idx = [i for i, lin in enumerate(linears) if lin.K == k]
-            for i, y in zip(idx, project_many([linears[i] for i in idx], x)):
+            for i, y in zip(idx, project_many([linears[i] for i in idx], x, one_wave)):
                 outs[i] = y
         return [outs[i] for i in range(len(linears))]
     joint = (
@@ -316,13 +318,15 @@ def project_many(linears, x: torch.Tensor):
     rows = rows.contiguous()
     ws = [lin._w for lin in linears]
     codes, routs, ocs = [w.code for w in ws], [w.rout for w in ws], [w.OC for w in ws]
+    splits = msl.wave_splits(first._w.IC, ocs) if one_wave else None
     if first._single_launch(rows.shape[0]):
         outs = msl.coded_projections(rows, codes, [w.rin for w in ws], routs, [w.K for w in ws],
-                                     first._w.IC, ocs, input_mode=msl.INPUT_RAW, rs=RS)
+                                     first._w.IC, ocs, input_mode=msl.INPUT_RAW, rs=RS,
+                                     splits=splits)
     else:
         xhs = msl.dense_scaled_had_many(rows, [w.rin for w in ws], RS)
         outs = msl.coded_projections(xhs[0], codes, None, routs, [w.K for w in ws], first._w.IC,
-                                     ocs, rs=RS, xs=xhs)
+                                     ocs, rs=RS, xs=xhs, splits=splits)
     return [lin._finish(y, shape, x.dtype) for lin, y in zip(linears, outs)]
 
 

@@ -64,6 +64,32 @@ def use_dense_mat() -> bool:
     return gemv_family() == "mma"
 
 
+def wave_splits(IC: int, OCs, njobs: int = 1) -> list[int]:
+    """Split factors for projections that share ONE launch, chosen for the launch as a whole:
+    the launch's CTAs (output blocks x splits, summed over the projections) should fill the
+    GPU's resident slots once, where ``split_k_for`` fills them once per projection.  The sums
+    of a projection then differ in their last bits from those of a launch of its own (each
+    composition is still bit-reproducible); measured on the 27B-class layer at one row, q/k/v/o
+    in one launch take 1192 CTAs of 2 to 4 input blocks with per-projection factors and 416
+    CTAs of 10 blocks this way, 119 against 126 us per layer step.  A launch too wide for one
+    wave gets the fewest waves it can fill (with a single, underfilled wave for gate/up the
+    step took 144 us)."""
+    blocks = sum(oc // 128 for oc in OCs) * max(1, njobs)
+    smax = max(1, (IC // 128) // 2)
+    slots = 3 * sm_count()
+    # the fewest waves whose slots the launch can fill to 85%: one wave for q/k/v/o of the
+    # 27B-class layer (104 blocks x 4 = 416 of 444 slots), two for gate/up (272 x 3 = 816 of 888)
+    s = smax
+    for waves in range(1, 9):
+        cand = min(smax, (waves * slots) // max(1, blocks))
+        if cand >= 1 and blocks * cand >= 0.85 * waves * slots:
+            s = cand
+            break
+        if cand == smax:
+            break
+    return [s] * len(OCs)
+
+
 def kt_block() -> int:
     """kt tiles per pipeline stage of the tensor-core kernel (fixed at 8 = one
     128-channel block; the reference stages a configurable count, :1229-1242)."""
@@ -372,6 +398,10 @@ def coded_projections(x: torch.Tensor, codes, rins, routs, K: int, IC: int, OCs,
     if splits is None:
         est = 1 if dense else expected_jobs(pr, E)
         per = [split_k_for(pr, oc, IC // 16, est) for oc in OCs]
+    elif isinstance(splits, (list, tuple)):
+        per = [max(1, min(int(v), IC // 128)) for v in splits]
+        if len(per) != n:
+            raise ValueError(f"{len(per)} split factors for {n} projections")
     else:
         per = [max(1, min(int(splits), IC // 128))] * n
     s = max(per)
