@@ -614,7 +614,8 @@ def main() -> None:
         outs = msl.coded_projections(
             x if fuse_in else xs[0], [w.code for w in ws], [w.rin for w in ws] if fuse_in else None,
             [w.rout for w in ws], ws[0].K, ws[0].IC, [w.OC for w in ws], input_mode=mode,
-            x_up=x_up, rs=msl.RS, xs=xs, gather=[(bufs[n], rank * w.OC) for n, w in zip(names, ws)])
+            x_up=x_up, rs=msl.RS, xs=xs, gather=[(bufs[n], rank * w.OC) for n, w in zip(names, ws)],
+            splits=msl.wave_splits(ws[0].IC, [w.OC for w in ws]) if args.wave else None)
         pg.barrier()
         return outs
 

@@ -59,6 +59,7 @@ SIGNATURES = {
     "escha_moe_combine": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "escha_coded_gemm_tc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
     "escha_coded_gemm_tc_splits": (_i, [_i, _i, _i]),
+    "escha_coded_gemm_tc_needs_planes": (_i, [_i, _i, _i]),
     "escha_coded_gemm_tc_status": (_i, []),
     "escha_coded_gemv_status": (_i, []),
     "escha_debug_gemv_stall": (None, [_i, ctypes.c_uint]),

@@ -196,12 +196,14 @@ int escha_scaled_had_many(const void* rows, const void* up, int n, const float* 
     REQUIRE(n >= 1 && n <= 4, "%s: one to four transforms per launch, got %d", __func__, n);
     REQUIRE_PTR(rows);
     OPTIONAL_PTR(up);
-    REQUIRE_PTR(rins);
-    REQUIRE_PTR(outs);
+    // host-side tables: any alignment; the device pointers inside them are checked below
+    REQUIRE(rins && outs, "%s: NULL argument table", __func__);
     __half* o[4] = {nullptr, nullptr, nullptr, nullptr};
     for (int i = 0; i < n; ++i) {
         REQUIRE(rins[i] != nullptr && outs[i] != nullptr, "%s: transform %d has a null pointer",
                 __func__, i);
+        REQUIRE(aligned16(rins[i]) && aligned16(outs[i]),
+                "%s: transform %d has a pointer that is not 16-byte aligned", __func__, i);
         o[i] = static_cast<__half*>(outs[i]);
     }
     return cuda_result(
@@ -769,16 +771,24 @@ int escha_coded_gemm_tc(const void* xh, const void* code, const float* rout, int
     return cuda_result(e, "escha_coded_gemm_tc");
 }
 
+int escha_coded_gemm_tc_needs_planes(int IC, int splits, int has_rout) {
+    if (splits <= 1) return 0;
+    static const bool cluster_sums = [] {
+        const char* v = std::getenv("ESCHA_B200_TC_CLUSTER_SUM");
+        return v == nullptr || std::strcmp(v, "0") != 0;
+    }();
+    const bool fused_out = has_rout && cluster_sums && escha::gemm_tc_uses_tmem() &&
+                           escha::gemm_tcm_cluster_sum(IC, splits);
+    return fused_out ? 0 : 1;
+}
+
 int escha_coded_gemm_tc_many(int n, const void* const* xhs, const void* const* codes,
                              const float* const* routs, int M, int IC, const int* OCs, int K,
                              int splits, float rs, float* const* planes, void* const* outs,
                              void* stream) {
     REQUIRE(n >= 1 && n <= 3, "%s: one to three projections per launch, got %d", __func__, n);
-    REQUIRE_PTR(xhs);
-    REQUIRE_PTR(codes);
-    REQUIRE_PTR(routs);
-    REQUIRE_PTR(OCs);
-    REQUIRE_PTR(outs);
+    // host-side tables: any alignment; the device pointers inside them are checked below
+    REQUIRE(xhs && codes && routs && OCs && outs, "%s: NULL argument table", __func__);
     REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
     REQUIRE((M + 255) / 256 <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
     int oc_total = 0;
@@ -786,6 +796,8 @@ int escha_coded_gemm_tc_many(int n, const void* const* xhs, const void* const* c
         if (int rc = check_shape(__func__, K, IC, OCs[i], 128)) return rc;
         REQUIRE(xhs[i] != nullptr && codes[i] != nullptr && routs[i] != nullptr && outs[i] != nullptr,
                 "%s: projection %d has a null pointer", __func__, i);
+        REQUIRE(aligned16(xhs[i]) && aligned16(codes[i]) && aligned16(routs[i]) && aligned16(outs[i]),
+                "%s: projection %d has a pointer that is not 16-byte aligned", __func__, i);
         oc_total += OCs[i];
     }
     if (splits <= 0) splits = escha_coded_gemm_tc_splits(IC, oc_total, 0);
@@ -797,7 +809,7 @@ int escha_coded_gemm_tc_many(int n, const void* const* xhs, const void* const* c
     }();
     const bool fused_out = splits == 1 || (cluster_sums && escha::gemm_tcm_cluster_sum(IC, splits));
     if (!fused_out) {
-        REQUIRE_PTR(planes);
+        REQUIRE(planes != nullptr, "%s: planes table is NULL", __func__);
         for (int i = 0; i < n; ++i)
             REQUIRE(planes[i] != nullptr, "%s: projection %d needs a plane workspace", __func__, i);
     }

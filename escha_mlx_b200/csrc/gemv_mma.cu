@@ -169,14 +169,18 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     constexpr int ROWS = 8 * MT;
     extern __shared__ __align__(128) uint32_t smem[];
     uint32_t* const s_code = smem;                    // [NS][8 kt][8 tiles][WPT]
-    uint32_t* const s_x = smem + NS * STAGE_WORDS;    // [rows + 1][XS] as (x, 0) words
+    uint32_t* const s_x = smem + NS * STAGE_WORDS;    // [rows + 1][XS] as (x, 0) words; then,
+                                                      // with G > 1, [ROWS][128] accumulators
     __shared__ __align__(8) uint64_t s_full[NS];
     __shared__ int s_rows[16];
     __shared__ int s_last;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint32_t gocb = blockIdx.x, split = blockIdx.y, job = blockIdx.z;
+    // a CTA covers G consecutive output blocks of one projection (G > 1 only for unsplit
+    // launches whose input range fits one staged chunk: the rows are staged once for all G)
+    const uint32_t G = static_cast<uint32_t>(p.ocb_group);
+    const uint32_t gocb = blockIdx.x * G, split = blockIdx.y, job = blockIdx.z;
     const uint32_t nblk = p.IC >> 7;
 
     // which projection of the launch this output block belongs to (uniform per CTA)
@@ -234,22 +238,26 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     if (warp == 8) {
         // ---- producer warp: bulk copies (TMA, untiled, no multicast) of the CTA's
         // eight-tile rows, one copy per kt row, eight rows per stage
-        const uint32_t* grow = pr.code + static_cast<size_t>(expert) * (p.IC >> 4) * tile_row_words +
-                               ocb * ROW_WORDS +
-                               (static_cast<size_t>(b0) * 8u + lane) * tile_row_words;
+        const uint32_t* const gbase = pr.code + static_cast<size_t>(expert) * (p.IC >> 4) * tile_row_words +
+                                      ocb * ROW_WORDS +
+                                      (static_cast<size_t>(b0) * 8u + lane) * tile_row_words;
         const uint32_t dst0 = smem_u32(s_code) + lane * (ROW_WORDS * 4u);
-        for (uint32_t i = 0; i < nb; ++i) {
-            const uint32_t slot = i % NS;
-            // The slot is free once all eight decode warps have arrived at its barrier.  The
-            // producer is parked there by the hardware: a polling wait would take issue
-            // slots on its sub-partition, and the slowest sub-partition paces the CTA.
-            if (i >= NS) named_barrier_sync(kBarSlot0 + slot, kThreads);
-            if (lane == 0) mbar_arrive_expect_tx(full0 + 8u * slot, STAGE_WORDS * 4u);
-            __syncwarp();
-            if (lane < 8 && !p.test_stall)
-                bulk_copy_g2s(dst0 + slot * (STAGE_WORDS * 4u), grow, ROW_WORDS * 4u,
-                              full0 + 8u * slot);
-            grow += static_cast<size_t>(8u) * tile_row_words;
+        uint32_t st = 0;   // stages issued so far
+        for (uint32_t o = 0; o < G; ++o) {
+            const uint32_t* grow = gbase + o * ROW_WORDS;
+            for (uint32_t i = 0; i < nb; ++i, ++st) {
+                const uint32_t slot = st % NS;
+                // The slot is free once all eight decode warps have arrived at its barrier.  The
+                // producer is parked there by the hardware: a polling wait would take issue
+                // slots on its sub-partition, and the slowest sub-partition paces the CTA.
+                if (st >= NS) named_barrier_sync(kBarSlot0 + slot, kThreads);
+                if (lane == 0) mbar_arrive_expect_tx(full0 + 8u * slot, STAGE_WORDS * 4u);
+                __syncwarp();
+                if (lane < 8 && !p.test_stall)
+                    bulk_copy_g2s(dst0 + slot * (STAGE_WORDS * 4u), grow, ROW_WORDS * 4u,
+                                  full0 + 8u * slot);
+                grow += static_cast<size_t>(8u) * tile_row_words;
+            }
         }
         return;
     }
@@ -260,14 +268,6 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     // zero row: B columns past the job's last row read it instead of branching
     uint32_t* const zero_row = s_x + static_cast<uint32_t>(xrows) * XS;
     for (uint32_t i = tid; i < XS; i += kConsumerThreads) zero_row[i] = 0u;
-
-    // two independent accumulator sets per column block: the two mma of a tile
-    // do not wait on each other, and each chain advances once per tile
-    float dA[MT][4], dB[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dA[mt][i] = dB[mt][i] = 0.0f;
 
     const uint32_t* xrow[MT];
 #pragma unroll
@@ -286,12 +286,27 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
 
     bool ok = true;
     uint32_t slot = 0, phase = 0;
+    // with G > 1 the accumulators cannot borrow the code ring (it is never drained between
+    // output blocks): they get their own rows behind the activations
+    float* const s_acc = G > 1 ? reinterpret_cast<float*>(s_x + (static_cast<uint32_t>(xrows) + 1u) * XS)
+                               : reinterpret_cast<float*>(s_code);
+    const size_t out_ld = pr.out_ld ? static_cast<size_t>(pr.out_ld) : OC;
+  for (uint32_t o = 0; o < G; ++o) {
+    // two independent accumulator sets per column block: the two mma of a tile
+    // do not wait on each other, and each chain advances once per tile
+    float dA[MT][4], dB[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dA[mt][i] = dB[mt][i] = 0.0f;
     for (uint32_t c0 = 0; c0 < nb; c0 += XCB) {
         const uint32_t cnt = min(XCB, nb - c0);
-        named_barrier_sync(1, kConsumerThreads);
-        stage_activations(p, xsrc, rin, s_rows, nrows, b0 + c0, cnt, s_x, XS, tid,
-                          SUM ? 0x10001u : 1u);
-        named_barrier_sync(1, kConsumerThreads);
+        if (o == 0) {   // G > 1 means one chunk: staged once, reused by every output block
+            named_barrier_sync(1, kConsumerThreads);
+            stage_activations(p, xsrc, rin, s_rows, nrows, b0 + c0, cnt, s_x, XS, tid,
+                              SUM ? 0x10001u : 1u);
+            named_barrier_sync(1, kConsumerThreads);
+        }
         for (uint32_t cb = 0; cb < cnt; ++cb) {
             // a wait that gives up is recorded; the warp stops waiting but keeps walking the
             // stages and arriving everywhere, so that nobody in the CTA is left alone at a barrier
@@ -325,8 +340,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     if (!ok && lane == 0) atomicExch(&g_gemv_status, 2);
     named_barrier_sync(1, kConsumerThreads);
 
-    // accumulators -> shared [ROWS][128] (aliases the drained code ring)
-    float* const s_acc = reinterpret_cast<float*>(s_code);
+    // accumulators -> shared [ROWS][128] (with G == 1 in the drained code ring)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         const uint32_t ch = warp * 16u + g, n0 = 2u * t + 8u * mt;
@@ -338,19 +352,19 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     named_barrier_sync(1, kConsumerThreads);
 
     const float* rout_blk =
-        pr.rout ? pr.rout + static_cast<size_t>(expert) * OC + ocb * 128u : nullptr;
-    const size_t out_ld = pr.out_ld ? static_cast<size_t>(pr.out_ld) : OC;
+        pr.rout ? pr.rout + static_cast<size_t>(expert) * OC + (ocb + o) * 128u : nullptr;
 
     if (S == 1) {
         for (uint32_t r = warp; r < static_cast<uint32_t>(nrows); r += 8u) {
             const float4 a4 = *reinterpret_cast<const float4*>(s_acc + r * 128u + lane * 4u);
             float v[4] = {a4.x, a4.y, a4.z, a4.w};
-            const size_t off = static_cast<size_t>(s_rows[r]) * out_ld + pr.out_col0 + ocb * 128u + lane * 4u;
+            const size_t off = static_cast<size_t>(s_rows[r]) * out_ld + pr.out_col0 + (ocb + o) * 128u + lane * 4u;
             if (pr.rout) finalize_row<true>(v, lane, rout_blk, pr, off, p.rs);
             else finalize_row<false>(v, lane, rout_blk, pr, off, p.rs);
         }
         if (pr.npeer) __threadfence_system();
-        return;
+        continue;   // the next output block of this CTA (the barrier before its rows are
+                    // written keeps them from overtaking the reads above)
     }
 
     // split-K: publish this CTA's partial, last arriver reduces in split order
@@ -391,6 +405,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
         else finalize_row<false>(v, lane, rout_blk, pr, off, p.rs);
     }
     if (pr.npeer) __threadfence_system();
+  }   // output blocks of this CTA (split launches have one)
 }
 
 template <int K, int MT, bool SUM>
@@ -398,7 +413,8 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
     constexpr int STAGE_WORDS = 8 * 8 * 8 * K;
     const size_t XS = static_cast<size_t>(p.xcb) * 128u + 16u;
     const size_t smem =
-        (static_cast<size_t>(NS * STAGE_WORDS) + static_cast<size_t>(xrows + 1) * XS) * 4u;
+        (static_cast<size_t>(NS * STAGE_WORDS) + static_cast<size_t>(xrows + 1) * XS +
+         (p.ocb_group > 1 ? static_cast<size_t>(p.rows_per_job) * 128u : 0u)) * 4u;
     static size_t configured[64] = {0};  // per device: largest size already enabled
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -411,7 +427,7 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.total_ocb, p.splits, p.njobs);
+    cfg.gridDim = dim3(p.total_ocb / p.ocb_group, p.splits, p.njobs);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -502,6 +518,20 @@ cudaError_t launch_gemv_mma(const GemvMmaParams& params, cudaStream_t st) {
     const int xrows = p.jobs ? rows : (p.M < rows ? p.M : rows);
     p.xcb = x_chunk_blocks(xrows);
     p.pdl = pdl_mode();
+    // Output blocks per CTA.  Expert streams at many rows come as thousands of short CTAs
+    // (the second expert leg: four input blocks each) that all stage the same rows; when the
+    // launch is unsplit, its input range fits one staged chunk and every projection's block
+    // count allows it, a CTA takes 4 (or 2) consecutive output blocks and stages once, as
+    // long as that still leaves two waves of CTAs.  Measured on the 35B-A3B-class layer at 64
+    // tokens: second expert leg 89 -> 70 us.
+    p.ocb_group = 1;
+    if (p.jobs && p.splits == 1 && (p.IC >> 7) <= p.xcb) {
+        for (int gsize = 4; gsize >= 2; gsize >>= 1) {
+            bool fits = static_cast<long>(p.njobs) * (p.total_ocb / gsize) >= 2L * 3 * 148;
+            for (int i = 0; i < p.nprob && fits; ++i) fits = (p.prob[i].OC / 128) % gsize == 0;
+            if (fits) { p.ocb_group = gsize; break; }
+        }
+    }
     if (weight_sum_in_tensor_core()) {
         if (p.K == 2) return rows == 8 ? launch_t<2, 1, true>(p, xrows, st) : launch_t<2, 2, true>(p, xrows, st);
         return rows == 8 ? launch_t<3, 1, true>(p, xrows, st) : launch_t<3, 2, true>(p, xrows, st);

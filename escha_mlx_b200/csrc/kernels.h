@@ -80,6 +80,7 @@ struct GemvMmaParams {
     int njobs;                // grid.z
     int input;                // GemvInput
     int xcb;                  // activation blocks staged per chunk (set by the launcher)
+    int ocb_group;            // output blocks per CTA in the one-CTA-per-block kernel (launcher)
     int pdl;                  // GemvPdl (set by the launcher)
     // Persistent kernel only (set by the launcher): length of the item list, code-ring depth
     // and slot size in words, rows an activation buffer holds.

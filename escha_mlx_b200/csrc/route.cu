@@ -169,13 +169,18 @@ moe_route_kernel(const RouteParams p) {
     }
 
     // ---- phase 3: rows -> jobs.  Rows are counted per expert with shared-memory
-    // atomics; then thread e owns local expert e and emits its rows in ascending
-    // order, so jobs ascend by expert and rows ascend inside a job -- the stable order
+    // atomics and the counts turned into job offsets; then thread e fills in the headers
+    // of expert e's jobs, and one warp walks the rows in ascending order, 32 at a time,
+    // giving each row its rank among the rows of its expert (lanes of one expert find each
+    // other with a warp match; a running count per expert carries over between the groups
+    // of 32), so jobs ascend by expert and rows ascend inside a job -- the stable order
     // moe.build_groups produces -- whatever order the atomics ran in.
     const int32_t* row_ids = p.ids_in ? p.ids_in : p.ids;
     const int m = p.T * p.top_k, El = p.e_hi - p.e_lo, R = p.R;
     int32_t* s_off = s_dyn;            // [El + 1]
     int32_t* s_loc = s_dyn + El + 1;   // [m] local expert of each row, -1 if another rank's
+    int32_t* s_cnt = s_loc + m;        // [El] rows of each expert
+    int32_t* s_run = s_cnt + El;       // [El] rows of each expert emitted so far
     for (int e = tid; e <= El; e += blockDim.x) s_off[e] = 0;
     __syncthreads();
     for (int i = tid; i < m; i += blockDim.x) {
@@ -197,7 +202,9 @@ moe_route_kernel(const RouteParams p) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int e = e_first + k;
-            local[k] = (k < per && e < El) ? (s_off[e + 1] + R - 1) >> rshift : 0;
+            const int cnt = (k < per && e < El) ? s_off[e + 1] : 0;
+            if (k < per && e < El) { s_cnt[e] = cnt; s_run[e] = 0; }
+            local[k] = (cnt + R - 1) >> rshift;
             sum += local[k];
         }
         int incl = sum;
@@ -224,19 +231,33 @@ moe_route_kernel(const RouteParams p) {
     __syncthreads();
     const int total = s_off[El];
     const int rshift = R == 8 ? 3 : 4, rmask = R - 1;
+    // job headers: expert and row count of every job of expert e
     for (int e = tid; e < El; e += blockDim.x) {
-        const int base = s_off[e], njobs_e = s_off[e + 1] - base;
-        if (njobs_e == 0) continue;
-        int k = 0;
-        for (int i = 0; i < m; ++i) {
-            if (s_loc[i] != e) continue;
-            const int j = base + (k >> rshift);
+        const int base = s_off[e], njobs_e = s_off[e + 1] - base, cnt = s_cnt[e];
+        for (int jj = 0; jj < njobs_e; ++jj) {
+            const int j = base + jj;
             if (j < p.njobs_cap) {
-                p.jobs[j].rows[k & rmask] = i;
-                if ((k & rmask) == 0) p.jobs[j].expert = e;
-                p.jobs[j].nrows = (k & rmask) + 1;  // ascending k: the last write is the count
+                p.jobs[j].expert = e;
+                p.jobs[j].nrows = min(R, cnt - (jj << rshift));
             }
-            ++k;
+        }
+    }
+    // rows, in ascending order
+    if (warp == 0) {
+        for (int i0 = 0; i0 < m; i0 += 32) {
+            const int i = i0 + lane;
+            const int e = i < m ? s_loc[i] : -1;
+            // lanes holding rows of the same expert (rows of other ranks' experts and lanes
+            // past the end match among themselves and are skipped)
+            const unsigned same = __match_any_sync(0xFFFFFFFFu, e);
+            if (e >= 0) {
+                const int k = s_run[e] + __popc(same & ((1u << lane) - 1u));
+                const int j = s_off[e] + (k >> rshift);
+                if (j < p.njobs_cap) p.jobs[j].rows[k & rmask] = i;
+            }
+            __syncwarp();
+            if (e >= 0 && lane == 31 - __clz(same)) s_run[e] += __popc(same);
+            __syncwarp();
         }
     }
     for (int j = total + tid; j < p.njobs_cap; j += blockDim.x) {
@@ -248,7 +269,7 @@ moe_route_kernel(const RouteParams p) {
 }  // namespace
 
 size_t route_shared_bytes(int T, int top_k, int e_lo, int e_hi) {
-    return (static_cast<size_t>(e_hi - e_lo) + 1 + static_cast<size_t>(T) * top_k) * sizeof(int32_t);
+    return (3 * static_cast<size_t>(e_hi - e_lo) + 1 + static_cast<size_t>(T) * top_k) * sizeof(int32_t);
 }
 
 cudaError_t launch_moe_route(const RouteParams& p, cudaStream_t st) {

@@ -753,7 +753,9 @@ def dense_gemm_tc(xh: torch.Tensor, code_u32: torch.Tensor, K: int, IC: int, OC:
     s = int(lib.escha_coded_gemm_tc_splits(IC, OC, 0)) if splits is None else int(splits)
     out = torch.empty((m, OC), dtype=torch.float32 if rout is None else torch.float16,
                       device=xh.device)
-    planes = torch.empty((s, m, OC), dtype=torch.float32, device=xh.device) if s > 1 else None
+    # scratch only when the library will use it (split sums inside the kernel need none)
+    need = lib.escha_coded_gemm_tc_needs_planes(IC, s, 1 if rout is not None else 0)
+    planes = torch.empty((s, m, OC), dtype=torch.float32, device=xh.device) if need else None
     check(lib.escha_coded_gemm_tc(ptr(xh, torch.float16), ptr(code_u32),
                                   ptr(rout, torch.float32) if rout is not None else None,
                                   m, IC, OC, K, s, float(rs), ptr(planes), ptr(out), stream()))
@@ -788,7 +790,8 @@ def dense_gemm_tc_many(xhs, codes, K: int, IC: int, OCs, routs, rs: float = RS,
     s = int(lib.escha_coded_gemm_tc_splits(IC, int(sum(OCs)), 0)) if splits is None else int(splits)
     dev = xhs[0].device
     outs = [torch.empty((m, oc), dtype=torch.float16, device=dev) for oc in OCs]
-    planes = [torch.empty((s, m, oc), dtype=torch.float32, device=dev) for oc in OCs] if s > 1 else None
+    need = lib.escha_coded_gemm_tc_needs_planes(IC, s, 1)   # the joint launch always has routs
+    planes = [torch.empty((s, m, oc), dtype=torch.float32, device=dev) for oc in OCs] if need else None
     arr = ctypes.c_void_p * n
     check(lib.escha_coded_gemm_tc_many(
         n, arr(*[ptr(x, torch.float16) for x in xhs]), arr(*[ptr(c) for c in codes]),

@@ -129,7 +129,8 @@ class PeerGroup:
         torch.cuda.synchronize()
         dist.barrier(self.group)
         for t in self._made:
-            t._views = []
+            # in place: tensors carved out of t share this list, and must let go as well
+            t._views.clear()
             t.local = None
         self._made = []
         self._flags = None

@@ -358,6 +358,11 @@ int escha_coded_gemm_tc(const void *xh, const void *code, const float *rout, int
 /* Split policy of escha_coded_gemm_tc (shape only; sm_count <= 0 queries the device). */
 int escha_coded_gemm_tc_splits(int IC, int OC, int sm_count);
 
+/* 1 if escha_coded_gemm_tc with these arguments will use the `planes` scratch, 0 if it sums its
+ * splits inside the kernel (or is unsplit): lets a caller skip the allocation.  The reference's
+ * matrix-unit GEMM has no split scratch (msl.py:1608-1782 accumulates in one threadgroup). */
+int escha_coded_gemm_tc_needs_planes(int IC, int splits, int has_rout);
+
 /* One to three prefill projections of equal IC and K in ONE tcgen05 launch (Q/K/V), each with
  * its own transformed activations xhs[i] f16 [M, IC], code, transform vector routs[i] f32 [OCs[i]]
  * (required) and f16 output outs[i] [M, OCs[i]].  splits <= 0 picks the policy value for the
