@@ -324,16 +324,9 @@ cudaError_t launch_tc(const GemmTcParams& p, cudaStream_t st) {
     const size_t smem = static_cast<size_t>(kAStages) * MT * kABytesPerMt +
                         static_cast<size_t>(kBStages) * kBBytes +
                         static_cast<size_t>(kCodeStages) * 4u * (8u * 8u * K * 4u) + 1024;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    static SmemLimit limit;
+    cudaError_t e = limit.ensure(gemm_tc_kernel<K, MT>, smem);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
-        e = cudaFuncSetAttribute(gemm_tc_kernel<K, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem));
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
-    }
     CUtensorMap xmap;
     e = encode_x_map(&xmap, p.xh, p.M, p.IC, 128 * MT);
     if (e != cudaSuccess) return e;

@@ -424,16 +424,9 @@ template <int K, int MT>
 cudaError_t launch_tcm(const GemmTcParams& p, const __half* const* xh_more, cudaStream_t st) {
     const size_t smem = static_cast<size_t>(kXStages) * 2u * MT * kXBytesPerMt +
                         static_cast<size_t>(kCodeStages) * 8u * (8u * 8u * K * 4u) + 1024;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    static SmemLimit limit;
+    cudaError_t e = limit.ensure(gemm_tcm_kernel<K, MT>, smem);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
-        e = cudaFuncSetAttribute(gemm_tcm_kernel<K, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem));
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
-    }
     CUtensorMap xmap[3];
     e = encode_x_map(&xmap[0], p.xh, p.M, p.IC, 128 * MT);
     if (e != cudaSuccess) return e;

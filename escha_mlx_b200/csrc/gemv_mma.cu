@@ -415,17 +415,9 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
     const size_t smem =
         (static_cast<size_t>(NS * STAGE_WORDS) + static_cast<size_t>(xrows + 1) * XS +
          (p.ocb_group > 1 ? static_cast<size_t>(p.rows_per_job) * 128u : 0u)) * 4u;
-    static size_t configured[64] = {0};  // per device: largest size already enabled
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    static SmemLimit limit;   // per device: largest size already enabled
+    cudaError_t e = limit.ensure(gemv_mma_kernel<K, MT, SUM>, smem);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || smem > configured[dev]) {
-        e = cudaFuncSetAttribute(gemv_mma_kernel<K, MT, SUM>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem));
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = smem;
-    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.total_ocb / p.ocb_group, p.splits, p.njobs);
     cfg.blockDim = dim3(kThreads);

@@ -53,18 +53,12 @@ namespace escha {
 
 namespace {
 
-#ifndef ITEMQ
-#define ITEMQ 3
-#endif
-#ifndef STREAM_MINB
-#define STREAM_MINB 3
-#endif
 constexpr int kDecodeWarps = 8;
-constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kFeederWarp = 8;
 constexpr int kFinisherWarp = 9;
 constexpr int kStreamThreads = (kDecodeWarps + 2) * 32;
-constexpr int kItemQ = ITEMQ;    // item descriptors in flight per CTA: the one being decoded and the next
+constexpr int kStreamMinBlocks = 3;   // resident CTAs per SM the kernel is built for
+constexpr int kItemQ = 3;        // item descriptors in flight per CTA: the one being decoded and the next
                                  // (a CTA that claimed further ahead would sit on work others could do)
 constexpr int kXBufs = 3;        // activation buffers: one in use, one staged ahead, one draining
 constexpr int kLutBytes = 65536 * 2;
@@ -74,25 +68,6 @@ struct ItemDesc {
     int32_t pi, job, ocb, nocb, split, b0, nb, expert, nrows, K;
     int32_t rows[16];
 };
-
-// Bounded wait that does not poll: try_wait with a suspend-time hint parks the thread in
-// hardware until the phase completes or the hint (nanoseconds) runs out, so a waiting
-// warp takes no issue slots from the decode warps.  `limit` tries of about a microsecond.
-__device__ __forceinline__ bool mbar_wait_lim(uint32_t bar, uint32_t parity, uint32_t limit) {
-#ifdef STREAM_SPIN
-    for (uint32_t it = 0; it < limit * 64u; ++it)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-#endif
-    for (uint32_t it = 0; it < limit; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
-            : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
 
 // Bounded wait of the two service warps: test, then sleep about a microsecond.  They wait most
 // of the time (for a free ring slot, for a finished block) and nothing needs them within
@@ -207,7 +182,7 @@ __device__ __forceinline__ void stage_rows(const GemvMmaParams& p, const GemvPro
 
 // Everything the roles of a CTA share.
 struct Shared {
-    uint64_t full[8], empty[8];              // code ring (up to 8 stages)
+    uint64_t full[8];                        // code ring (up to 8 stages)
     uint64_t item_full[kItemQ], item_empty[kItemQ];
     uint64_t x_full[kXBufs], x_empty[kXBufs];
     uint64_t acc_full[2], acc_empty[2];      // a finished block's accumulators in s_acc
@@ -395,12 +370,7 @@ __device__ __forceinline__ bool item_block(const GemvMmaParams& p, Shared& sh, c
             if (live && ok && !mbar_try_wait(full0 + rp.slot8, rp.phase) &&
                 !mbar_wait_slow(full0 + rp.slot8, rp.phase, limit)) ok = false;
             decode_block<K, MT, NLUT>(wa0 + rp.slot_off, wb0 + rp.slot_off, xr, dA, dB, lc, muls, hmask, hxor, lut);
-#ifdef FEEDER_SPIN
-            __syncwarp();
-            if (live) mbar_arrive_lane0(smem_u32(sh.empty) + rp.slot8, lane);
-#else
             if (live) named_barrier_arrive(kBarSlot0 + rp.slot, kBarThreads);   // done with the stage
-#endif
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) xr[mt] += 128;
             rp.slot_off += SLOT;
@@ -416,7 +386,7 @@ __device__ __forceinline__ bool item_block(const GemvMmaParams& p, Shared& sh, c
 }
 
 template <int MT, int NLUT>
-__global__ void __launch_bounds__(kStreamThreads, NLUT ? 1 : STREAM_MINB)
+__global__ void __launch_bounds__(kStreamThreads, NLUT ? 1 : kStreamMinBlocks)
 gemv_stream_kernel(const __grid_constant__ GemvMmaParams p) {
     constexpr int ROWS = 8 * MT;
     extern __shared__ __align__(128) uint32_t smem[];
@@ -430,7 +400,7 @@ gemv_stream_kernel(const __grid_constant__ GemvMmaParams p) {
     uint32_t* const s_lut = reinterpret_cast<uint32_t*>(s_acc + 2 * ROWS * 128);   // 128 KiB when NLUT
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t full0 = smem_u32(sh.full), empty0 = smem_u32(sh.empty);
+    const uint32_t full0 = smem_u32(sh.full);
     const uint32_t ifull0 = smem_u32(sh.item_full), iempty0 = smem_u32(sh.item_empty);
     const uint32_t xfull0 = smem_u32(sh.x_full), xempty0 = smem_u32(sh.x_empty);
     const uint32_t accfull0 = smem_u32(sh.acc_full), accempty0 = smem_u32(sh.acc_empty);
@@ -439,7 +409,6 @@ gemv_stream_kernel(const __grid_constant__ GemvMmaParams p) {
     if (tid == 0) {
         for (uint32_t s = 0; s < NS; ++s) {
             mbar_init(full0 + 8u * s, 1u);               // the producer's arrive.expect_tx
-            mbar_init(empty0 + 8u * s, kDecodeWarps);    // one arrival per decode warp
         }
         for (int q = 0; q < kItemQ; ++q) {
             mbar_init(ifull0 + 8u * q, 1u);
@@ -480,11 +449,7 @@ gemv_stream_kernel(const __grid_constant__ GemvMmaParams p) {
         // free right now and reports whether it did.
         auto issue_stage = [&](const uint32_t* grow, uint32_t row_bytes) {
             // the slot is free once all eight decode warps have arrived at its barrier
-#ifdef FEEDER_SPIN
-            if (lap > 0 && !mbar_wait(empty0 + 8u * rslot, (lap - 1u) & 1u)) ok = false;
-#else
             if (lap > 0) named_barrier_sync(kBarSlot0 + rslot, kBarThreads);
-#endif
             if (lane == 0) mbar_arrive_expect_tx(full0 + 8u * rslot, 8u * row_bytes);
             __syncwarp();
             if (lane < 8 && p.test_stall != 1)
@@ -740,21 +705,14 @@ gemv_stream_kernel(const __grid_constant__ GemvMmaParams p) {
 // ---- host side
 
 // Shared memory per CTA that keeps three CTAs on an SM (228 KiB per SM, 1 KiB reserved per CTA).
-constexpr size_t kSmemBudget3 = (228 / STREAM_MINB - 2) * 1024;
+constexpr size_t kSmemBudget3 = (228 / kStreamMinBlocks - 2) * 1024;
 constexpr size_t kSmemBudget1 = 226 * 1024;
 
 template <int MT, int NLUT>
 cudaError_t launch_stream_t(const GemvMmaParams& p, size_t smem, int grid, cudaStream_t st) {
-    static size_t configured[64] = {0};  // per device: largest size already enabled
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    static SmemLimit limit;   // per device: largest size already enabled
+    cudaError_t e = limit.ensure(gemv_stream_kernel<MT, NLUT>, smem);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || smem > configured[dev]) {
-        e = cudaFuncSetAttribute(gemv_stream_kernel<MT, NLUT>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = smem;
-    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kStreamThreads);
@@ -825,7 +783,7 @@ cudaError_t launch_gemv_stream(const GemvMmaParams& params, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) sm_count[dev] = sms;
     }
-    const int ctas = (nlut ? 1 : STREAM_MINB) * sms;
+    const int ctas = (nlut ? 1 : kStreamMinBlocks) * sms;
 
     // rows an activation buffer holds, and blocks per staged chunk: about 10 KiB per buffer
     p.xrows = p.jobs ? ROWS : (p.M < ROWS ? p.M : ROWS);

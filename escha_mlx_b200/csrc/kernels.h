@@ -5,7 +5,31 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 namespace escha {
+
+// Dynamic shared memory limit of one kernel, raised at most once per device and size.  The
+// launchers keep one of these per kernel instantiation; check and update happen under its
+// lock, so host threads launching on different streams cannot leave the attribute below the
+// size another thread has recorded.
+struct SmemLimit {
+    std::mutex mu;
+    size_t have[64] = {0};
+    template <class Kernel>
+    cudaError_t ensure(Kernel kernel, size_t smem) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev >= 0 && dev < 64 && smem <= have[dev]) return cudaSuccess;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+        if (e == cudaSuccess && dev >= 0 && dev < 64) have[dev] = smem;
+        return e;
+    }
+};
+
 
 // One unit of row work for the tensor-core GEMV: up to 16 rows that share one
 // code stream (one expert).  Built on the device by the grouping kernel for the

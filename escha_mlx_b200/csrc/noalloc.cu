@@ -43,6 +43,7 @@ struct DeviceSlot {
     void* base = nullptr;  // resolved device address of g_static_scratch on this device
 };
 DeviceSlot g_slots[64];
+std::mutex g_slots_mu;   // the one-time set-up below may be reached from several host threads
 
 }  // namespace
 
@@ -79,6 +80,7 @@ extern "C" int escha_coded_gemv_static(const void* xh, const void* code, const f
         return ESCHA_EINVAL;
     }
     DeviceSlot& slot = g_slots[dev];
+    std::unique_lock<std::mutex> setup_lock(g_slots_mu);
     if (slot.base == nullptr) {
         // one-time set-up for this device, with this device current
         void* ptr = nullptr;
@@ -95,6 +97,7 @@ extern "C" int escha_coded_gemv_static(const void* xh, const void* code, const f
         }
         slot.base = ptr;
     }
+    setup_lock.unlock();
     return escha::coded_gemv_with_scratch(xh, code, rout, M, IC, OC, K, splits, rs,
                                          static_cast<int32_t*>(slot.base),
                                          reinterpret_cast<float*>(static_cast<unsigned char*>(slot.base) +

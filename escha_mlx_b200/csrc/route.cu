@@ -276,15 +276,10 @@ cudaError_t launch_moe_route(const RouteParams& p, cudaStream_t st) {
     const int n_rows = (p.ids_in ? 0 : p.E) + (p.shg_w ? 1 : 0);
     const dim3 grid(n_rows > 0 ? n_rows : 1, (p.T + 7) / 8);
     const size_t smem = route_shared_bytes(p.T, p.top_k, p.e_lo, p.e_hi);
-    static size_t configured[64] = {0};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || smem > configured[dev])) {
-        e = cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem));
+    static SmemLimit limit;
+    if (smem > 48 * 1024) {
+        const cudaError_t e = limit.ensure(moe_route_kernel, smem);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
     return launch_dependent(moe_route_kernel, grid, dim3(256), smem, st, p);
 }
