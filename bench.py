@@ -86,32 +86,47 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int) -> None:
-        self.gpu = gpu_index
+    def __init__(self, gpus, active: bool = True) -> None:
+        """`gpus`: one index or a list (rank 0 of a multi-rank run samples every GPU of the job
+        with one nvidia-smi; the other ranks pass active=False and start nothing: one
+        nvidia-smi per rank took seconds to come up on an 8-GPU box and sampled nothing)."""
+        self.gpus = [gpus] if isinstance(gpus, int) else list(gpus)
+        self.active = active
         self.rows: list[list[str]] = []
         self.proc = None
+        self.closing = False
 
     def __enter__(self):
+        if not self.active:
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "20", "-i", str(self.gpu)],
+                 "-lms", "20", "-i", ",".join(str(g) for g in self.gpus)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
+            # the timed region starts only once the sampler delivers (bounded: 10 s)
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 10.0 and self.proc.poll() is None:
+                time.sleep(0.01)
         except OSError:
             self.proc = None
         return self
 
     def _pump(self):
         for line in self.proc.stdout:
+            if self.closing:
+                break
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 8:
                 self.rows.append(parts)
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
+            if len(self.rows) < 2 * len(self.gpus):
+                time.sleep(0.05)          # a region shorter than the sampling period: one more sample
+            self.closing = True
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -306,7 +321,7 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
         g.replay()
     sync_all()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(list(range(world)) if world > 1 else local_rank, active=(rank == 0)) as clocks:
         sync_all()
         ev0.record(stream)
         for _ in range(replays):
@@ -384,15 +399,13 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
         g.close()
         for layer in layers:
             layer.block._peer_bufs = {}
-        del layers
+        del layers, pass_, g
         if pg is not None:
             pg.close()
         dist.barrier()
         dist.destroy_process_group()
         sys.stdout.flush()
         sys.stderr.flush()
-        if os.environ.get("ESCHA_BENCH_EXIT") != "plain":
-            os._exit(0)     # see the note at the end of main()
 
 
 def moe_legs(device, token_counts=(1, 8, 64), replays: int = 10) -> dict:
@@ -753,7 +766,7 @@ def main() -> None:
     # the K-step region is timed `--repeats` times back to back; the line reports the median
     # repeat and how far the first and the last lie from it (drift control)
     rep_ms = []
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(list(range(world)) if world > 1 else local_rank, active=(rank == 0)) as clocks:
         for _ in range(max(1, args.repeats)):
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             sync_all()
@@ -1010,14 +1023,8 @@ def main() -> None:
         torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
-        # Everything is released and reported.  Leave without running interpreter and
-        # library finalisers: with CUDA IPC mappings having existed in the process, their
-        # order against the CUDA runtime's own teardown is not defined (seen as a crash
-        # after the last line of main on this software stack).
         sys.stdout.flush()
         sys.stderr.flush()
-        if os.environ.get("ESCHA_BENCH_EXIT") != "plain":   # plain: let the finalisers run (diagnosis)
-            os._exit(0)
 
 
 if __name__ == "__main__":

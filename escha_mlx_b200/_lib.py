@@ -35,6 +35,7 @@ SIGNATURES = {
     "escha_scaled_had_out_pair": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _vp, _vp]),
     "escha_had128": (_i, [_vp, ctypes.c_long, _vp, _vp]),
     "escha_w8a16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
+    "escha_w8a16_many": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "escha_q8_embed": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "escha_gemv_ref": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "escha_coded_gemv_workspace_bytes": (_sz, [_i, _i, _i, _i]),

@@ -264,6 +264,42 @@ int escha_w8a16(const void* x, const void* w8, const void* scale, int M, int N, 
         "escha_w8a16");
 }
 
+int escha_w8a16_many(const void* x, int n, const void* const* w8, const void* const* scale,
+                     const int* N, int Kd, int M, void* const* y, void* stream) {
+    REQUIRE(n >= 1 && n <= 4, "%s: 1..4 linears per launch, got %d", __func__, n);
+    REQUIRE(M >= 1, "%s: needs at least one row, got M=%d", __func__, M);
+    REQUIRE(Kd >= 64 && Kd % 64 == 0, "%s: input width must be a positive multiple of 64, got %d",
+            __func__, Kd);
+    REQUIRE_PTR(x);
+    REQUIRE(w8 != nullptr && scale != nullptr && N != nullptr && y != nullptr,
+            "%s: NULL table", __func__);
+    REQUIRE((M + 7) / 8 <= 65535, "%s: M=%d exceeds the launch grid", __func__, M);
+    escha::Q8Params q{};
+    q.x = static_cast<const __half*>(x);
+    q.M = M; q.Kd = Kd;
+    q.input = escha::kQ8InputPlain;
+    q.epilogue = escha::kQ8StorePlain;
+    q.nseg = n;
+    int blocks = 0;
+    for (int i = 0; i < n; ++i) {
+        REQUIRE(N[i] >= 16 && N[i] % 16 == 0,
+                "%s: output widths must be positive multiples of 16, got N[%d]=%d", __func__, i, N[i]);
+        REQUIRE(w8[i] != nullptr && scale[i] != nullptr && y[i] != nullptr,
+                "%s: NULL pointer in table entry %d", __func__, i);
+        REQUIRE((reinterpret_cast<uintptr_t>(w8[i]) & 15u) == 0,
+                "%s: w8[%d] must be 16-byte aligned", __func__, i);
+        q.seg_w8[i] = static_cast<const int8_t*>(w8[i]);
+        q.seg_scale[i] = static_cast<const __half*>(scale[i]);
+        q.seg_y[i] = static_cast<__half*>(y[i]);
+        q.seg_N[i] = N[i];
+        q.blk0[i] = blocks;
+        blocks += N[i] / 16;
+    }
+    q.blk0[n] = blocks;
+    q.w8 = q.seg_w8[0]; q.scale = q.seg_scale[0]; q.y = q.seg_y[0]; q.N = q.seg_N[0];
+    return cuda_result(escha::launch_w8a16_mma(q, as_stream(stream)), "escha_w8a16_many");
+}
+
 int escha_q8_embed(const int64_t* ids, const void* w8, const void* scale, int rows, int N, int Kd,
                    void* out, void* stream) {
     REQUIRE(rows >= 1 && N >= 1, "%s: empty input (rows=%d N=%d)", __func__, rows, N);

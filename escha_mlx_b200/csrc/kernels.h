@@ -163,6 +163,14 @@ struct Q8Params {
     const float* scores;      // [M * top_k]
     const float* gate_logit;  // [M]
     int top_k;
+    // several linears of one input in one launch (plain input and store only): nseg > 0 makes
+    // blockIdx.x pick its segment from blk0 (16-row blocks before each segment, ascending)
+    int nseg;
+    const int8_t* seg_w8[4];
+    const __half* seg_scale[4];
+    __half* seg_y[4];
+    int seg_N[4];
+    int blk0[5];
 };
 
 cudaError_t launch_lut_init(__half* lut, cudaStream_t st);

@@ -71,7 +71,17 @@ w8a16_mma_kernel(const Q8Params p) {
     __shared__ float s_red[8][16][8 * NT + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16;
+    // the linear this CTA belongs to (one unless several share the launch) and its 16 rows
+    const int8_t* w8 = p.w8;
+    const __half* scale = p.scale;
+    __half* yout = p.y;
+    int N = p.N, n0 = blockIdx.x * 16;
+    if (p.nseg > 0) {
+        int sg = 0;
+        while (sg + 1 < p.nseg && static_cast<int>(blockIdx.x) >= p.blk0[sg + 1]) ++sg;
+        w8 = p.seg_w8[sg]; scale = p.seg_scale[sg]; yout = p.seg_y[sg]; N = p.seg_N[sg];
+        n0 = (static_cast<int>(blockIdx.x) - p.blk0[sg]) * 16;
+    }
     const int r0 = blockIdx.y * (8 * NT);
     const int chunks = p.Kd >> 6;
     const int cbase = chunks / 8, crem = chunks % 8;
@@ -80,9 +90,9 @@ w8a16_mma_kernel(const Q8Params p) {
     grid_dependency_wait();
     const int c0 = warp * cbase + min(warp, crem), cn = cbase + (warp < crem ? 1 : 0);
 
-    const int8_t* wa_row = p.w8 + static_cast<size_t>(n0 + g) * p.Kd + 16 * t;
+    const int8_t* wa_row = w8 + static_cast<size_t>(n0 + g) * p.Kd + 16 * t;
     const int8_t* wb_row = wa_row + static_cast<size_t>(8) * p.Kd;
-    const __half2 sa = __half2half2(p.scale[n0 + g]), sb = __half2half2(p.scale[n0 + g + 8]);
+    const __half2 sa = __half2half2(scale[n0 + g]), sb = __half2half2(scale[n0 + g + 8]);
     int xrow[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) xrow[nt] = min(r0 + 8 * nt + g, p.M - 1);
@@ -139,9 +149,9 @@ w8a16_mma_kernel(const Q8Params p) {
 #pragma unroll
         for (int w = 1; w < 8; ++w) v = __fadd_rn(v, s_red[w][rr][j]);
         const __half y = __float2half_rn(v);
-        const size_t o = static_cast<size_t>(row) * p.N + n0 + rr;
+        const size_t o = static_cast<size_t>(row) * N + n0 + rr;
         if (EP == kQ8StorePlain) {
-            p.y[o] = y;
+            yout[o] = y;
         } else {
             // routed-expert combine for this (token, channel), then the gated add
             float comb = 0.0f;
@@ -166,7 +176,7 @@ template <int IN, int EP>
 cudaError_t launch_nt(const Q8Params& p, cudaStream_t st) {
     const int rows = p.M < 32 ? p.M : 32;
     const int nt = (rows + 7) / 8;
-    const dim3 grid(p.N / 16, (p.M + 8 * nt - 1) / (8 * nt));
+    const dim3 grid(p.nseg > 0 ? p.blk0[p.nseg] : p.N / 16, (p.M + 8 * nt - 1) / (8 * nt));
     switch (nt) {
         case 1: return launch_dependent(w8a16_mma_kernel<1, IN, EP>, grid, dim3(256), 0, st, p);
         case 2: return launch_dependent(w8a16_mma_kernel<2, IN, EP>, grid, dim3(256), 0, st, p);

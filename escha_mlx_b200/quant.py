@@ -82,6 +82,45 @@ def w8a16(x: torch.Tensor, w8: torch.Tensor, scale: torch.Tensor) -> torch.Tenso
     return y
 
 
+Q8_MANY_MAX = 4
+
+
+def w8a16_many(x: torch.Tensor, weights: list[tuple[torch.Tensor, torch.Tensor]]) -> list[torch.Tensor]:
+    """Several int8 linears of the same rows in one launch (1..4; output widths multiples of
+    16, input width a multiple of 64), each output bit-identical to its own `w8a16` call.
+    No reference counterpart: it issues one quantized matmul per linear (:129-143)."""
+    import ctypes
+    n = len(weights)
+    if not 1 <= n <= Q8_MANY_MAX:
+        raise ValueError(f"w8a16_many takes 1..{Q8_MANY_MAX} linears, got {n}")
+    m, kd = x.shape
+    for w8, _ in weights:
+        if w8.shape[1] != kd:
+            raise ValueError(f"input has {kd} channels, an int8 linear takes {w8.shape[1]}")
+    ys = [torch.empty((m, w8.shape[0]), dtype=torch.float16, device=x.device) for w8, _ in weights]
+    table = ctypes.c_void_p * n
+    check(lib.escha_w8a16_many(
+        ptr(x, torch.float16), n,
+        table(*[ptr(w8, torch.int8).value for w8, _ in weights]),
+        table(*[ptr(sc, torch.float16).value for _, sc in weights]),
+        (ctypes.c_int * n)(*[w8.shape[0] for w8, _ in weights]), kd, m,
+        table(*[ptr(y).value for y in ys]), stream()))
+    return ys
+
+
+def project_many_q8(linears: list["EschaQ8Linear"], x: torch.Tensor) -> list[torch.Tensor]:
+    """`[lin(x) for lin in linears]` in one launch when the shapes allow it (as `w8a16_many`),
+    otherwise one launch each."""
+    shape = x.shape
+    rows = x.reshape(-1, shape[-1]).to(torch.float16).contiguous()
+    ok = (1 <= len(linears) <= Q8_MANY_MAX and rows.shape[1] % 64 == 0
+          and all(l.out_features % 16 == 0 and l.in_features == rows.shape[1] for l in linears))
+    if not ok:
+        return [lin(x) for lin in linears]
+    ys = w8a16_many(rows, [(l._w8, l._scale) for l in linears])
+    return [y.reshape(*shape[:-1], l.out_features) for y, l in zip(ys, linears)]
+
+
 class EschaQ8Linear(torch.nn.Module):
     """An int8-weight linear with per-output-row scale (reference :129-143)."""
 

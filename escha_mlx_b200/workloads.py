@@ -87,9 +87,7 @@ class MoeLayer(torch.nn.Module):
     def _attention_projections(self, x: torch.Tensor) -> torch.Tensor:
         if not self.attention:
             return x
-        q = self.q(x)
-        self.k(x)
-        self.v(x)
+        q, _, _ = quant.project_many_q8([self.q, self.k, self.v], x)   # one launch, as one input
         return torch.add(x, self.o(q), alpha=0.01)   # residual keeps the scale bounded
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

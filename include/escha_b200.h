@@ -101,6 +101,17 @@ int escha_had128(const float *x, long nblocks, float *out, void *stream);
 int escha_w8a16(const void *x, const void *w8, const void *scale, int M, int N, int Kd, void *y,
                 void *stream);
 
+/* Up to four int8-weight linears of the SAME input rows in one launch: y[i] =
+ * escha_w8a16(x, w8[i], scale[i]) for i < n, each bit-identical to its own call
+ * (an output channel's sum does not depend on which launch computes it).  w8,
+ * scale, N and y are HOST tables of n entries; N[i] multiples of 16, Kd a
+ * multiple of 64.  The reference issues one mx.quantized_matmul per
+ * EschaQ8Linear (escha_mlx/quant.py:129-143); q/k/v of an attention block read
+ * the same rows, and at decode batch sizes each launch costs more than its
+ * bytes. */
+int escha_w8a16_many(const void *x, int n, const void *const *w8, const void *const *scale,
+                     const int *N, int Kd, int M, void *const *y, void *stream);
+
 /* Embedding lookup in an int8 table with one binary16 scale per row:
  *   out[r,:] = f16( f32(w8[ids[r],:]) * f32(scale[ids[r]]) ),  ids int64 [rows],
  * w8 [N,Kd] int8, out [rows,Kd] binary16, Kd a multiple of 16.  Replaces

@@ -355,6 +355,38 @@ def test_w8a16_tensor_core_path(cuda, oracle, M, N, Kd):
     assert torch.equal(lin(dev(x, cuda)), got)
 
 
+@pytest.mark.parametrize("M", [1, 8, 32, 45])
+@pytest.mark.parametrize("Ns,Kd", [((512, 64, 64), 256), ((4096, 512, 512), 2048), ((48,), 192),
+                                   ((16, 32, 48, 64), 64)])
+def test_w8a16_many_is_bit_identical_to_separate_launches(cuda, oracle, M, Ns, Kd):
+    """q/k/v-style: several int8 linears of one input in one launch; every output equals the
+    linear's own launch bit for bit and the oracle within the int8 path's bar."""
+    rng = np.random.default_rng(M + sum(Ns) + Kd)
+    ws = [synth.int8_linear(rng, n, Kd) for n in Ns]
+    x = synth.activations(rng, M, Kd)
+    lins = [quant.make_linear(w8, sc, device=cuda) for w8, sc in ws]
+    xd = dev(x, cuda)
+    got = quant.project_many_q8(lins, xd)
+    assert [tuple(g.shape) for g in got] == [(M, n) for n in Ns]
+    for g, lin, (w8, sc) in zip(got, lins, ws):
+        assert torch.equal(g, lin(xd))
+        assert rel_err(host(g), oracle.w8a16(x, w8, sc)) < 2e-3
+
+
+def test_w8a16_many_contract(cuda):
+    rng = np.random.default_rng(5)
+    w8, sc = synth.int8_linear(rng, 64, 128)
+    lin = quant.make_linear(w8, sc, device=cuda)
+    x = dev(synth.activations(rng, 2, 128), cuda)
+    with pytest.raises(ValueError, match="1..4"):
+        quant.w8a16_many(x, [(lin._w8, lin._scale)] * 5)
+    # shapes the joint launch does not take fall back to one launch each, same results
+    w8b, scb = synth.int8_linear(rng, 24, 128)      # 24 output rows: not a multiple of 16
+    odd = quant.make_linear(w8b, scb, device=cuda)
+    a, b = quant.project_many_q8([lin, odd], x)
+    assert torch.equal(a, lin(x)) and torch.equal(b, odd(x))
+
+
 @pytest.mark.parametrize("T", [1, 9, 40])
 def test_shared_expert_tail_vs_oracle(cuda, oracle, T):
     rng = np.random.default_rng(T)
