@@ -640,7 +640,8 @@ def main() -> None:
     # needs (q/k/v | o | gate/up | SwiGLU + down)
     joint_launches = args.group == "layer" and (world == 1 or replica) and M <= msl.FUSE_INPUT_MAX_ROWS
 
-    def layer_step(layer, x, bufs=None):
+    def layer_step(layer, x, bufs=None, joint=None):
+        joint = joint_launches if joint is None else joint
         if world > 1 and not replica and (pg is None or tc_shards):
             # NCCL form of the same exchange: an all-gather of every projection's f16 output
             # (also from 32 rows on, where each rank's shard runs on the tcgen05 kernel, whose
@@ -659,7 +660,7 @@ def main() -> None:
             g, u = tp_launch(layer, bufs, ("gate_proj", "up_proj"), x)
             (d,) = tp_launch(layer, bufs, ("down_proj",), g, u)   # full-width SwiGLU input
             return q, k, v, o, d
-        if joint_launches:
+        if joint:
             # every projection that reads the step's input in ONE launch (2-bit and 3-bit
             # streams side by side), SwiGLU + down in a second
             q, k, v, o, g, u = dense.project_many(
@@ -861,7 +862,9 @@ def main() -> None:
     def prefill_leg(rows: int = 256, steps: int = 12) -> dict:
         """The same layer at 256 rows on the tcgen05 GEMM (`--workload prefill`, shortened)."""
         xp = torch.randn((rows, HIDDEN), device=device, generator=gen).half()
-        pgraphs = [graphs.GraphedCall(lambda xx, L=L: layer_step(L, xx), [xp]) for L in sets]
+        # launch grouping of the prefill workload (q/k/v | o | gate/up | SwiGLU + down), whatever
+        # grouping the batch-1 step of this run uses
+        pgraphs = [graphs.GraphedCall(lambda xx, L=L: layer_step(L, xx, joint=False), [xp]) for L in sets]
         for gph in pgraphs:
             gph.replay()
         torch.cuda.synchronize()

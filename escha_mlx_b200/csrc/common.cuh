@@ -57,13 +57,6 @@ __device__ __forceinline__ uint32_t cba_decode_dup(uint32_t state16, uint32_t ma
     return as_u32(__hadd2(__low2half2(h), __high2half2(h)));
 }
 
-// The two binary16 halves of a state's hash, un-added: (lo, hi) in one register.
-__device__ __forceinline__ uint32_t cba_hash_halves(uint32_t state16, uint32_t mask, uint32_t x) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(state16 * 0xCBAC1FEDu), "r"(mask), "r"(x));
-    return r;
-}
-
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));

@@ -94,7 +94,7 @@ __device__ __forceinline__ __half swiglu_half(__half g16, __half u16) {
 __device__ __forceinline__ void stage_activations(const GemvMmaParams& p, const __half* xsrc, const float* rin,
                                                   const int* s_rows, int nrows, uint32_t blk0,
                                                   uint32_t cnt, uint32_t* s_x, uint32_t XS,
-                                                  uint32_t tid, uint32_t dup) {
+                                                  uint32_t tid) {
     const uint32_t lane = tid & 31u, warp = tid >> 5;
     if (p.input == kInputTransformed) {
         const uint32_t grp_per_row = cnt * 8u;  // 16-channel groups per row
@@ -107,11 +107,10 @@ __device__ __forceinline__ void stage_activations(const GemvMmaParams& p, const 
             const uint4 lo = src[0], hi = src[1];  // channels 0..7 and 8..15 of the group
             uint4* dst = reinterpret_cast<uint4*>(s_x + r * XS + v * 16u);
             // staged order c0 c8 c1 c9 ... c7 c15, each as a (x, 0) word
-            // dup = 1: (x, 0) words; dup = 0x10001: (x, x) words (see kernel comment on SUM)
-            dst[0] = make_uint4((lo.x & 0xFFFFu) * dup, (hi.x & 0xFFFFu) * dup, (lo.x >> 16) * dup, (hi.x >> 16) * dup);
-            dst[1] = make_uint4((lo.y & 0xFFFFu) * dup, (hi.y & 0xFFFFu) * dup, (lo.y >> 16) * dup, (hi.y >> 16) * dup);
-            dst[2] = make_uint4((lo.z & 0xFFFFu) * dup, (hi.z & 0xFFFFu) * dup, (lo.z >> 16) * dup, (hi.z >> 16) * dup);
-            dst[3] = make_uint4((lo.w & 0xFFFFu) * dup, (hi.w & 0xFFFFu) * dup, (lo.w >> 16) * dup, (hi.w >> 16) * dup);
+            dst[0] = make_uint4(lo.x & 0xFFFFu, hi.x & 0xFFFFu, lo.x >> 16, hi.x >> 16);
+            dst[1] = make_uint4(lo.y & 0xFFFFu, hi.y & 0xFFFFu, lo.y >> 16, hi.y >> 16);
+            dst[2] = make_uint4(lo.z & 0xFFFFu, hi.z & 0xFFFFu, lo.z >> 16, hi.z >> 16);
+            dst[3] = make_uint4(lo.w & 0xFFFFu, hi.w & 0xFFFFu, lo.w >> 16, hi.w >> 16);
         }
         return;
     }
@@ -140,10 +139,10 @@ __device__ __forceinline__ void stage_activations(const GemvMmaParams& p, const 
         // c = 4*(lane%4)+i within it, staged at word 2*(c%8) + c/8
         uint32_t* dst = s_x + r * XS + b * 128u + (lane >> 2) * 16u + ((lane & 1u) * 8u) +
                         ((lane >> 1) & 1u);
-        dst[0] = __half_as_ushort(__float2half_rn(__fmul_rn(v[0], p.rs))) * dup;
-        dst[2] = __half_as_ushort(__float2half_rn(__fmul_rn(v[1], p.rs))) * dup;
-        dst[4] = __half_as_ushort(__float2half_rn(__fmul_rn(v[2], p.rs))) * dup;
-        dst[6] = __half_as_ushort(__float2half_rn(__fmul_rn(v[3], p.rs))) * dup;
+        dst[0] = __half_as_ushort(__float2half_rn(__fmul_rn(v[0], p.rs)));
+        dst[2] = __half_as_ushort(__float2half_rn(__fmul_rn(v[1], p.rs)));
+        dst[4] = __half_as_ushort(__float2half_rn(__fmul_rn(v[2], p.rs)));
+        dst[6] = __half_as_ushort(__float2half_rn(__fmul_rn(v[3], p.rs)));
     }
 }
 
@@ -154,13 +153,11 @@ constexpr int kConsumerThreads = 256;   // 8 decode warps
 constexpr int kThreads = kConsumerThreads + 32;  // + 1 producer warp
 constexpr uint32_t kBarSlot0 = 2;       // named barriers 2..7: the ring's slots (1: the decode warps' own)
 
-// SUM = false (the default): each weight is rounded to binary16 exactly as the format
-// defines it, w = f16(lo) + f16(hi), kept as (w, w) against (x, 0).  SUM = true (opt-in,
-// ESCHA_B200_WEIGHT_SUM=tensor): the two halves go to the tensor core un-added, (lo, hi)
-// against (x, x), so the product uses lo + hi without the binary16 rounding of the sum:
-// one instruction fewer per weight, outputs within 3e-4 (max-norm) of the exact-weight
-// product instead of 2e-7.
-template <int K, int MT, bool SUM>
+// Each weight is rounded to binary16 exactly as the format defines it, w = f16(lo) + f16(hi),
+// and kept as (w, w) against activations staged as (x, 0).  GRP = true is the form for expert
+// row jobs, where a CTA may take several consecutive output blocks (p.ocb_group); the dense
+// form is compiled without that loop (measured: 1.8% on the batch-1 layer).
+template <int K, int MT, bool GRP>
 __global__ void __launch_bounds__(kThreads, 3)
 gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     constexpr int WPT = 8 * K;
@@ -179,7 +176,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
     const uint32_t g = lane >> 2, t = lane & 3u;
     // a CTA covers G consecutive output blocks of one projection (G > 1 only for unsplit
     // launches whose input range fits one staged chunk: the rows are staged once for all G)
-    const uint32_t G = static_cast<uint32_t>(p.ocb_group);
+    const uint32_t G = GRP ? static_cast<uint32_t>(p.ocb_group) : 1u;
     const uint32_t gocb = blockIdx.x * G, split = blockIdx.y, job = blockIdx.z;
     const uint32_t nblk = p.IC >> 7;
 
@@ -303,8 +300,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
         const uint32_t cnt = min(XCB, nb - c0);
         if (o == 0) {   // G > 1 means one chunk: staged once, reused by every output block
             named_barrier_sync(1, kConsumerThreads);
-            stage_activations(p, xsrc, rin, s_rows, nrows, b0 + c0, cnt, s_x, XS, tid,
-                              SUM ? 0x10001u : 1u);
+            stage_activations(p, xsrc, rin, s_rows, nrows, b0 + c0, cnt, s_x, XS, tid);
             named_barrier_sync(1, kConsumerThreads);
         }
         for (uint32_t cb = 0; cb < cnt; ++cb) {
@@ -322,7 +318,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
                 lc.states(wa[kk * ROW_WORDS], wb[kk * ROW_WORDS], muls, s);
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
-                    a[j] = SUM ? cba_hash_halves(s[j], hmask, hxor) : cba_decode_dup(s[j], hmask, hxor);
+                    a[j] = cba_decode_dup(s[j], hmask, hxor);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     // (x[2t], x[2t+8], x[2t+1], x[2t+9]) as (x, 0) words
@@ -408,7 +404,7 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
   }   // output blocks of this CTA (split launches have one)
 }
 
-template <int K, int MT, bool SUM>
+template <int K, int MT, bool GRP>
 cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
     constexpr int STAGE_WORDS = 8 * 8 * 8 * K;
     const size_t XS = static_cast<size_t>(p.xcb) * 128u + 16u;
@@ -416,7 +412,7 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
         (static_cast<size_t>(NS * STAGE_WORDS) + static_cast<size_t>(xrows + 1) * XS +
          (p.ocb_group > 1 ? static_cast<size_t>(p.rows_per_job) * 128u : 0u)) * 4u;
     static SmemLimit limit;   // per device: largest size already enabled
-    cudaError_t e = limit.ensure(gemv_mma_kernel<K, MT, SUM>, smem);
+    cudaError_t e = limit.ensure(gemv_mma_kernel<K, MT, GRP>, smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.total_ocb / p.ocb_group, p.splits, p.njobs);
@@ -428,7 +424,7 @@ cudaError_t launch_t(const GemvMmaParams& p, int xrows, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.pdl != kPdlOff ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<K, MT, SUM>, p);
+    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<K, MT, GRP>, p);
 }
 
 }  // namespace
@@ -449,16 +445,6 @@ static int pdl_mode() {
         return static_cast<int>(kPdlPrefetch);
     }();
     return mode;
-}
-
-// ESCHA_B200_WEIGHT_SUM=tensor selects the un-rounded lo + hi product (see the kernel);
-// read once per process.  Anything else, or unset: exact binary16 weights.
-static bool weight_sum_in_tensor_core() {
-    static const bool on = [] {
-        const char* v = std::getenv("ESCHA_B200_WEIGHT_SUM");
-        return v != nullptr && !std::strcmp(v, "tensor");
-    }();
-    return on;
 }
 
 cudaError_t gemv_mma_status(int* host_status) {
@@ -524,7 +510,7 @@ cudaError_t launch_gemv_mma(const GemvMmaParams& params, cudaStream_t st) {
             if (fits) { p.ocb_group = gsize; break; }
         }
     }
-    if (weight_sum_in_tensor_core()) {
+    if (p.jobs) {
         if (p.K == 2) return rows == 8 ? launch_t<2, 1, true>(p, xrows, st) : launch_t<2, 2, true>(p, xrows, st);
         return rows == 8 ? launch_t<3, 1, true>(p, xrows, st) : launch_t<3, 2, true>(p, xrows, st);
     }

@@ -11,6 +11,14 @@
 #include <cstdio>
 #include <vector>
 #include "../common.cuh"
+
+// the two binary16 halves of a state's hash, un-added (the variant without the format's
+// rounding point; measurement only, no kernel of the library decodes this way)
+__device__ __forceinline__ uint32_t cba_hash_halves(uint32_t state16, uint32_t mask, uint32_t x) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(state16 * 0xCBAC1FEDu), "r"(mask), "r"(x));
+    return r;
+}
 using namespace escha;
 
 #define DI __device__ __forceinline__
