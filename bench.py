@@ -383,7 +383,10 @@ def run_moe(args, rank: int, world: int, local_rank: int) -> None:
                     "h2d_bytes_per_step": T * cfg["hidden"] * 2 // steps_per_replay,
                     "d2h_bytes_per_step": T * cfg["hidden"] * 2 // steps_per_replay},
             "touched_gb_per_s": gbs, "pct_of_hbm_peak": 100.0 * gbs / (peak * world),
-            "gpu_launches": (7 + (4 if full_step else 0)) * MOE_LAYERS * passes,
+            # per layer: router, two expert legs, the shared expert's gate/up and the tail kernel
+            # (+ the cross-GPU barrier under expert parallelism; + int8 q/k/v in one launch and o
+            # in another for the full step)
+            "gpu_launches": (5 + (1 if pg is not None else 0) + (2 if full_step else 0)) * MOE_LAYERS * passes,
             "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s",
                          "frac": gbs / world / peak, "traffic": None,
                          "kernel": "whole step: bytes of routed expert streams, int8 matrices and "
@@ -528,7 +531,8 @@ def main() -> None:
                          "it has alone (bit-identical to separate calls)")
     ap.add_argument("--group", default="layer", choices=["layer", "model"],
                     help="launch grouping at small batch: layer = the projections that read the "
-                         "step input share one launch (2 launches per step); model = q/k/v | o | "
+                         "step input share one launch per rate (3 launches per step; 2 with the persistent "
+                         "kernel, which mixes rates); model = q/k/v | o | "
                          "gate/up | SwiGLU+down (4 launches)")
     ap.add_argument("--no-moe-leg", action="store_true",
                     help="skip the short MoE-layer measurement appended to the default line")
