@@ -358,7 +358,9 @@ gemv_mma_kernel(const __grid_constant__ GemvMmaParams p) {
             if (pr.rout) finalize_row<true>(v, lane, rout_blk, pr, off, p.rs);
             else finalize_row<false>(v, lane, rout_blk, pr, off, p.rs);
         }
-        if (pr.npeer) __threadfence_system();
+        // stores into other GPUs' buffers: one system-wide fence per CTA, after its last output
+        // block (a fence per block makes every warp wait out an NVLink round trip each time)
+        if (pr.npeer && o + 1u == G) __threadfence_system();
         continue;   // the next output block of this CTA (the barrier before its rows are
                     // written keeps them from overtaking the reads above)
     }

@@ -111,3 +111,25 @@ def test_synth_coded_bytes():
     assert synth.coded_bytes(4096, 4096, 2) == 4_194_304
     total = sum(synth.coded_bytes(ic, oc, k) for _, ic, oc, k in synth.DENSE_LAYER_27B)
     assert total == 117_309_440
+
+
+def test_wave_splits_policy_is_shape_only(monkeypatch):
+    """Launch-wide split factors on a 148-SM part (444 resident CTA slots): the fewest waves
+    the launch fills to 85%, never fewer than two input blocks per split, same factor for
+    every projection of the launch, and nothing but shapes goes in."""
+    from escha_mlx_b200 import msl
+    monkeypatch.setattr(msl, "sm_count", lambda: 148)
+    # q/k/v/o of the 27B-class layer: 104 output blocks x 4 = 416 CTAs, one wave
+    assert msl.wave_splits(5120, [6144, 1024, 1024, 5120]) == [4, 4, 4, 4]
+    # gate/up: 272 blocks do not fill one wave to 85% at any factor; x 3 = 816 of 888 (two waves)
+    assert msl.wave_splits(5120, [17408, 17408]) == [3, 3]
+    # down: 40 blocks x 11 = 440 CTAs
+    assert msl.wave_splits(17408, [5120]) == [11]
+    # the 4096x4096 gate projection: 32 blocks x 13 = 416
+    assert msl.wave_splits(4096, [4096]) == [13]
+    # two input blocks per split at least: a 256-wide input is never split
+    assert msl.wave_splits(256, [128]) == [1]
+    # wider than eight waves at factor 1: stays unsplit
+    assert msl.wave_splits(5120, [17408 * 16]) == [1]
+    # row jobs multiply the block count: 8 x 57 = 456 blocks, x 5 = 2280 CTAs fill six waves to 86%
+    assert msl.wave_splits(2048, [1024], njobs=57) == [5]
