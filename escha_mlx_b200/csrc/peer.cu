@@ -13,6 +13,9 @@
 // (acquire, system scope) until it reaches the epoch.  The epoch lives on the device, so
 // the launch is identical every time and can be replayed from a CUDA graph.
 //
+// The launch is chained with programmatic dependent launch (unless ESCHA_B200_PDL=off), so
+// only its polling, not its launch latency, sits between producer and consumer.
+//
 // The kernels of different ranks run on different GPUs at the same time; ranks must
 // never share a GPU.  The poll is bounded (about two seconds): a rank that never shows
 // up raises the status word instead of hanging the others.
@@ -38,6 +41,11 @@ __device__ __forceinline__ int32_t load_acquire_sys(const int32_t* p) {
 __global__ void __launch_bounds__(32)
 peer_barrier_kernel(const PeerBarrierParams p, const uint32_t poll_limit) {
     const int lane = threadIdx.x, n = p.nranks;
+    // chained to its neighbours in the stream (programmatic dependent launch): the warp is
+    // resident while the producing kernel drains and the consumer's CTAs are scheduled while
+    // it polls; it waits here until the producer has completed and its stores are visible
+    grid_launch_dependents();
+    grid_dependency_wait();
     int32_t epoch = 0;
     if (lane == 0) {
         epoch = p.local[n] + 1;
@@ -66,8 +74,7 @@ peer_barrier_kernel(const PeerBarrierParams p, const uint32_t poll_limit) {
 void peer_barrier_poll_limit(unsigned polls) { g_poll_limit = polls ? polls : kPollLimit; }
 
 cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t st) {
-    peer_barrier_kernel<<<1, 32, 0, st>>>(p, g_poll_limit);
-    return cudaGetLastError();
+    return launch_chained(peer_barrier_kernel, dim3(1), dim3(32), 0, st, p, g_poll_limit);
 }
 
 }  // namespace escha
