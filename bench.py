@@ -618,8 +618,11 @@ def main() -> None:
                 off += M * oc
             gathered.append(bufs)
 
-    def tp_launch(layer, bufs, names, x, x_up=None):
-        """One fused launch of the named projections' shards into their gathered buffers."""
+    def tp_launch(layer, bufs, names, x, x_up=None, join=True):
+        """One fused launch of the named projections' shards into their gathered buffers,
+        closed by the cross-GPU barrier unless a later launch's barrier covers it (a rank's
+        barrier kernel runs after all its earlier launches, so one barrier completes the
+        gathers of every launch before it)."""
         ws = [layer[n]._w for n in names]
         fuse_in = M <= msl.FUSE_INPUT_MAX_ROWS
         mode = (msl.INPUT_SWIGLU if x_up is not None else msl.INPUT_RAW) if fuse_in \
@@ -634,7 +637,8 @@ def main() -> None:
             [w.rout for w in ws], ws[0].K, ws[0].IC, [w.OC for w in ws], input_mode=mode,
             x_up=x_up, rs=msl.RS, xs=xs, gather=[(bufs[n], rank * w.OC) for n, w in zip(names, ws)],
             splits=msl.wave_splits(ws[0].IC, [w.OC for w in ws]) if args.wave else None)
-        pg.barrier()
+        if join:
+            pg.barrier()
         return outs
 
     tc_shards = False   # from 32 rows on ranks are row replicas (above); shards stay on the GEMV
@@ -660,7 +664,9 @@ def main() -> None:
             return q, k, v, o, d
         if world > 1 and not replica:
             # one launch (and one cross-GPU join) per rate among the projections of the input
-            q, k, v, o = tp_launch(layer, bufs, ("q_proj", "k_proj", "v_proj", "o_proj"), x)
+            # q/k/v/o and gate/up read the same input: nobody needs q/k/v/o gathered before
+            # gate/up has run, so the two launches share the second one's barrier
+            q, k, v, o = tp_launch(layer, bufs, ("q_proj", "k_proj", "v_proj", "o_proj"), x, join=False)
             g, u = tp_launch(layer, bufs, ("gate_proj", "up_proj"), x)
             (d,) = tp_launch(layer, bufs, ("down_proj",), g, u)   # full-width SwiGLU input
             return q, k, v, o, d
@@ -682,7 +688,7 @@ def main() -> None:
     if M <= msl.FUSE_INPUT_MAX_ROWS:
         # joint: one launch for all rates (persistent kernel) or one per rate
         per_step = (2 if msl.mixed_rates_supported() else 3) if joint_launches else 4
-        launches_per_step = per_step if world == 1 else 6   # 3 fused GEMV + 3 peer barriers
+        launches_per_step = per_step if world == 1 else 5   # 3 fused GEMV + 2 peer barriers
     elif msl.use_prefill_kernel(M) and (world == 1 or replica):
         # four input-transform launches (q/k/v, o, gate/up, SwiGLU + down), the tcgen05 GEMMs,
         # and a plane sum + output transform for every projection split more than 4 ways along K

@@ -57,6 +57,15 @@ def test_host_side_validation_raises_value_error():
         check(lib.escha_coded_gemv(fake, fake, None, 1, 512, 128, 2, 2, 0.5, fake, 16, fake, None))
     with pytest.raises(ValueError, match="rows per job"):
         check(lib.escha_moe_group_rows(fake, 8, 4, 5, fake, 100, None, None))
+    # host tables of the joint int8 launch: plain arrays, no alignment demanded of the tables
+    tab = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    widths = (ctypes.c_int * 2)(64, 24)
+    with pytest.raises(ValueError, match="1..4 linears"):
+        check(lib.escha_w8a16_many(fake, 5, tab, tab, widths, 128, 1, tab, None))
+    with pytest.raises(ValueError, match="multiple of 64"):
+        check(lib.escha_w8a16_many(fake, 2, tab, tab, widths, 96, 1, tab, None))
+    with pytest.raises(ValueError, match="multiples of 16"):
+        check(lib.escha_w8a16_many(fake, 2, tab, tab, widths, 128, 1, tab, None))
 
 
 def test_pure_helpers():
