@@ -457,7 +457,7 @@ def moe_legs(device, token_counts=(1, 8, 64), replays: int = 10) -> dict:
     return out
 
 
-def c1_leg(device, reps: int = 5) -> dict:
+def c1_leg(device, reps: int = 5, e2e: bool = False) -> dict:
     """The single dense coded projection of the reference's own gate (4096x4096, 2-bit, one
     row; escha_mlx bench/p0_gates.py:111-118): 4 MiB of code, below launch latency and smaller
     than L2, so two figures, both from CUDA-graph replays of 128 back-to-back launches:
@@ -500,7 +500,72 @@ def c1_leg(device, reps: int = 5) -> dict:
         gbs = IC * OC * K // 8 / (us * 1e-6) / 1e9
         out[name] = {"us_per_launch": us, "gb_per_s": gbs, "frac_of_hbm_peak": gbs / peak,
                      "weight_buffers": nbuf if name == "hbm_resident" else 1}
+    if e2e:
+        # through the module call with a pinned host row in and the host result out, every
+        # launch (one single-launch graph per weight buffer, copies on the launching stream)
+        gs = [graphs.GraphedCall(lambda xx, lin=lin: lin(xx), [x]) for lin in lins]
+        xh = torch.randn((1, IC)).half().pin_memory()
+        yh = torch.empty((1, OC), dtype=torch.float16).pin_memory()
+        for i in range(8):
+            yh.copy_(gs[i % nbuf](xh), non_blocking=True)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = 4 * launches
+        e0.record()
+        for i in range(n):
+            yh.copy_(gs[i % nbuf](xh), non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / n
+        for g in gs:
+            g.close()
+        out["e2e"] = {"us_per_launch": us, "gb_per_s": IC * OC * K // 8 / (us * 1e-6) / 1e9,
+                      "launches": n, "h2d_bytes_per_step": IC * 2, "d2h_bytes_per_step": OC * 2}
     return out
+
+
+def run_c1(args, rank: int, world: int, local_rank: int) -> None:
+    """`--workload c1`: the reference's simplest configuration as a line of its own.  A step
+    is one launch of the 4096x4096 2-bit projection at one row (input transform, GEMV and
+    output transform in the launch), replayed 128 at a time from a CUDA graph; `value` is the
+    HBM-resident figure (64 rotating weight buffers), the L2-resident one rides along.  The
+    path does not shard at this size: N > 1 runs independent replicas (rank 0 reports its own
+    time; nothing is exchanged)."""
+    import torch
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    reps = max(5, args.repeats)
+    with ClockSampler(local_rank, active=(rank == 0)) as clocks:
+        leg = c1_leg(device, reps=reps, e2e=True)
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peak_gbs()
+    hbm, l2 = leg["hbm_resident"], leg["l2_resident"]
+    launches = leg["launches_per_replay"] * reps
+    line = {
+        "metric": METRIC, "value": hbm["gb_per_s"] * world, "unit": "GB/s", "n_gpus": world,
+        "steps": launches, "warmup": 3 * leg["launches_per_replay"],
+        "ms_per_step": hbm["us_per_launch"] * 1e-3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 weights, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": leg["workload"], "code_bytes_per_step": leg["code_bytes"],
+                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                   "l2_policy": "value: 64 weight buffers (256 MiB) rotated, every launch misses L2; "
+                                "l2_resident: one buffer"},
+        "l2_resident": l2,
+        "e2e": {"value": leg["e2e"]["gb_per_s"] * world, "unit": "GB/s",
+                "h2d_bytes_per_step": leg["e2e"]["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": leg["e2e"]["d2h_bytes_per_step"],
+                "note": "one graph launch per step with the host row copied in and the result "
+                        "copied out on the same stream: bound by three enqueues per step on the host"},
+        "gpu_launches": 2 * launches,
+        "roofline": {"bound": "hbm", "achieved": hbm["gb_per_s"], "peak": peak, "unit": "GB/s",
+                     "frac": hbm["gb_per_s"] / peak, "traffic": None,
+                     "kernel": "gemv_mma_kernel<2,1> (coded GEMV + fused transforms), one launch per step",
+                     "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"},
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line), flush=True)
 
 
 # --------------------------------------------------------------------------- GPU side
@@ -512,11 +577,12 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "prefill", "moe", "step"],
+    ap.add_argument("--workload", default="dense", choices=["dense", "prefill", "moe", "step", "c1"],
                     help="dense: 27B-class layer at decode batch --batch (default, the headline); "
                          "prefill: the same layer at 256 rows on the tcgen05 GEMM, reported in "
                          "TFLOP/s; moe: one 35B-A3B-class MoE layer at --tokens; step: 40-layer "
-                         "MoE decode step at batch 32")
+                         "MoE decode step at batch 32; c1: the single 4096x4096 2-bit GEMV at one row, "
+                         "HBM- and L2-resident")
     ap.add_argument("--tokens", type=int, default=8, help="tokens per step for --workload moe")
     ap.add_argument("--layers", type=int, default=0,
                     help="resident MoE layers for --workload moe/step (default 40; fewer only for "
@@ -545,6 +611,9 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "c1":
+        run_c1(args, rank, world, local_rank)
         return
     if args.workload in ("moe", "step"):
         run_moe(args, rank, world, local_rank)
