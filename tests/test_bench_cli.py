@@ -39,3 +39,32 @@ def test_gpu_arm_refuses_to_run_without_a_device():
     run = _run("--steps", "1")
     assert run.returncode != 0
     assert "needs a CUDA device" in (run.stderr + run.stdout)
+
+
+def test_clock_sampler_reads_a_fake_nvidia_smi(tmp_path, monkeypatch):
+    """The sampler starts the timed region only after the first sample, takes rows of every
+    GPU of the job from one process, reports the median SM clock and the throttle reasons
+    it saw, and an inactive sampler (ranks other than 0) starts nothing."""
+    import importlib.util
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text(
+        "#!/bin/sh\n"
+        "while true; do\n"
+        "  echo '0, 1965, 1965, 412.5, Not Active, Not Active, Not Active, Not Active'\n"
+        "  echo '1, 1935, 1965, 988.0, Not Active, Not Active, Not Active, Active'\n"
+        "  sleep 0.02\n"
+        "done\n")
+    fake.chmod(0o755)
+    monkeypatch.setenv("PATH", f"{tmp_path}{os.pathsep}{os.environ['PATH']}")
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    with bench.ClockSampler([0, 1]) as clocks:
+        assert clocks.rows, "the region must not start before the first sample"
+    got = clocks.summary()
+    assert got["samples"] >= 2 and got["sm_max_mhz"] == 1965.0
+    assert 1935.0 <= got["sm_mhz"] <= 1965.0
+    assert got["reasons"] == ["sw_power_cap"]
+    with bench.ClockSampler([0, 1], active=False) as idle:
+        pass
+    assert idle.summary() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
