@@ -65,6 +65,7 @@ SIGNATURES = {
     "escha_coded_gemv_status": (_i, []),
     "escha_debug_gemv_stall": (None, [_i, ctypes.c_uint]),
     "escha_debug_peer_poll_limit": (None, [ctypes.c_uint]),
+    "escha_debug_gemm_tc_stall": (None, [_i, ctypes.c_uint]),
     "escha_moe_route": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
                             _vp, _i, _vp, _sz, _vp]),
     "escha_moe_shared_finish": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),

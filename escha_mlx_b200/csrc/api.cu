@@ -899,6 +899,8 @@ void escha_debug_gemv_stall(int on, unsigned limit) { escha::gemv_stream_test_st
 
 void escha_debug_peer_poll_limit(unsigned polls) { escha::peer_barrier_poll_limit(polls); }
 
+void escha_debug_gemm_tc_stall(int on, unsigned limit) { escha::gemm_tcm_test_stall(on, limit); }
+
 int escha_coded_gemm_tc_status(void) {
     int st = 0;
     if (escha::gemm_tc_status(&st) != cudaSuccess) return -1;

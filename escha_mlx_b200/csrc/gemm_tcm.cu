@@ -226,7 +226,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
         const uint32_t my_cols = tmem + ((32u * qd) << 16) + kWCol0 + 16u * kq;
         for (uint32_t c = 0; c < nstage; ++c) {
             const uint32_t cslot = c % kCodeStages;
-            if (!mbar_wait_relaxed(cfull0 + 8u * cslot, (c / kCodeStages) & 1u)) {
+            if (!mbar_wait_relaxed(cfull0 + 8u * cslot, (c / kCodeStages) & 1u, p.wait_limit)) {
                 ok = false;
                 break;
             }
@@ -258,7 +258,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
             }
             const uint32_t wslot = c % kWStages;
             if (c >= kWStages && !mbar_wait_relaxed(free0 + 8u * ((c - kWStages) % kFreeBars),
-                                                    ((c - kWStages) / kFreeBars) & 1u)) {
+                                                    ((c - kWStages) / kFreeBars) & 1u, p.wait_limit)) {
                 ok = false;
                 break;
             }
@@ -275,8 +275,8 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
         const uint32_t idesc = idesc_for(128u * MT);
         for (uint32_t c = 0; c < nstage; ++c) {
             const uint32_t ws = c % kWStages, xs = c % kXStages;
-            if (!mbar_wait_relaxed(wfull0 + 8u * ws, (c / kWStages) & 1u) ||
-                !mbar_wait_relaxed(xfull0 + 8u * xs, (c / kXStages) & 1u)) {
+            if (!mbar_wait_relaxed(wfull0 + 8u * ws, (c / kWStages) & 1u, p.wait_limit) ||
+                !mbar_wait_relaxed(xfull0 + 8u * xs, (c / kXStages) & 1u, p.wait_limit)) {
                 ok = false;
                 break;
             }
@@ -303,7 +303,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
             for (uint32_t c = 0; c < nstage; ++c) {
                 const uint32_t slot = c % kXStages;
                 if (c >= kXStages && !mbar_wait_relaxed(free0 + 8u * ((c - kXStages) % kFreeBars),
-                                                        ((c - kXStages) / kFreeBars) & 1u)) {
+                                                        ((c - kXStages) / kFreeBars) & 1u, p.wait_limit)) {
                     ok = false;
                     break;
                 }
@@ -324,13 +324,13 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
         for (uint32_t c = 0; c < nstage; ++c) {
             const uint32_t cslot = c % kCodeStages;
             if (c >= kCodeStages &&
-                !mbar_wait_relaxed(cempty0 + 8u * cslot, ((c / kCodeStages) - 1u) & 1u)) {
+                !mbar_wait_relaxed(cempty0 + 8u * cslot, ((c / kCodeStages) - 1u) & 1u, p.wait_limit)) {
                 ok = false;
                 break;
             }
             if (lane == 0) mbar_arrive_expect_tx(cfull0 + 8u * cslot, kCodeStageBytes);
             __syncwarp();
-            if (lane < 8)
+            if (lane < 8 && !p.test_stall)   // the test hook announces the bytes and never sends them
                 bulk_copy_g2s(code0 + cslot * kCodeStageBytes + lane * kRowBytes, grow, kRowBytes,
                               cfull0 + 8u * cslot);
             grow += 8u * kt_words;
@@ -345,7 +345,7 @@ gemm_tcm_kernel(const __grid_constant__ GemmTcParams p, const __grid_constant__ 
         // warp w reads lanes 32(w&3).. (the only ones it may address) and a quarter of the columns
         const uint32_t qd = warp & 3u, cq = (warp - kServiceWarps) >> 2;
         bool ready = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0 && nstage > 0;
-        if (ready && !mbar_wait_relaxed(done, 0u)) {
+        if (ready && !mbar_wait_relaxed(done, 0u, p.wait_limit)) {
             ready = false;
             if (lane == 0) atomicExch(&g_gemm_tcm_status, 2);
         }
@@ -459,7 +459,20 @@ bool gemm_tcm_supports(const GemmTcParams& p) {
     return p.IC % kStageK == 0 && p.splits >= 1 && p.splits <= p.IC / kStageK;
 }
 
-cudaError_t launch_gemm_tcm_many(const GemmTcParams& p, const __half* const* xh_more, cudaStream_t st) {
+namespace {
+int g_tcm_stall = 0;                    // host side; tests only
+unsigned g_tcm_wait_limit = 1u << 21;   // about two seconds per wait
+}  // namespace
+
+void gemm_tcm_test_stall(int on, unsigned limit) {
+    g_tcm_stall = on ? 1 : 0;
+    g_tcm_wait_limit = (on && limit) ? limit : (1u << 21);
+}
+
+cudaError_t launch_gemm_tcm_many(const GemmTcParams& p_in, const __half* const* xh_more, cudaStream_t st) {
+    GemmTcParams p = p_in;
+    p.wait_limit = g_tcm_wait_limit;
+    p.test_stall = g_tcm_stall;
     const bool two = p.M > 128;
     if (p.K == 2) return two ? launch_tcm<2, 2>(p, xh_more, st) : launch_tcm<2, 1>(p, xh_more, st);
     return two ? launch_tcm<3, 2>(p, xh_more, st) : launch_tcm<3, 1>(p, xh_more, st);

@@ -249,6 +249,10 @@ struct GemmTcParams {
     };
     int nproj;      // 0 or 1: just the projection above
     More more[2];
+    // set by the launcher: tries of about a microsecond every bounded wait gets, and the test
+    // hook that announces the weight copies without issuing them (so that the waits run out)
+    uint32_t wait_limit;
+    int test_stall;
 };
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);
 cudaError_t launch_planes_out(const float* planes, const float* rout, __half* y, int M, int OC,
@@ -258,6 +262,7 @@ cudaError_t launch_planes_out_many(int n, const float* const* planes, const floa
                                    cudaStream_t st);
 cudaError_t launch_sum_planes(const float* planes, float* mid, size_t n, int splits, cudaStream_t st);
 cudaError_t gemm_tc_status(int* host_status);
+void gemm_tcm_test_stall(int on, unsigned limit);
 // the same product with the decoded weights handed over through tensor memory (gemm_tcm.cu)
 bool gemm_tcm_supports(const GemmTcParams& p);
 bool gemm_tcm_cluster_sum(int IC, int splits);

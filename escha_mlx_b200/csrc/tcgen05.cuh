@@ -8,11 +8,13 @@ namespace escha {
 
 // Bounded wait that does not poll: a waiting warp must not take issue slots from the
 // decode warps, which are what limits this kernel.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
+                                                  uint32_t limit = 1u << 21) {
     // try_wait with a suspend-time hint parks the thread in hardware until the phase
     // completes or the hint (in nanoseconds) runs out: one instruction per microsecond of
     // waiting instead of a polling loop
-    for (uint32_t it = 0; it < (1u << 21); ++it) {
+    // (`limit` tries: about two seconds by default; a test shortens it)
+    for (uint32_t it = 0; it < limit; ++it) {
         uint32_t ok;
         asm volatile(
             "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"

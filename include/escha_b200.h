@@ -425,6 +425,13 @@ int escha_coded_gemv_status(void);
  * usable.  on == 0 restores normal operation. */
 void escha_debug_gemv_stall(int on, unsigned limit);
 
+/* The same hook for the tensor-memory prefill GEMM (escha_coded_gemm_tc[_many] in its
+ * default form): weight copies are announced and not issued, every bounded wait of the
+ * kernel gets `limit` tries of about a microsecond, all roles run out of patience, meet at
+ * the CTA barrier, free their tensor memory and return; escha_coded_gemm_tc_status()
+ * reports it (that word is not cleared by reading: use a process of its own). */
+void escha_debug_gemm_tc_stall(int on, unsigned limit);
+
 /* Test hook, no counterpart in the reference: the number of polls (about 100 ns apart) an
  * escha_peer_barrier launch makes for a peer before it gives up, raises word nranks+1 of
  * local_flags (see escha_peer_barrier) and returns; 0 restores the default
