@@ -297,15 +297,17 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 cudaError_t encode_x_map(CUtensorMap* map, const __half* xh, int M, int IC, int rows_per_box) {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
+    // resolved once per process (the initialisation of a function-local static is safe from
+    // several host threads); nullptr if the driver does not offer the entry point
+    static const EncodeTiledFn fn = [] {
         void* sym = nullptr;
         cudaDriverEntryPointQueryResult q;
-        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
-        if (e != cudaSuccess) return e;
-        if (q != cudaDriverEntryPointSuccess || !sym) return cudaErrorNotSupported;
-        fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
+        const cudaError_t e =
+            cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+        return (e == cudaSuccess && q == cudaDriverEntryPointSuccess) ? reinterpret_cast<EncodeTiledFn>(sym)
+                                                                      : static_cast<EncodeTiledFn>(nullptr);
+    }();
+    if (!fn) return cudaErrorNotSupported;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(IC), static_cast<cuuint64_t>(M)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(IC) * 2u};   // bytes between rows
     const cuuint32_t box[2] = {static_cast<cuuint32_t>(kChunkK), static_cast<cuuint32_t>(rows_per_box)};
