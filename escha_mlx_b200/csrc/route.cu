@@ -90,7 +90,7 @@ __device__ __forceinline__ void topk_softmax_token(const RouteParams& p, int tok
 
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const RouteParams p) {
-    extern __shared__ int32_t s_dyn[];  // phase 3: [El + 1] job offsets, then [m] local experts
+    extern __shared__ int32_t s_dyn[];  // phase 3: [El + 1] job offsets, [m] local experts, [El] + [1 or 8][El] counts
     __shared__ float s_part[8][8];
     __shared__ int s_flag;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -169,25 +169,36 @@ moe_route_kernel(const RouteParams p) {
     }
 
     // ---- phase 3: rows -> jobs.  Rows are counted per expert with shared-memory
-    // atomics and the counts turned into job offsets; then thread e fills in the headers
-    // of expert e's jobs, and one warp walks the rows in ascending order, 32 at a time,
-    // giving each row its rank among the rows of its expert (lanes of one expert find each
-    // other with a warp match; a running count per expert carries over between the groups
-    // of 32), so jobs ascend by expert and rows ascend inside a job -- the stable order
-    // moe.build_groups produces -- whatever order the atomics ran in.
+    // atomics (per expert, and beyond 128 rows per expert and eighth of the rows) and the
+    // counts turned into job offsets; then thread e fills in the headers of expert e's jobs,
+    // and the rows are walked in ascending order, 32 at a time, giving each row its rank
+    // among the rows of its expert: rows of earlier ranges (a prefix of the counts) + rows
+    // seen so far in this range (a running count) + lanes before it in the group of 32
+    // (lanes of one expert find each other with a warp match).  So jobs ascend by expert
+    // and rows ascend inside a job -- the stable order moe.build_groups produces --
+    // whatever order the atomics ran in.
     const int32_t* row_ids = p.ids_in ? p.ids_in : p.ids;
     const int m = p.T * p.top_k, El = p.e_hi - p.e_lo, R = p.R;
     int32_t* s_off = s_dyn;            // [El + 1]
     int32_t* s_loc = s_dyn + El + 1;   // [m] local expert of each row, -1 if another rank's
     int32_t* s_cnt = s_loc + m;        // [El] rows of each expert
-    int32_t* s_run = s_cnt + El;       // [El] rows of each expert emitted so far
+    int32_t* s_run = s_cnt + El;       // [ranges][El] rows of each expert in (then: before) each range
+    // Beyond 128 rows the rows are cut into eight contiguous ranges, one per warp, of a
+    // multiple of 32 rows; up to 128 rows one warp walks them all (measured: the set-up of
+    // the ranges costs small batches more than the shorter walk saves).
+    const int n_ranges = m > 128 ? 8 : 1;
+    const int per_warp = n_ranges == 1 ? ((m + 31) & ~31) : (((m + 255) >> 8) << 5);
     for (int e = tid; e <= El; e += blockDim.x) s_off[e] = 0;
+    for (int e = tid; e < n_ranges * El; e += blockDim.x) s_run[e] = 0;
     __syncthreads();
     for (int i = tid; i < m; i += blockDim.x) {
         const int e = __ldcg(row_ids + i);
         const int loc = (e >= p.e_lo && e < p.e_hi) ? e - p.e_lo : -1;
         s_loc[i] = loc;
-        if (loc >= 0) atomicAdd(&s_off[loc + 1], 1);
+        if (loc >= 0) {
+            atomicAdd(&s_off[loc + 1], 1);
+            if (n_ranges > 1) atomicAdd(&s_run[(i / per_warp) * El + loc], 1);
+        }
     }
     __syncthreads();
     // counts -> job offsets: exclusive prefix sum of ceil(count / R) over the experts.
@@ -203,7 +214,7 @@ moe_route_kernel(const RouteParams p) {
         for (int k = 0; k < 4; ++k) {
             const int e = e_first + k;
             const int cnt = (k < per && e < El) ? s_off[e + 1] : 0;
-            if (k < per && e < El) { s_cnt[e] = cnt; s_run[e] = 0; }
+            if (k < per && e < El) s_cnt[e] = cnt;
             local[k] = (cnt + R - 1) >> rshift;
             sum += local[k];
         }
@@ -242,21 +253,36 @@ moe_route_kernel(const RouteParams p) {
             }
         }
     }
-    // rows, in ascending order
-    if (warp == 0) {
-        for (int i0 = 0; i0 < m; i0 += 32) {
+    // an expert's rows before each range: exclusive prefix over the ranges
+    if (n_ranges > 1) {
+        for (int e = tid; e < El; e += blockDim.x) {
+            int before = 0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                const int here = s_run[w * El + e];
+                s_run[w * El + e] = before;
+                before += here;
+            }
+        }
+        __syncthreads();
+    }
+    // rows, in ascending order inside every range: a warp walks its range 32 rows at a time
+    if (warp < n_ranges) {
+        int32_t* const run = s_run + warp * El;
+        const int i_end = min(m, (warp + 1) * per_warp);
+        for (int i0 = warp * per_warp; i0 < i_end; i0 += 32) {
             const int i = i0 + lane;
-            const int e = i < m ? s_loc[i] : -1;
+            const int e = i < i_end ? s_loc[i] : -1;
             // lanes holding rows of the same expert (rows of other ranks' experts and lanes
             // past the end match among themselves and are skipped)
             const unsigned same = __match_any_sync(0xFFFFFFFFu, e);
             if (e >= 0) {
-                const int k = s_run[e] + __popc(same & ((1u << lane) - 1u));
+                const int k = run[e] + __popc(same & ((1u << lane) - 1u));
                 const int j = s_off[e] + (k >> rshift);
                 if (j < p.njobs_cap) p.jobs[j].rows[k & rmask] = i;
             }
             __syncwarp();
-            if (e >= 0 && lane == 31 - __clz(same)) s_run[e] += __popc(same);
+            if (e >= 0 && lane == 31 - __clz(same)) run[e] += __popc(same);
             __syncwarp();
         }
     }
@@ -269,7 +295,8 @@ moe_route_kernel(const RouteParams p) {
 }  // namespace
 
 size_t route_shared_bytes(int T, int top_k, int e_lo, int e_hi) {
-    return (3 * static_cast<size_t>(e_hi - e_lo) + 1 + static_cast<size_t>(T) * top_k) * sizeof(int32_t);
+    const size_t m = static_cast<size_t>(T) * top_k;
+    return ((m > 128 ? 10 : 3) * static_cast<size_t>(e_hi - e_lo) + 1 + m) * sizeof(int32_t);
 }
 
 cudaError_t launch_moe_route(const RouteParams& p, cudaStream_t st) {
